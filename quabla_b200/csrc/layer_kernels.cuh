@@ -1,0 +1,265 @@
+// Layer-wise engine: the kernels that run a tanh MLP of any width over a chunk
+// of collocation points while carrying the primal and the derivative streams.
+//
+// Activation layout for a chunk of C points and a layer of width d:
+//   [S][C][d], stream-major, d contiguous,
+// so the S streams of a layer form ONE row-major matrix of S*C rows and every
+// weight contraction is a single GEMM over all streams (the reference issues a
+// batch=B, M=1 strided-batched GEMM per stream instead,
+// crates/quabla-core/src/tensor_ir/cuda.rs:4936-5035).
+#pragma once
+#include "jet_math.cuh"
+
+namespace qb {
+
+// ---------------------------------------------------------------------------
+// Tiled SIMT GEMM, C[m][n] = sum_k A(m,k) * B(k,n), with arbitrary element
+// strides so that the same kernel serves
+//   forward   Z  = H W            (A k-fast, B n-fast)
+//   dgrad     G' = G W^T          (A k-fast, B k-fast)
+//   wgrad     dW = H^T G          (A m-fast, B n-fast, split over k = rows)
+// gridDim.z splits k; slice z writes its partial to C + z * M * N.
+// ---------------------------------------------------------------------------
+template <typename T>
+struct GemmArgs {
+    const T* A;
+    const T* B;
+    T* C;
+    const T* bias;       // added to rows < bias_rows (the primal stream), may be null
+    long long sam, sak;  // strides of A(m,k)
+    long long sbk, sbn;  // strides of B(k,n)
+    int M, N, K;
+    int ldc;
+    int bias_rows;
+    int k_chunk;         // k range per grid.z slice
+};
+
+constexpr int GEMM_BM = 64;
+constexpr int GEMM_BN = 64;
+constexpr int GEMM_BK = 16;
+
+template <typename T, bool A_KFAST, bool B_NFAST>
+__global__ void __launch_bounds__(256) gemm_kernel(GemmArgs<T> g) {
+    __shared__ T As[GEMM_BK][GEMM_BM + 4];
+    __shared__ T Bs[GEMM_BK][GEMM_BN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * GEMM_BM, n0 = blockIdx.x * GEMM_BN;
+    const int k_begin = blockIdx.z * g.k_chunk;
+    const int k_end = min(g.K, k_begin + g.k_chunk);
+    T acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = T(0);
+
+    for (int kt = k_begin; kt < k_end; kt += GEMM_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * 256;
+            int m, k;
+            if (A_KFAST) {
+                k = idx % GEMM_BK;
+                m = idx / GEMM_BK;
+            } else {
+                m = idx % GEMM_BM;
+                k = idx / GEMM_BM;
+            }
+            const int gm = m0 + m, gk = kt + k;
+            As[k][m] = (gm < g.M && gk < k_end) ? g.A[gm * g.sam + gk * g.sak] : T(0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = tid + i * 256;
+            int n, k;
+            if (B_NFAST) {
+                n = idx % GEMM_BN;
+                k = idx / GEMM_BN;
+            } else {
+                k = idx % GEMM_BK;
+                n = idx / GEMM_BK;
+            }
+            const int gn = n0 + n, gk = kt + k;
+            Bs[k][n] = (gn < g.N && gk < k_end) ? g.B[gk * g.sbk + gn * g.sbn] : T(0);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GEMM_BK; ++k) {
+            T a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Bs[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += a[i] * b[j];
+        }
+        __syncthreads();
+    }
+    T* C = g.C + (long long)blockIdx.z * g.M * g.ldc;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gm = m0 + ty * 4 + i;
+        if (gm >= g.M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= g.N) continue;
+            T v = acc[i][j];
+            if (g.bias != nullptr && gm < g.bias_rows) v += g.bias[gn];
+            C[(long long)gm * g.ldc + gn] = v;
+        }
+    }
+}
+
+// Column sums of the first `rows` rows of G[rows][N] (bias gradients), split
+// over rows: slice z writes partial[z][n].
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ G, T* __restrict__ partial, int rows,
+                                                     int N, int row_chunk) {
+    __shared__ T red[8][33];
+    const int lane = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int n = blockIdx.x * 32 + lane;
+    const int r0 = blockIdx.y * row_chunk;
+    const int r1 = min(rows, r0 + row_chunk);
+    T s = T(0);
+    if (n < N)
+        for (int r = r0 + ty; r < r1; r += 8) s += G[(long long)r * N + n];
+    red[ty][lane] = s;
+    __syncthreads();
+    if (ty == 0 && n < N) {
+        T total = red[0][lane];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) total += red[i][lane];
+        partial[(long long)blockIdx.y * N + n] = total;
+    }
+}
+
+// acc[i] += sum_z partial[z][i], z ascending, in double: the fixed-order
+// second pass that keeps gradients bit-reproducible (the reference sums long
+// axes in double as well, cuda.rs:8202-8247).
+template <typename T>
+__global__ void accumulate_partials_kernel(const T* __restrict__ partial, double* __restrict__ acc, int count,
+                                           int slices) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    double s = 0.0;
+    for (int z = 0; z < slices; ++z) s += (double)partial[(long long)z * count + i];
+    acc[i] += s;
+}
+
+// ---------------------------------------------------------------------------
+// Input streams of the first layer from the point table:
+//   stream 0 = the coordinates, first-order stream of direction j = v_j,
+//   every higher-order stream = 0.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void seed_input_kernel(const T* __restrict__ table, int table_cols, long long point0, int C, int d0,
+                                  JetSpec spec, const T* __restrict__ dirs, T* __restrict__ H0) {
+    const long long total = (long long)spec.S * C * d0;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        const int k = (int)(e % d0);
+        const long long r = e / d0;
+        const int c = (int)(r % C);
+        const int s = (int)(r / C);
+        T v = T(0);
+        if (s == 0) {
+            v = table[(point0 + c) * table_cols + k];
+        } else {
+            for (int j = 0; j < spec.ndirs; ++j)
+                if (s == spec.base[j]) v = dirs[j * d0 + k];
+        }
+        H0[e] = v;
+    }
+}
+
+// H = tanh-jet(Z), all streams, one thread per (point, unit).
+template <typename T>
+__global__ void jet_forward_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane, JetSpec spec) {
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < plane;
+         e += (long long)gridDim.x * blockDim.x) {
+        const T t = qb_tanh<T>(Z[e]);
+        H[e] = t;
+        const TanhD<T> d(t);
+        for (int j = 0; j < spec.ndirs; ++j) {
+            const long long off = (long long)spec.base[j] * plane + e;
+            T z[MAX_ORDER], h[MAX_ORDER];
+            const int K = spec.order[j];
+#pragma unroll
+            for (int m = 0; m < MAX_ORDER; ++m) z[m] = (m < K) ? Z[off + m * plane] : T(0);
+            switch (K) {
+                case 1: jet_compose<T, 1>(d, z, h); break;
+                case 2: jet_compose<T, 2>(d, z, h); break;
+                case 3: jet_compose<T, 3>(d, z, h); break;
+                default: jet_compose<T, 4>(d, z, h); break;
+            }
+#pragma unroll
+            for (int m = 0; m < MAX_ORDER; ++m)
+                if (m < K) H[off + m * plane] = h[m];
+        }
+    }
+}
+
+// In place: G (cotangents of H) becomes the cotangents of Z.
+template <typename T>
+__global__ void jet_backward_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal, T* __restrict__ G,
+                                    long long plane, JetSpec spec) {
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < plane;
+         e += (long long)gridDim.x * blockDim.x) {
+        const T t = Hprimal[e];
+        const TanhD<T> d(t);
+        T z0bar = d.t1 * G[e];
+        for (int j = 0; j < spec.ndirs; ++j) {
+            const long long off = (long long)spec.base[j] * plane + e;
+            T z[MAX_ORDER], g[MAX_ORDER], gz[MAX_ORDER];
+            const int K = spec.order[j];
+#pragma unroll
+            for (int m = 0; m < MAX_ORDER; ++m) {
+                z[m] = (m < K) ? Z[off + m * plane] : T(0);
+                g[m] = (m < K) ? G[off + m * plane] : T(0);
+            }
+            switch (K) {
+                case 1: z0bar += jet_compose_transposed<T, 1>(d, z, g, gz); break;
+                case 2: z0bar += jet_compose_transposed<T, 2>(d, z, g, gz); break;
+                case 3: z0bar += jet_compose_transposed<T, 3>(d, z, g, gz); break;
+                default: z0bar += jet_compose_transposed<T, 4>(d, z, g, gz); break;
+            }
+#pragma unroll
+            for (int m = 0; m < MAX_ORDER; ++m)
+                if (m < K) G[off + m * plane] = gz[m];
+        }
+        G[e] = z0bar;
+    }
+}
+
+// Last (linear, width -> 1) layer: U[row] = H[row][:] . w (+ b on the primal
+// rows); one warp per row, fixed shuffle tree.
+template <typename T>
+__global__ void head_forward_kernel(const T* __restrict__ H, const T* __restrict__ w, const T* __restrict__ b,
+                                    T* __restrict__ U, long long rows, int d, int primal_rows) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long r = warp; r < rows; r += nwarps) {
+        T s = T(0);
+        for (int k = lane; k < d; k += 32) s += H[r * d + k] * w[k];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) U[r] = s + ((b != nullptr && r < primal_rows) ? b[0] : T(0));
+    }
+}
+
+// Cotangent of the last hidden layer: G[row][k] = Uhat[row] * w[k].
+template <typename T>
+__global__ void head_backward_kernel(const T* __restrict__ Uhat, const T* __restrict__ w, T* __restrict__ G,
+                                     long long rows, int d) {
+    const long long total = rows * d;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total;
+         e += (long long)gridDim.x * blockDim.x) {
+        G[e] = Uhat[e / d] * w[e % d];
+    }
+}
+
+}  // namespace qb

@@ -1,0 +1,873 @@
+// Plan executor and optimizer state (see plan.h).
+#include "plan.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+#include "layer_kernels.cuh"
+#include "point_kernels.cuh"
+
+namespace qb {
+
+static const char* kCotangentName = "__quabla_loss_cotangent";
+
+qb200_status validate_opt_config(const qb200_opt_config* c) {
+    // Ranges of DeviceOptimizerConfig::validate
+    // (crates/quabla-core/src/tensor_ir/device_optimizer.rs:65-95).
+    if (c == nullptr) return fail(QB200_INVALID, "optimizer config is null");
+    if (c->rule != QB200_SGD && c->rule != QB200_ADAM) return fail(QB200_INVALID, "unknown optimizer rule %d", c->rule);
+    if (!(std::isfinite(c->learning_rate) && c->learning_rate >= 0.0))
+        return fail(QB200_INVALID, "device optimizer learning_rate must be finite and nonnegative");
+    if (c->has_clip && !(std::isfinite(c->clip_norm) && c->clip_norm > 0.0))
+        return fail(QB200_INVALID, "device optimizer clip_norm must be positive and finite");
+    if (c->rule == QB200_ADAM) {
+        if (!(c->beta1 >= 0.0 && c->beta1 < 1.0 && c->beta2 >= 0.0 && c->beta2 < 1.0))
+            return fail(QB200_INVALID, "device Adam beta1 and beta2 must be in [0, 1)");
+        if (!(std::isfinite(c->epsilon) && c->epsilon > 0.0))
+            return fail(QB200_INVALID, "device Adam epsilon must be positive and finite");
+        if (!(std::isfinite(c->weight_decay) && c->weight_decay >= 0.0))
+            return fail(QB200_INVALID, "device AdamW weight_decay must be finite and nonnegative");
+    }
+    return QB200_OK;
+}
+
+qb200_status validate_desc(const qb200_desc& d) {
+    if (d.dtype != QB200_F32 && d.dtype != QB200_F64) return fail(QB200_INVALID, "unknown dtype %d", d.dtype);
+    const int L = (int)d.sizes.size() - 1;
+    if (L < 1) return fail(QB200_INVALID, "the network needs at least one layer");
+    for (int s : d.sizes)
+        if (s <= 0) return fail(QB200_INVALID, "layer sizes must be positive");
+    if (d.sizes.back() != 1)
+        return fail(QB200_UNSUPPORTED, "the network output must be one scalar per point, got width %d", d.sizes.back());
+    if (d.sizes[0] > MAX_COLS) return fail(QB200_UNSUPPORTED, "network input width %d exceeds %d", d.sizes[0], MAX_COLS);
+    std::vector<int> weights(L, 0), biases(L, 0);
+    for (size_t i = 0; i < d.params.size(); ++i) {
+        const auto& p = d.params[i];
+        if (p.layer < 0 || p.layer >= L) return fail(QB200_INVALID, "parameter '%s' names layer %d of %d", p.name.c_str(), p.layer, L);
+        if (p.kind != QB200_WEIGHT && p.kind != QB200_BIAS) return fail(QB200_INVALID, "parameter '%s' has unknown kind", p.name.c_str());
+        (p.kind == QB200_WEIGHT ? weights : biases)[p.layer]++;
+        for (size_t j = 0; j < i; ++j)
+            if (d.params[j].name == p.name) return fail(QB200_INVALID, "duplicate parameter name '%s'", p.name.c_str());
+        for (const auto& in : d.inputs)
+            if (in.name == p.name) return fail(QB200_INVALID, "name '%s' is both a parameter and an input", p.name.c_str());
+        if (p.name == kCotangentName) return fail(QB200_INVALID, "'%s' is reserved", kCotangentName);
+    }
+    for (int l = 0; l < L; ++l) {
+        if (weights[l] != 1) return fail(QB200_INVALID, "layer %d needs exactly one weight parameter, got %d", l, weights[l]);
+        if (biases[l] > 1) return fail(QB200_INVALID, "layer %d has %d bias parameters", l, biases[l]);
+    }
+    for (size_t i = 0; i < d.inputs.size(); ++i) {
+        const auto& in = d.inputs[i];
+        if (in.rows <= 0 || in.cols <= 0) return fail(QB200_INVALID, "input '%s' has an empty shape", in.name.c_str());
+        for (size_t j = 0; j < i; ++j)
+            if (d.inputs[j].name == in.name) return fail(QB200_INVALID, "duplicate input name '%s'", in.name.c_str());
+    }
+    if (d.sets.empty()) return fail(QB200_INVALID, "the plan has no point set");
+    if ((int)d.sets.size() > MAX_SETS) return fail(QB200_UNSUPPORTED, "more than %d point sets", MAX_SETS);
+    const int d0 = d.sizes[0];
+    for (size_t si = 0; si < d.sets.size(); ++si) {
+        const auto& s = d.sets[si];
+        if (s.n <= 0 || s.n > (int64_t)1 << 31) return fail(QB200_INVALID, "set %zu: point count out of range", si);
+        if (!std::isfinite(s.weight)) return fail(QB200_INVALID, "set %zu: weight must be finite", si);
+        if ((int)s.cols.size() < d0) return fail(QB200_INVALID, "set %zu: %zu columns for %d network inputs", si, s.cols.size(), d0);
+        if ((int)s.cols.size() > MAX_COLS) return fail(QB200_UNSUPPORTED, "set %zu: more than %d columns", si, MAX_COLS);
+        for (const auto& c : s.cols) {
+            if (c.first < 0 || c.first >= (int)d.inputs.size()) return fail(QB200_INVALID, "set %zu: column names input %d", si, c.first);
+            const auto& in = d.inputs[c.first];
+            if (in.rows != s.n) return fail(QB200_INVALID, "set %zu: input '%s' has %lld rows for %lld points", si, in.name.c_str(), (long long)in.rows, (long long)s.n);
+            if (c.second < 0 || c.second >= in.cols) return fail(QB200_INVALID, "set %zu: column %d of input '%s'", si, c.second, in.name.c_str());
+        }
+        if ((int)s.dirs.size() > MAX_DIRS) return fail(QB200_UNSUPPORTED, "set %zu: more than %d derivative directions", si, MAX_DIRS);
+        for (size_t j = 0; j < s.dirs.size(); ++j) {
+            if ((int)s.dirs[j].size() != d0) return fail(QB200_INVALID, "set %zu: direction %zu has the wrong length", si, j);
+            if (s.orders[j] < 1 || s.orders[j] > MAX_ORDER) return fail(QB200_UNSUPPORTED, "set %zu: derivative order %d (1..%d supported)", si, s.orders[j], MAX_ORDER);
+        }
+        const int S = s.streams();
+        if (S > MAX_STREAMS) return fail(QB200_UNSUPPORTED, "set %zu: %d streams exceed %d", si, S, MAX_STREAMS);
+        if (!s.has_program) return fail(QB200_INVALID, "set %zu has no residual program", si);
+        const int n_instr = (int)s.code.size() / 4;
+        if (n_instr < 1 || n_instr > MAX_INSTR) return fail(QB200_UNSUPPORTED, "set %zu: program of %d instructions (1..%d)", si, n_instr, MAX_INSTR);
+        if (s.n_regs < 1 || s.n_regs > MAX_REGS) return fail(QB200_UNSUPPORTED, "set %zu: %d registers (1..%d)", si, s.n_regs, MAX_REGS);
+        std::vector<char> written(s.n_regs, 0);
+        for (int pc = 0; pc < n_instr; ++pc) {
+            const int op = s.code[4 * pc], dst = s.code[4 * pc + 1], a = s.code[4 * pc + 2], b = s.code[4 * pc + 3];
+            if (dst < 0 || dst >= s.n_regs) return fail(QB200_INVALID, "set %zu: instruction %d writes register %d", si, pc, dst);
+            auto reg_ok = [&](int r) { return r >= 0 && r < s.n_regs && written[r]; };
+            bool ok = true;
+            switch (op) {
+                case OP_CONST: ok = a >= 0 && a < (int)s.consts.size(); break;
+                case OP_COL: ok = a >= 0 && a < (int)s.cols.size(); break;
+                case OP_JET: ok = a >= 0 && a < S; break;
+                case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV: ok = reg_ok(a) && reg_ok(b); break;
+                case OP_NEG: case OP_SIN: case OP_COS: case OP_EXP: case OP_TANH: case OP_SQRT: case OP_LOG:
+                case OP_POWI: ok = reg_ok(a); break;
+                default: return fail(QB200_UNSUPPORTED, "set %zu: instruction %d has unknown opcode %d", si, pc, op);
+            }
+            if (!ok) return fail(QB200_INVALID, "set %zu: instruction %d has an operand out of range or read before it is written", si, pc);
+            written[dst] = 1;
+        }
+        if (s.value_reg < 0 || s.value_reg >= s.n_regs || !written[s.value_reg]) return fail(QB200_INVALID, "set %zu: value register is never written", si);
+        if ((int)s.grad_regs.size() != S) return fail(QB200_INVALID, "set %zu: %zu gradient registers for %d streams", si, s.grad_regs.size(), S);
+        for (int r : s.grad_regs)
+            if (r < -1 || r >= s.n_regs || (r >= 0 && !written[r])) return fail(QB200_INVALID, "set %zu: a gradient register is never written", si);
+    }
+    return QB200_OK;
+}
+
+namespace {
+
+template <typename T> struct DTypeOf;
+template <> struct DTypeOf<float> { static constexpr int value = QB200_F32; static constexpr ncclDataType_t nccl = ncclFloat32; };
+template <> struct DTypeOf<double> { static constexpr int value = QB200_F64; static constexpr ncclDataType_t nccl = ncclFloat64; };
+
+inline int grid_for(long long total, int block, int cap = 148 * 16) {
+    long long g = (total + block - 1) / block;
+    return (int)std::max<long long>(1, std::min<long long>(g, cap));
+}
+
+template <typename T>
+class Plan final : public qb200_plan {
+  public:
+    Plan(const qb200_desc& d, int device) : desc_(d), device_(device) {}
+    ~Plan() override { release(); }
+
+    qb200_status init();
+
+    qb200_status bind(const char* name, const void* host, size_t nbytes) override;
+    qb200_status execute_local() override;
+    qb200_status all_reduce() override;
+    qb200_status read_output(int index, void* host, size_t nbytes) override;
+    qb200_status optimizer_step(const qb200_opt_config* config) override;
+    qb200_status loss(void* host_scalar) override;
+    qb200_status read_input(const char* name, void* host, size_t nbytes) override;
+    qb200_status read_moments(int which, void* host, size_t nbytes) override;
+    qb200_status write_moments(int which, const void* host, size_t nbytes, int64_t step_count) override;
+    qb200_status query(int key, int64_t* out) override;
+    qb200_status synchronize() override;
+    qb200_status attach_comm(const void* id, int rank, int world, int reduction) override;
+    qb200_status detach_comm() override;
+
+    void* flat_device_ptr() override { return d_flat_; }
+    size_t flat_count() const override { return 1 + n_params_; }
+    cudaStream_t stream() const override { return stream_; }
+    void set_dp_scale(double inv_world) override { dp_scale_ = inv_world; }
+    int device() const override { return device_; }
+    int dtype() const override { return DTypeOf<T>::value; }
+    int64_t input_shard_bytes(const char* name) const override;
+
+  private:
+    struct Leaf {
+        size_t offset, count;
+        bool bound = false;
+    };
+    struct InputState {
+        T* dev = nullptr;
+        bool bound = false;
+    };
+    struct SetState {
+        JetSpec spec;
+        int ncols = 0;
+        T* table = nullptr;
+        T* dirs = nullptr;
+        int4* code = nullptr;
+        T* consts = nullptr;
+        ProgramRef prog;
+        int chunk = 0;             // points per chunk
+        int partial_offset = 0;    // first loss partial of this set
+        int partial_count = 0;
+        bool table_dirty = true;
+    };
+
+    template <typename P> qb200_status dev_alloc(P** ptr, size_t count) {
+        void* raw = nullptr;
+        QB_CUDA(cudaMalloc(&raw, std::max<size_t>(count, 1) * sizeof(P)));
+        *ptr = static_cast<P*>(raw);
+        buffers_.push_back(raw);
+        return QB200_OK;
+    }
+    void release();
+    qb200_status use_device() const {
+        QB_CUDA(cudaSetDevice(device_));
+        return QB200_OK;
+    }
+    qb200_status check_bound() const;
+    qb200_status refresh_tables();
+    qb200_status run(bool forward_only);
+    qb200_status run_chunk(int si, long long point0, int C, int partial_slot, bool forward_only);
+    qb200_status launched(const char* what) {
+        ++launches_;
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of %s failed: %s", what, cudaGetErrorString(e));
+        return QB200_OK;
+    }
+    const T* weight(int layer) const { return d_params_ + leaves_[w_leaf_[layer]].offset; }
+    const T* bias(int layer) const { return b_leaf_[layer] >= 0 ? d_params_ + leaves_[b_leaf_[layer]].offset : nullptr; }
+
+    qb200_desc desc_;
+    int device_;
+    cudaStream_t stream_ = nullptr;
+    std::vector<void*> buffers_;
+    int L_ = 0;  // layers (hidden + head)
+    size_t n_params_ = 0;
+    std::vector<Leaf> leaves_;
+    std::vector<int> w_leaf_, b_leaf_;
+    std::vector<InputState> inputs_;
+    std::vector<SetState> sets_;
+    T* d_params_ = nullptr;
+    T* d_flat_ = nullptr;      // [loss, gradients...]
+    double* d_acc_ = nullptr;  // gradient accumulators
+    T* d_m_ = nullptr;
+    T* d_v_ = nullptr;
+    T* d_ct_ = nullptr;
+    T* d_loss_only_ = nullptr;
+    double* d_partials_ = nullptr;
+    double* d_clip_ = nullptr;
+    int total_partials_ = 0;
+    // chunk scratch
+    std::vector<T*> H_, Z_;
+    T* G_[2] = {nullptr, nullptr};
+    T* U_ = nullptr;
+    T* Uhat_ = nullptr;
+    T* wpartial_ = nullptr;
+    size_t scratch_bytes_ = 0;
+    int64_t launches_ = 0;
+    int64_t steps_ = 0;
+    bool executed_ = false;
+    bool moments_ready_ = false;
+    double dp_scale_ = 1.0;
+    ncclComm_t comm_ = nullptr;
+    int world_ = 1;
+};
+
+constexpr int K_CHUNK_ROWS = 4096;  // rows summed in the plan dtype before the double reduction
+
+template <typename T>
+void Plan<T>::release() {
+    cudaSetDevice(device_);
+    if (comm_ != nullptr) {
+        const NcclApi* api = nccl_api();
+        if (api != nullptr) api->CommDestroy(comm_);
+        comm_ = nullptr;
+    }
+    if (stream_ != nullptr) cudaStreamSynchronize(stream_);
+    for (void* p : buffers_) cudaFree(p);
+    buffers_.clear();
+    if (stream_ != nullptr) cudaStreamDestroy(stream_);
+    stream_ = nullptr;
+}
+
+template <typename T>
+qb200_status Plan<T>::init() {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+        return fail(QB200_CUDA_ERROR, "no CUDA device is available: the qb200 backend has no CPU fallback");
+    if (device_ < 0 || device_ >= count) return fail(QB200_INVALID, "device ordinal %d of %d", device_, count);
+    QB_TRY(use_device());
+    QB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+
+    L_ = (int)desc_.sizes.size() - 1;
+    w_leaf_.assign(L_, -1);
+    b_leaf_.assign(L_, -1);
+    size_t offset = 0;
+    for (size_t i = 0; i < desc_.params.size(); ++i) {
+        const auto& p = desc_.params[i];
+        Leaf leaf;
+        leaf.offset = offset;
+        leaf.count = p.kind == QB200_WEIGHT ? (size_t)desc_.sizes[p.layer] * desc_.sizes[p.layer + 1] : (size_t)desc_.sizes[p.layer + 1];
+        offset += leaf.count;
+        leaves_.push_back(leaf);
+        (p.kind == QB200_WEIGHT ? w_leaf_ : b_leaf_)[p.layer] = (int)i;
+    }
+    n_params_ = offset;
+    QB_TRY(dev_alloc(&d_params_, n_params_));
+    QB_TRY(dev_alloc(&d_flat_, 1 + n_params_));
+    QB_TRY(dev_alloc(&d_acc_, n_params_));
+    QB_TRY(dev_alloc(&d_ct_, 1));
+    QB_TRY(dev_alloc(&d_loss_only_, 1));
+    QB_TRY(dev_alloc(&d_clip_, 3));
+    QB_CUDA(cudaMemsetAsync(d_flat_, 0, (1 + n_params_) * sizeof(T), stream_));
+    QB_CUDA(cudaMemsetAsync(d_clip_, 0, 3 * sizeof(double), stream_));
+    const T one = T(1);
+    QB_CUDA(cudaMemcpyAsync(d_ct_, &one, sizeof(T), cudaMemcpyHostToDevice, stream_));
+    QB_CUDA(cudaStreamSynchronize(stream_));
+
+    inputs_.resize(desc_.inputs.size());
+    for (size_t i = 0; i < desc_.inputs.size(); ++i)
+        QB_TRY(dev_alloc(&inputs_[i].dev, (size_t)(desc_.inputs[i].rows * desc_.inputs[i].cols)));
+
+    // Saved-jet scratch: sized per set from a byte budget, then the maximum over sets.
+    const int d0 = desc_.sizes[0];
+    int dmax = 0;
+    size_t sum_h = 0, sum_z = 0, wmax = 0;
+    for (int l = 0; l < L_; ++l) {
+        sum_h += desc_.sizes[l];
+        if (l >= 1) {
+            sum_z += desc_.sizes[l];
+            dmax = std::max(dmax, desc_.sizes[l]);
+        }
+        wmax = std::max(wmax, (size_t)desc_.sizes[l] * desc_.sizes[l + 1]);
+    }
+    dmax = std::max(dmax, d0);
+    size_t budget = (size_t)6 << 30;
+    if (const char* env = getenv("QB200_SCRATCH_BYTES")) {
+        const long long v = atoll(env);
+        if (v > 0) budget = (size_t)v;
+    }
+    int chunk_cap = 1 << 20;
+    if (const char* env = getenv("QB200_CHUNK_POINTS")) {
+        const long long v = atoll(env);
+        if (v > 0) chunk_cap = (int)std::min<long long>(v, 1 << 24);
+    }
+    size_t max_rows = 0, max_chunk = 0;
+    std::vector<size_t> h_elems(L_, 0), z_elems(L_, 0);
+    size_t g_elems = 0;
+    sets_.resize(desc_.sets.size());
+    for (size_t si = 0; si < desc_.sets.size(); ++si) {
+        const auto& s = desc_.sets[si];
+        SetState& st = sets_[si];
+        st.spec.S = s.streams();
+        st.spec.ndirs = (int)s.dirs.size();
+        int base = 1;
+        for (int j = 0; j < MAX_DIRS; ++j) {
+            st.spec.order[j] = j < st.spec.ndirs ? s.orders[j] : 0;
+            st.spec.base[j] = base;
+            base += st.spec.order[j];
+        }
+        st.ncols = (int)s.cols.size();
+        const size_t S = st.spec.S;
+        const size_t per_point = S * (sum_h + sum_z + 2 * (size_t)dmax + 2) * sizeof(T);
+        long long chunk = (long long)std::min<size_t>(budget / per_point, (size_t)chunk_cap);
+        // Bound the split-K slices of a weight gradient.
+        chunk = std::min<long long>(chunk, (long long)K_CHUNK_ROWS * 256 / (long long)S);
+        if (chunk >= s.n) {
+            chunk = s.n;
+        } else {
+            chunk = std::max<long long>(256, chunk / 256 * 256);
+        }
+        st.chunk = (int)chunk;
+        max_chunk = std::max(max_chunk, (size_t)chunk);
+        max_rows = std::max(max_rows, S * (size_t)chunk);
+        for (int l = 0; l < L_; ++l) {
+            h_elems[l] = std::max(h_elems[l], S * (size_t)chunk * desc_.sizes[l]);
+            if (l >= 1) z_elems[l] = std::max(z_elems[l], S * (size_t)chunk * desc_.sizes[l]);
+        }
+        g_elems = std::max(g_elems, S * (size_t)chunk * dmax);
+
+        QB_TRY(dev_alloc(&st.table, (size_t)s.n * st.ncols));
+        std::vector<T> dirs(std::max<size_t>(1, s.dirs.size() * d0));
+        for (size_t j = 0; j < s.dirs.size(); ++j)
+            for (int k = 0; k < d0; ++k) dirs[j * d0 + k] = (T)s.dirs[j][k];
+        QB_TRY(dev_alloc(&st.dirs, dirs.size()));
+        QB_CUDA(cudaMemcpy(st.dirs, dirs.data(), dirs.size() * sizeof(T), cudaMemcpyHostToDevice));
+        const int n_instr = (int)s.code.size() / 4;
+        QB_TRY(dev_alloc(&st.code, (size_t)n_instr));
+        QB_CUDA(cudaMemcpy(st.code, s.code.data(), (size_t)n_instr * sizeof(int4), cudaMemcpyHostToDevice));
+        // Constants are rounded once to the plan dtype, as plan compilation folds a
+        // weak Python scalar into the strong dtype (tensor_ir.rs:6995-7004, 6278-6283).
+        std::vector<T> consts(std::max<size_t>(1, s.consts.size()));
+        for (size_t i = 0; i < s.consts.size(); ++i) consts[i] = (T)s.consts[i];
+        QB_TRY(dev_alloc(&st.consts, consts.size()));
+        QB_CUDA(cudaMemcpy(st.consts, consts.data(), consts.size() * sizeof(T), cudaMemcpyHostToDevice));
+        st.prog.code = st.code;
+        st.prog.consts = st.consts;
+        st.prog.n_instr = n_instr;
+        st.prog.value_reg = s.value_reg;
+        for (int k = 0; k < MAX_STREAMS; ++k) st.prog.grad_regs[k] = k < (int)s.grad_regs.size() ? s.grad_regs[k] : -1;
+        const int chunks = (int)((s.n + chunk - 1) / chunk);
+        st.partial_offset = total_partials_;
+        st.partial_count = chunks * (int)((chunk + 255) / 256);
+        total_partials_ += st.partial_count;
+    }
+    QB_TRY(dev_alloc(&d_partials_, (size_t)total_partials_));
+    H_.assign(L_, nullptr);
+    Z_.assign(L_, nullptr);
+    scratch_bytes_ = 0;
+    for (int l = 0; l < L_; ++l) {
+        QB_TRY(dev_alloc(&H_[l], h_elems[l]));
+        scratch_bytes_ += h_elems[l] * sizeof(T);
+        if (l >= 1) {
+            QB_TRY(dev_alloc(&Z_[l], z_elems[l]));
+            scratch_bytes_ += z_elems[l] * sizeof(T);
+        }
+    }
+    QB_TRY(dev_alloc(&G_[0], g_elems));
+    QB_TRY(dev_alloc(&G_[1], g_elems));
+    QB_TRY(dev_alloc(&U_, max_rows));
+    QB_TRY(dev_alloc(&Uhat_, max_rows));
+    const size_t slices = (max_rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS;
+    QB_TRY(dev_alloc(&wpartial_, slices * std::max<size_t>(wmax, (size_t)dmax)));
+    scratch_bytes_ += (2 * g_elems + 2 * max_rows + slices * std::max<size_t>(wmax, (size_t)dmax)) * sizeof(T);
+    return QB200_OK;
+}
+
+template <typename T>
+int64_t Plan<T>::input_shard_bytes(const char* name) const {
+    for (size_t i = 0; i < desc_.inputs.size(); ++i)
+        if (desc_.inputs[i].name == name) return (int64_t)(desc_.inputs[i].rows * desc_.inputs[i].cols * sizeof(T));
+    for (size_t i = 0; i < desc_.params.size(); ++i)
+        if (desc_.params[i].name == name) return (int64_t)(leaves_[i].count * sizeof(T));
+    if (kCotangentName == std::string(name)) return (int64_t)sizeof(T);
+    return -1;
+}
+
+template <typename T>
+qb200_status Plan<T>::bind(const char* name, const void* host, size_t nbytes) {
+    if (name == nullptr || host == nullptr) return fail(QB200_INVALID, "bind needs a name and a host buffer");
+    QB_TRY(use_device());
+    const std::string key(name);
+    if (key == kCotangentName) {
+        if (nbytes != sizeof(T)) return fail(QB200_INVALID, "input '%s' is one scalar of %zu bytes, got %zu", name, sizeof(T), nbytes);
+        QB_CUDA(cudaMemcpyAsync(d_ct_, host, nbytes, cudaMemcpyHostToDevice, stream_));
+        QB_CUDA(cudaStreamSynchronize(stream_));
+        return QB200_OK;
+    }
+    for (size_t i = 0; i < desc_.params.size(); ++i) {
+        if (desc_.params[i].name != key) continue;
+        const size_t want = leaves_[i].count * sizeof(T);
+        if (nbytes != want) return fail(QB200_INVALID, "parameter '%s' needs %zu bytes, got %zu", name, want, nbytes);
+        QB_CUDA(cudaMemcpyAsync(d_params_ + leaves_[i].offset, host, nbytes, cudaMemcpyHostToDevice, stream_));
+        QB_CUDA(cudaStreamSynchronize(stream_));
+        leaves_[i].bound = true;
+        return QB200_OK;
+    }
+    for (size_t i = 0; i < desc_.inputs.size(); ++i) {
+        if (desc_.inputs[i].name != key) continue;
+        const size_t want = (size_t)(desc_.inputs[i].rows * desc_.inputs[i].cols) * sizeof(T);
+        if (nbytes != want) return fail(QB200_INVALID, "input '%s' needs %zu bytes, got %zu", name, want, nbytes);
+        QB_CUDA(cudaMemcpyAsync(inputs_[i].dev, host, nbytes, cudaMemcpyHostToDevice, stream_));
+        // The host buffer may be pageable and reused by the caller right away.
+        QB_CUDA(cudaStreamSynchronize(stream_));
+        inputs_[i].bound = true;
+        for (size_t si = 0; si < desc_.sets.size(); ++si)
+            for (const auto& c : desc_.sets[si].cols)
+                if (c.first == (int)i) sets_[si].table_dirty = true;
+        return QB200_OK;
+    }
+    return fail(QB200_INVALID, "the plan has no input named '%s'", name);
+}
+
+template <typename T>
+qb200_status Plan<T>::check_bound() const {
+    for (size_t i = 0; i < desc_.params.size(); ++i)
+        if (!leaves_[i].bound) return fail(QB200_NOT_BOUND, "parameter '%s' was never bound", desc_.params[i].name.c_str());
+    for (size_t i = 0; i < desc_.inputs.size(); ++i)
+        if (!inputs_[i].bound) return fail(QB200_NOT_BOUND, "input '%s' was never bound", desc_.inputs[i].name.c_str());
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::refresh_tables() {
+    for (size_t si = 0; si < sets_.size(); ++si) {
+        SetState& st = sets_[si];
+        if (!st.table_dirty) continue;
+        GatherArgs a;
+        a.ncols = st.ncols;
+        for (int c = 0; c < st.ncols; ++c) {
+            const auto& col = desc_.sets[si].cols[c];
+            a.src[c] = inputs_[col.first].dev;
+            a.stride[c] = (int)desc_.inputs[col.first].cols;
+            a.column[c] = col.second;
+        }
+        const long long n = desc_.sets[si].n;
+        gather_table_kernel<T><<<grid_for(n * st.ncols, 256), 256, 0, stream_>>>(a, st.table, n);
+        QB_TRY(launched("gather_table_kernel"));
+        st.table_dirty = false;
+    }
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slot, bool forward_only) {
+    SetState& st = sets_[si];
+    const JetSpec& spec = st.spec;
+    const int S = spec.S;
+    const long long rows = (long long)S * C;
+    const std::vector<int>& sz = desc_.sizes;
+    const int head = L_ - 1;  // index of the linear output layer
+
+    seed_input_kernel<T><<<grid_for(rows * sz[0], 256), 256, 0, stream_>>>(st.table, st.ncols, point0, C, sz[0], spec,
+                                                                           st.dirs, H_[0]);
+    QB_TRY(launched("seed_input_kernel"));
+    for (int l = 1; l <= head; ++l) {
+        // Z_l = H_{l-1} W_{l-1} (+ bias on the primal rows), H_l = tanh-jet(Z_l).
+        GemmArgs<T> g;
+        g.A = H_[l - 1];
+        g.B = weight(l - 1);
+        g.C = Z_[l];
+        g.bias = bias(l - 1);
+        g.sam = sz[l - 1];
+        g.sak = 1;
+        g.sbk = sz[l];
+        g.sbn = 1;
+        g.M = (int)rows;
+        g.N = sz[l];
+        g.K = sz[l - 1];
+        g.ldc = sz[l];
+        g.bias_rows = C;
+        g.k_chunk = g.K;
+        dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
+        gemm_kernel<T, true, true><<<grid, 256, 0, stream_>>>(g);
+        QB_TRY(launched("gemm_kernel(forward)"));
+        const long long plane = (long long)C * sz[l];
+        jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec);
+        QB_TRY(launched("jet_forward_kernel"));
+    }
+    head_forward_kernel<T><<<grid_for(rows * 32, 256), 256, 0, stream_>>>(H_[head], weight(head), bias(head), U_, rows,
+                                                                          sz[head], C);
+    QB_TRY(launched("head_forward_kernel"));
+    const T w = (T)desc_.sets[si].weight;
+    residual_kernel<T><<<(C + 255) / 256, 256, 0, stream_>>>(st.table, st.ncols, point0, C, S, U_,
+                                                             forward_only ? nullptr : Uhat_, st.prog, d_ct_, w,
+                                                             (T)dp_scale_, d_partials_ + partial_slot);
+    QB_TRY(launched("residual_kernel"));
+    if (forward_only) return QB200_OK;
+
+    auto wgrad = [&](const T* Hprev, const T* Gz, int d_in, int d_out, int leaf) -> qb200_status {
+        GemmArgs<T> g;
+        g.A = Hprev;
+        g.B = Gz;
+        g.C = wpartial_;
+        g.bias = nullptr;
+        g.sam = 1;
+        g.sak = d_in;
+        g.sbk = d_out;
+        g.sbn = 1;
+        g.M = d_in;
+        g.N = d_out;
+        g.K = (int)rows;
+        g.ldc = d_out;
+        g.bias_rows = 0;
+        g.k_chunk = K_CHUNK_ROWS;
+        const int slices = (int)((rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS);
+        dim3 grid((d_out + GEMM_BN - 1) / GEMM_BN, (d_in + GEMM_BM - 1) / GEMM_BM, slices);
+        gemm_kernel<T, false, true><<<grid, 256, 0, stream_>>>(g);
+        QB_TRY(launched("gemm_kernel(wgrad)"));
+        const int count = d_in * d_out;
+        accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
+                                                                                count, slices);
+        return launched("accumulate_partials_kernel");
+    };
+    auto bgrad = [&](const T* Gz, int d_out, int leaf) -> qb200_status {
+        if (leaf < 0) return QB200_OK;
+        const int slices = (C + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS;
+        dim3 grid((d_out + 31) / 32, slices);
+        colsum_kernel<T><<<grid, 256, 0, stream_>>>(Gz, wpartial_, C, d_out, K_CHUNK_ROWS);
+        QB_TRY(launched("colsum_kernel"));
+        accumulate_partials_kernel<T><<<(d_out + 255) / 256, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
+                                                                                d_out, slices);
+        return launched("accumulate_partials_kernel");
+    };
+
+    // Head: dW = H^T Uhat, db = sum of the primal cotangents, G = Uhat (x) w.
+    QB_TRY(wgrad(H_[head], Uhat_, sz[head], 1, w_leaf_[head]));
+    QB_TRY(bgrad(Uhat_, 1, b_leaf_[head]));
+    int cur = 0;
+    head_backward_kernel<T><<<grid_for(rows * sz[head], 256), 256, 0, stream_>>>(Uhat_, weight(head), G_[cur], rows,
+                                                                                 sz[head]);
+    QB_TRY(launched("head_backward_kernel"));
+    for (int l = head; l >= 1; --l) {
+        const long long plane = (long long)C * sz[l];
+        jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec);
+        QB_TRY(launched("jet_backward_kernel"));
+        QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1]));
+        QB_TRY(bgrad(G_[cur], sz[l], b_leaf_[l - 1]));
+        if (l > 1) {
+            GemmArgs<T> g;
+            g.A = G_[cur];
+            g.B = weight(l - 1);
+            g.C = G_[cur ^ 1];
+            g.bias = nullptr;
+            g.sam = sz[l];
+            g.sak = 1;
+            g.sbk = 1;
+            g.sbn = sz[l];
+            g.M = (int)rows;
+            g.N = sz[l - 1];
+            g.K = sz[l];
+            g.ldc = sz[l - 1];
+            g.bias_rows = 0;
+            g.k_chunk = g.K;
+            dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
+            gemm_kernel<T, true, false><<<grid, 256, 0, stream_>>>(g);
+            QB_TRY(launched("gemm_kernel(dgrad)"));
+            cur ^= 1;
+        }
+    }
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::run(bool forward_only) {
+    QB_TRY(use_device());
+    QB_TRY(check_bound());
+    QB_TRY(refresh_tables());
+    if (!forward_only) QB_CUDA(cudaMemsetAsync(d_acc_, 0, n_params_ * sizeof(double), stream_));
+    LossArgs la;
+    la.n_sets = (int)sets_.size();
+    for (size_t si = 0; si < sets_.size(); ++si) {
+        SetState& st = sets_[si];
+        const long long n = desc_.sets[si].n;
+        int slot = st.partial_offset;
+        for (long long p0 = 0; p0 < n; p0 += st.chunk) {
+            const int C = (int)std::min<long long>(st.chunk, n - p0);
+            QB_TRY(run_chunk((int)si, p0, C, slot, forward_only));
+            slot += (C + 255) / 256;
+        }
+        la.offset[si] = st.partial_offset;
+        la.count[si] = slot - st.partial_offset;
+        la.weight[si] = desc_.sets[si].weight;
+    }
+    T* loss_out = forward_only ? d_loss_only_ : d_flat_;
+    loss_finalize_kernel<T><<<1, 256, 0, stream_>>>(d_partials_, la, forward_only ? T(1) : (T)dp_scale_, loss_out);
+    QB_TRY(launched("loss_finalize_kernel"));
+    if (!forward_only) {
+        finalize_gradients_kernel<T><<<((int)n_params_ + 255) / 256, 256, 0, stream_>>>(d_acc_, d_flat_ + 1, (int)n_params_);
+        QB_TRY(launched("finalize_gradients_kernel"));
+        executed_ = true;
+    }
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::execute_local() {
+    return run(false);
+}
+
+template <typename T>
+qb200_status Plan<T>::all_reduce() {
+    if (comm_ == nullptr) return QB200_OK;
+    const NcclApi* api = nccl_api();
+    if (api == nullptr) return QB200_NCCL_ERROR;
+    ncclResult_t r = api->AllReduce(d_flat_, d_flat_, 1 + n_params_, DTypeOf<T>::nccl, ncclSum, comm_, stream_);
+    if (r != ncclSuccess) {
+        // Failure contract: drop the communicator, the caller re-attaches
+        // (crates/quabla-core/src/tensor_ir/cuda.rs:132-145, 699-716).
+        api->CommAbort(comm_);
+        comm_ = nullptr;
+        dp_scale_ = 1.0;
+        return fail(QB200_NCCL_ERROR, "ncclAllReduce failed: %s; the communicator was aborted, attach a new one", api->GetErrorString(r));
+    }
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::read_output(int index, void* host, size_t nbytes) {
+    QB_TRY(use_device());
+    if (!executed_) return fail(QB200_INVALID, "read_output before execute");
+    if (index < 0 || index > (int)leaves_.size()) return fail(QB200_INVALID, "output index %d of %zu", index, leaves_.size() + 1);
+    const size_t offset = index == 0 ? 0 : 1 + leaves_[index - 1].offset;
+    const size_t count = index == 0 ? 1 : leaves_[index - 1].count;
+    if (nbytes != count * sizeof(T)) return fail(QB200_INVALID, "output %d has %zu bytes, got a buffer of %zu", index, count * sizeof(T), nbytes);
+    QB_CUDA(cudaMemcpyAsync(host, d_flat_ + offset, nbytes, cudaMemcpyDeviceToHost, stream_));
+    QB_CUDA(cudaStreamSynchronize(stream_));
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::optimizer_step(const qb200_opt_config* c) {
+    QB_TRY(validate_opt_config(c));  // before any device work (cuda_optimizer.rs:207-212)
+    QB_TRY(use_device());
+    if (!executed_) return fail(QB200_INVALID, "optimizer_step before execute: there are no gradients");
+    if (!moments_ready_ && c->rule == QB200_ADAM) {
+        QB_TRY(dev_alloc(&d_m_, n_params_));
+        QB_TRY(dev_alloc(&d_v_, n_params_));
+        QB_CUDA(cudaMemsetAsync(d_m_, 0, n_params_ * sizeof(T), stream_));
+        QB_CUDA(cudaMemsetAsync(d_v_, 0, n_params_ * sizeof(T), stream_));
+        moments_ready_ = true;
+    }
+    const double* clip = nullptr;
+    if (c->has_clip) {
+        global_norm_kernel<T><<<1, 1024, 0, stream_>>>(d_flat_ + 1, (long long)n_params_, c->clip_norm, d_clip_);
+        QB_TRY(launched("global_norm_kernel"));
+        clip = d_clip_;
+    }
+    ++steps_;
+    const int grid = grid_for((long long)n_params_, 256);
+    if (c->rule == QB200_SGD) {
+        sgd_kernel<T><<<grid, 256, 0, stream_>>>(d_params_, d_flat_ + 1, (T)c->learning_rate, clip, (long long)n_params_);
+        return launched("sgd_kernel");
+    }
+    // Coefficients in double, rounded once (AdamCoefficients::new(..).map(T::from_f64),
+    // device_optimizer.rs:97-101, 129-150; cuda_optimizer.rs:340-359).
+    AdamCoeffs<T> k;
+    k.learning_rate = (T)c->learning_rate;
+    k.beta1 = (T)c->beta1;
+    k.beta2 = (T)c->beta2;
+    k.one_minus_beta1 = (T)(1.0 - c->beta1);
+    k.one_minus_beta2 = (T)(1.0 - c->beta2);
+    k.epsilon = (T)c->epsilon;
+    k.correction1 = (T)(1.0 - std::pow(c->beta1, (double)steps_));
+    k.correction2 = (T)(1.0 - std::pow(c->beta2, (double)steps_));
+    k.weight_decay = (T)c->weight_decay;
+    adam_kernel<T><<<grid, 256, 0, stream_>>>(d_params_, d_flat_ + 1, d_m_, d_v_, k, clip, (long long)n_params_);
+    return launched("adam_kernel");
+}
+
+template <typename T>
+qb200_status Plan<T>::loss(void* host_scalar) {
+    if (host_scalar == nullptr) return fail(QB200_INVALID, "loss needs a host scalar");
+    QB_TRY(run(true));
+    QB_CUDA(cudaMemcpyAsync(host_scalar, d_loss_only_, sizeof(T), cudaMemcpyDeviceToHost, stream_));
+    QB_CUDA(cudaStreamSynchronize(stream_));
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::read_input(const char* name, void* host, size_t nbytes) {
+    if (name == nullptr || host == nullptr) return fail(QB200_INVALID, "read_input needs a name and a host buffer");
+    QB_TRY(use_device());
+    const std::string key(name);
+    const T* src = nullptr;
+    size_t count = 0;
+    if (key == kCotangentName) {
+        src = d_ct_;
+        count = 1;
+    }
+    for (size_t i = 0; i < desc_.params.size() && src == nullptr; ++i)
+        if (desc_.params[i].name == key) {
+            if (!leaves_[i].bound) return fail(QB200_NOT_BOUND, "parameter '%s' was never bound", name);
+            src = d_params_ + leaves_[i].offset;
+            count = leaves_[i].count;
+        }
+    for (size_t i = 0; i < desc_.inputs.size() && src == nullptr; ++i)
+        if (desc_.inputs[i].name == key) {
+            if (!inputs_[i].bound) return fail(QB200_NOT_BOUND, "input '%s' was never bound", name);
+            src = inputs_[i].dev;
+            count = (size_t)(desc_.inputs[i].rows * desc_.inputs[i].cols);
+        }
+    if (src == nullptr) return fail(QB200_INVALID, "the plan has no input named '%s'", name);
+    if (nbytes != count * sizeof(T)) return fail(QB200_INVALID, "input '%s' has %zu bytes, got a buffer of %zu", name, count * sizeof(T), nbytes);
+    QB_CUDA(cudaMemcpyAsync(host, src, nbytes, cudaMemcpyDeviceToHost, stream_));
+    QB_CUDA(cudaStreamSynchronize(stream_));
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::read_moments(int which, void* host, size_t nbytes) {
+    QB_TRY(use_device());
+    if (which != 0 && which != 1) return fail(QB200_INVALID, "moment selector must be 0 or 1");
+    if (nbytes != n_params_ * sizeof(T)) return fail(QB200_INVALID, "moments are %zu bytes, got a buffer of %zu", n_params_ * sizeof(T), nbytes);
+    if (!moments_ready_) {
+        memset(host, 0, nbytes);
+        return QB200_OK;
+    }
+    QB_CUDA(cudaMemcpyAsync(host, which == 0 ? d_m_ : d_v_, nbytes, cudaMemcpyDeviceToHost, stream_));
+    QB_CUDA(cudaStreamSynchronize(stream_));
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::write_moments(int which, const void* host, size_t nbytes, int64_t step_count) {
+    QB_TRY(use_device());
+    if (which != 0 && which != 1) return fail(QB200_INVALID, "moment selector must be 0 or 1");
+    if (nbytes != n_params_ * sizeof(T)) return fail(QB200_INVALID, "moments are %zu bytes, got a buffer of %zu", n_params_ * sizeof(T), nbytes);
+    if (step_count < 0) return fail(QB200_INVALID, "step count must be nonnegative");
+    if (!moments_ready_) {
+        QB_TRY(dev_alloc(&d_m_, n_params_));
+        QB_TRY(dev_alloc(&d_v_, n_params_));
+        QB_CUDA(cudaMemsetAsync(d_m_, 0, n_params_ * sizeof(T), stream_));
+        QB_CUDA(cudaMemsetAsync(d_v_, 0, n_params_ * sizeof(T), stream_));
+        moments_ready_ = true;
+    }
+    QB_CUDA(cudaMemcpyAsync(which == 0 ? d_m_ : d_v_, host, nbytes, cudaMemcpyHostToDevice, stream_));
+    QB_CUDA(cudaStreamSynchronize(stream_));
+    steps_ = step_count;
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::query(int key, int64_t* out) {
+    if (out == nullptr) return fail(QB200_INVALID, "query needs an output");
+    switch (key) {
+        case QB200_Q_DEVICE_BUFFER_COUNT: *out = (int64_t)buffers_.size(); return QB200_OK;
+        case QB200_Q_NONFINITE_CLIP_SEEN: {
+            QB_TRY(use_device());
+            double s[3];
+            QB_CUDA(cudaMemcpyAsync(s, d_clip_, sizeof(s), cudaMemcpyDeviceToHost, stream_));
+            QB_CUDA(cudaStreamSynchronize(stream_));
+            *out = s[2] != 0.0;
+            return QB200_OK;
+        }
+        case QB200_Q_STREAM: *out = (int64_t)(intptr_t)stream_; return QB200_OK;
+        case QB200_Q_PARAMETER_COUNT: *out = (int64_t)n_params_; return QB200_OK;
+        case QB200_Q_OUTPUT_COUNT: *out = (int64_t)leaves_.size() + 1; return QB200_OK;
+        case QB200_Q_KERNEL_LAUNCHES: *out = launches_; return QB200_OK;
+        case QB200_Q_FLAT_DEVICE_PTR: *out = (int64_t)(intptr_t)d_flat_; return QB200_OK;
+        case QB200_Q_SCRATCH_BYTES: *out = (int64_t)scratch_bytes_; return QB200_OK;
+        case QB200_Q_STEP_COUNT: *out = steps_; return QB200_OK;
+        case QB200_Q_ENGINE: *out = 0; return QB200_OK;
+        default: return fail(QB200_INVALID, "unknown query key %d", key);
+    }
+}
+
+template <typename T>
+qb200_status Plan<T>::synchronize() {
+    QB_TRY(use_device());
+    QB_CUDA(cudaStreamSynchronize(stream_));
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::attach_comm(const void* id, int rank, int world, int reduction) {
+    if (id == nullptr) return fail(QB200_INVALID, "attach_comm needs the 128-byte NCCL id");
+    if (world < 1 || rank < 0 || rank >= world) return fail(QB200_INVALID, "rank %d of world %d", rank, world);
+    if (reduction != QB200_REDUCE_SUM && reduction != QB200_REDUCE_MEAN) return fail(QB200_INVALID, "reduction must be sum or mean");
+    if (comm_ != nullptr) return fail(QB200_INVALID, "a communicator is already attached");
+    const NcclApi* api = nccl_api();
+    if (api == nullptr) return QB200_NCCL_ERROR;
+    QB_TRY(use_device());
+    ncclUniqueId uid;
+    memcpy(&uid, id, sizeof(uid));
+    ncclResult_t r = api->CommInitRank(&comm_, world, uid, rank);
+    if (r != ncclSuccess) {
+        comm_ = nullptr;
+        return fail(QB200_NCCL_ERROR, "ncclCommInitRank failed: %s", api->GetErrorString(r));
+    }
+    world_ = world;
+    dp_scale_ = reduction == QB200_REDUCE_MEAN ? 1.0 / world : 1.0;
+    return QB200_OK;
+}
+
+template <typename T>
+qb200_status Plan<T>::detach_comm() {
+    if (comm_ == nullptr) return QB200_OK;
+    const NcclApi* api = nccl_api();
+    if (api != nullptr) {
+        use_device();
+        cudaStreamSynchronize(stream_);
+        api->CommAbort(comm_);
+    }
+    comm_ = nullptr;
+    world_ = 1;
+    dp_scale_ = 1.0;
+    return QB200_OK;
+}
+
+}  // namespace
+
+qb200_status make_plan(const qb200_desc& desc, int device, qb200_plan** out) {
+    QB_TRY(validate_desc(desc));
+    qb200_status st;
+    if (desc.dtype == QB200_F32) {
+        auto* p = new Plan<float>(desc, device);
+        st = p->init();
+        if (st != QB200_OK) {
+            delete p;
+            return st;
+        }
+        *out = p;
+    } else {
+        auto* p = new Plan<double>(desc, device);
+        st = p->init();
+        if (st != QB200_OK) {
+            delete p;
+            return st;
+        }
+        *out = p;
+    }
+    return QB200_OK;
+}
+
+}  // namespace qb

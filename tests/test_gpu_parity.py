@@ -1,0 +1,108 @@
+"""Device results against the CPU oracle, through the public API and the C ABI."""
+
+import numpy as np
+import pytest
+
+import quabla_b200 as qb
+from oracle import contracted
+from quabla_b200 import _lib, workloads
+from quabla_b200._plan import Plan, opt_config
+
+from _util import TOLERANCE, relative_error, traced
+
+pytestmark = pytest.mark.gpu
+
+SMALL = {"poisson1d": 128, "poisson2d": 2048, "burgers": 1024, "heat3d": 512, "beam": 2048}
+
+
+@pytest.mark.parametrize("name", workloads.ORDER)
+def test_value_and_grad_matches_the_oracle(cuda_device, name):
+    w, compiled, inputs = traced(name, SMALL[name])
+    expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
+    step = qb.jit(qb.value_and_grad(w.loss), device="cuda:0")
+    value, grads = step(w.params, *w.data)
+    tol = TOLERANCE[np.dtype(w.dtype)]
+    assert value.dtype == np.dtype(w.dtype)
+    assert relative_error(value, expected_loss) <= tol
+    got = {}
+    for layer, tree in enumerate(grads):
+        got[f"params/{layer}/w"], got[f"params/{layer}/b"] = tree["w"], tree["b"]
+    for (pname, _, _), expected in zip(compiled.spec.parameters, expected_grads):
+        assert got[pname].shape == np.shape(inputs[pname])
+        assert relative_error(got[pname].reshape(expected.shape), expected) <= tol, pname
+
+
+@pytest.mark.parametrize("name", ["poisson1d", "poisson2d"])
+def test_forward_only_loss_matches_execute(cuda_device, name):
+    w, compiled, inputs = traced(name, SMALL[name])
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    plan.execute()
+    tol = TOLERANCE[np.dtype(w.dtype)]
+    assert relative_error(plan.loss(), plan.read_output(0)) <= tol
+    plan.close()
+
+
+def test_repeated_steps_are_bit_identical(cuda_device):
+    # The reference guarantees one bit pattern over repeated runs
+    # (crates/quabla-core/tests/cuda_determinism.rs:1-11).
+    w, compiled, inputs = traced("poisson2d", 4096)
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    plan.execute()
+    first = [o.copy() for o in plan.outputs()]
+    for _ in range(20):
+        plan.execute()
+        for a, b in zip(first, plan.outputs()):
+            assert a.tobytes() == b.tobytes()
+    plan.close()
+
+
+@pytest.mark.parametrize("name,rule", [("poisson1d", "adam"), ("poisson2d", "adam"), ("poisson2d", "adamw"),
+                                        ("poisson1d", "sgd")])
+def test_optimizer_step_matches_the_host_rule(cuda_device, name, rule):
+    from oracle import adam as host
+
+    w, compiled, inputs = traced(name, SMALL[name])
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    kind = "sgd" if rule == "sgd" else "adam"
+    decay = 0.01 if rule == "adamw" else 0.0
+    config = opt_config(kind, 1e-3, weight_decay=decay)
+    dtype = np.dtype(w.dtype)
+    params = {p[0]: np.array(inputs[p[0]], dtype=dtype) for p in compiled.spec.parameters}
+    m = {k: np.zeros(v.shape, dtype=dtype) for k, v in params.items()}
+    v = {k: np.zeros(p.shape, dtype=dtype) for k, p in params.items()}
+    for step in range(1, 4):
+        plan.execute()
+        grads = plan.outputs()[1:]
+        plan.optimizer_step(config)
+        for (pname, _, _), g in zip(compiled.spec.parameters, grads):
+            if kind == "sgd":
+                params[pname] = host.sgd_update(params[pname], g.reshape(params[pname].shape), 1e-3, dtype)
+            else:
+                params[pname], m[pname], v[pname] = host.adam_update(
+                    params[pname], g.reshape(params[pname].shape), m[pname], v[pname], step, 1e-3, 0.9, 0.999, 1e-8,
+                    decay, dtype)
+        for index, (pname, _, _) in enumerate(compiled.spec.parameters):
+            device = plan.read_parameter(index)
+            # Same rounded operations in the same order: bit-exact.
+            assert device.tobytes() == params[pname].reshape(device.shape).tobytes(), (pname, step)
+    assert plan.query(_lib.Q_STEP_COUNT) == 3
+    plan.close()
+
+
+def test_trainer_reduces_the_loss(cuda_device):
+    w = workloads.make("poisson1d")
+    trainer = qb.optim.Trainer(w.loss, w.params, qb.optim.Adam(learning_rate=1e-2), *w.data, device="cuda:0")
+    initial = float(trainer.loss())
+    for _ in range(200):
+        trainer.step()
+    final = float(trainer.loss())
+    assert np.isfinite(final) and final < 0.2 * initial
+    params = trainer.params
+    assert params[0]["w"].shape == (1, 16) and params[2]["b"].shape == (1,)
+    assert trainer._executor.device_buffer_count > 0
