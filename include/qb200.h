@@ -255,6 +255,19 @@ qb200_status qb200_optimizer_apply(int32_t dtype, void* d_param, const void* d_g
                                    int64_t count, const qb200_opt_config* config, int64_t step,
                                    void* cuda_stream);
 
+/* ------------------------------------------------------------------------
+ * Stand-alone batch-reduced weight gradient over caller-owned device arrays:
+ *   grad[d_in][d_out] = sum over rows of acts[row][d_in]^T cots[row][d_out],
+ * the contraction the reference reaches as a materialised [B, in, out] product
+ * followed by a sum over the batch axis (op/vjp.rs:176-209,
+ * tensor_ir.rs:9324-9353, cuda.rs:8202-8247).  Rows are summed in the array
+ * dtype per slice of 4096 rows, the slices then in double in ascending order,
+ * so the result is bit-reproducible.  Allocates its split scratch from the
+ * stream-ordered pool for the duration of the call.
+ * ------------------------------------------------------------------------ */
+qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void* d_cots, int64_t rows,
+                                   int32_t d_in, int32_t d_out, void* d_grad, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

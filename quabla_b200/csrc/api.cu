@@ -10,6 +10,7 @@
 #include <mutex>
 #include <set>
 
+#include "layer_kernels.cuh"
 #include "plan.h"
 #include "point_kernels.cuh"
 
@@ -148,6 +149,38 @@ static qb200_status optimizer_apply_typed(void* p, const void* g, void* m, void*
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "optimizer launch failed: %s", cudaGetErrorString(e));
+    return QB200_OK;
+}
+
+template <typename T>
+static qb200_status weight_gradient_typed(const void* acts, const void* cots, int64_t rows, int d_in, int d_out,
+                                          void* grad, cudaStream_t stream) {
+    const int slices = (int)((rows + qb::WGRAD_ROWS_PER_SLICE - 1) / qb::WGRAD_ROWS_PER_SLICE);
+    const size_t count = (size_t)d_in * d_out;
+    void* scratch = nullptr;
+    QB_CUDA(cudaMallocAsync(&scratch, (size_t)slices * count * sizeof(T), stream));
+    qb::GemmArgs<T> g;
+    g.A = static_cast<const T*>(acts);
+    g.B = static_cast<const T*>(cots);
+    g.C = static_cast<T*>(scratch);
+    g.bias = nullptr;
+    g.sam = 1;
+    g.sak = d_in;
+    g.sbk = d_out;
+    g.sbn = 1;
+    g.M = d_in;
+    g.N = d_out;
+    g.K = (int)rows;
+    g.ldc = d_out;
+    g.bias_rows = 0;
+    g.k_chunk = qb::WGRAD_ROWS_PER_SLICE;
+    dim3 grid((d_out + qb::GEMM_BN - 1) / qb::GEMM_BN, (d_in + qb::GEMM_BM - 1) / qb::GEMM_BM, slices);
+    qb::gemm_kernel<T, false, true><<<grid, 256, 0, stream>>>(g);
+    qb::reduce_partials_kernel<T><<<((int)count + 255) / 256, 256, 0, stream>>>(static_cast<const T*>(scratch),
+                                                                               static_cast<T*>(grad), (int)count, slices);
+    cudaError_t e = cudaGetLastError();
+    cudaFreeAsync(scratch, stream);
+    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "weight gradient launch failed: %s", cudaGetErrorString(e));
     return QB200_OK;
 }
 
@@ -485,6 +518,17 @@ qb200_status qb200_optimizer_apply(int32_t dtype, void* d_param, const void* d_g
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     if (dtype == QB200_F32) return optimizer_apply_typed<float>(d_param, d_grad, d_m, d_v, count, config, step, s);
     if (dtype == QB200_F64) return optimizer_apply_typed<double>(d_param, d_grad, d_m, d_v, count, config, step, s);
+    return fail(QB200_INVALID, "unknown dtype %d", dtype);
+}
+
+qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void* d_cots, int64_t rows, int32_t d_in,
+                                   int32_t d_out, void* d_grad, void* cuda_stream) {
+    if (d_acts == nullptr || d_cots == nullptr || d_grad == nullptr) return fail(QB200_INVALID, "weight_gradient needs three device arrays");
+    if (rows < 1 || rows > (int64_t)1 << 30 || d_in < 1 || d_out < 1 || d_in > 65536 || d_out > 65536)
+        return fail(QB200_INVALID, "weight_gradient: rows %lld, d_in %d, d_out %d out of range", (long long)rows, d_in, d_out);
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    if (dtype == QB200_F32) return weight_gradient_typed<float>(d_acts, d_cots, rows, d_in, d_out, d_grad, s);
+    if (dtype == QB200_F64) return weight_gradient_typed<double>(d_acts, d_cots, rows, d_in, d_out, d_grad, s);
     return fail(QB200_INVALID, "unknown dtype %d", dtype);
 }
 

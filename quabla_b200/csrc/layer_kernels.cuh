@@ -34,6 +34,7 @@ struct GemmArgs {
     int k_chunk;         // k range per grid.z slice
 };
 
+constexpr int WGRAD_ROWS_PER_SLICE = 4096;  // rows summed in the plan dtype before the double reduction
 constexpr int GEMM_BM = 64;
 constexpr int GEMM_BN = 64;
 constexpr int GEMM_BK = 16;
@@ -147,6 +148,16 @@ __global__ void accumulate_partials_kernel(const T* __restrict__ partial, double
     double s = 0.0;
     for (int z = 0; z < slices; ++z) s += (double)partial[(long long)z * count + i];
     acc[i] += s;
+}
+
+// out[i] = sum_z partial[z][i], z ascending, summed in double and rounded once.
+template <typename T>
+__global__ void reduce_partials_kernel(const T* __restrict__ partial, T* __restrict__ out, int count, int slices) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    double s = 0.0;
+    for (int z = 0; z < slices; ++z) s += (double)partial[(long long)z * count + i];
+    out[i] = (T)s;
 }
 
 // ---------------------------------------------------------------------------

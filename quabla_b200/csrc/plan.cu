@@ -241,7 +241,7 @@ class Plan final : public qb200_plan {
     int world_ = 1;
 };
 
-constexpr int K_CHUNK_ROWS = 4096;  // rows summed in the plan dtype before the double reduction
+constexpr int K_CHUNK_ROWS = WGRAD_ROWS_PER_SLICE;
 
 template <typename T>
 void Plan<T>::release() {

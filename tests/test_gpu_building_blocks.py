@@ -1,0 +1,73 @@
+"""The stand-alone entry points over caller-owned device arrays."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from quabla_b200 import _lib
+from quabla_b200._plan import opt_config
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptr(tensor):
+    return C.c_void_p(tensor.data_ptr())
+
+
+@pytest.mark.parametrize("dtype_name,rows,d_in,d_out", [
+    ("float64", 1, 1, 1), ("float64", 127, 3, 17), ("float64", 5000, 16, 16), ("float32", 129, 17, 1),
+    ("float32", 40000, 64, 64), ("float32", 8192, 2, 64), ("float64", 12289, 128, 65),
+])
+def test_weight_gradient_matches_a_float64_contraction(cuda_device, dtype_name, rows, d_in, d_out):
+    import torch
+
+    lib = _lib.load()
+    dtype = getattr(torch, dtype_name)
+    generator = torch.Generator(device="cuda").manual_seed(rows + d_in)
+    acts = torch.randn(rows, d_in, dtype=dtype, device="cuda", generator=generator)
+    cots = torch.randn(rows, d_out, dtype=dtype, device="cuda", generator=generator)
+    grad = torch.full((d_in, d_out), float("nan"), dtype=dtype, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = _lib.F32 if dtype_name == "float32" else _lib.F64
+    _lib.check(lib.qb200_weight_gradient(code, _ptr(acts), _ptr(cots), rows, d_in, d_out, _ptr(grad), stream))
+    torch.cuda.synchronize()
+    expected = (acts.double().T @ cots.double()).cpu().numpy()
+    # float32: each 4096-row slice is summed in float32 (relative ~1e-6 of the
+    # term magnitudes), slices in double; float64 is limited by summation order.
+    scale = np.sqrt(rows)
+    tolerance = (2e-6 if dtype_name == "float32" else 1e-14) * scale * 4
+    assert np.max(np.abs(grad.cpu().numpy() - expected)) <= tolerance
+
+
+def test_weight_gradient_rejects_bad_arguments(cuda_device):
+    lib = _lib.load()
+    assert lib.qb200_weight_gradient(_lib.F32, None, None, 1, 1, 1, None, None) == _lib.INVALID
+    assert lib.qb200_weight_gradient(7, C.c_void_p(8), C.c_void_p(8), 1, 1, 1, C.c_void_p(8), None) == _lib.INVALID
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "float64"])
+def test_optimizer_apply_matches_the_host_rule_bit_for_bit(cuda_device, dtype_name):
+    import torch
+
+    from oracle import adam as host
+
+    lib = _lib.load()
+    dtype = np.dtype(dtype_name)
+    rng = np.random.default_rng(3)
+    count = 10007
+    p = rng.standard_normal(count).astype(dtype)
+    g = (rng.standard_normal(count) * 10.0 ** rng.integers(-6, 3, count)).astype(dtype)
+    m = np.zeros(count, dtype=dtype)
+    v = np.zeros(count, dtype=dtype)
+    dp, dg, dm, dv = (torch.from_numpy(a.copy()).cuda() for a in (p, g, m, v))
+    config = opt_config("adam", 3e-3, 0.9, 0.999, 1e-8, 0.01)
+    code = _lib.F32 if dtype_name == "float32" else _lib.F64
+    for step in range(1, 4):
+        _lib.check(lib.qb200_optimizer_apply(code, _ptr(dp), _ptr(dg), _ptr(dm), _ptr(dv), count, C.byref(config),
+                                             step, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        torch.cuda.synchronize()
+        p, m, v = host.adam_update(p, g, m, v, step, 3e-3, 0.9, 0.999, 1e-8, 0.01, dtype)
+        assert dp.cpu().numpy().tobytes() == p.tobytes()
+        assert dm.cpu().numpy().tobytes() == m.tobytes()
+        assert dv.cpu().numpy().tobytes() == v.tobytes()
