@@ -268,6 +268,31 @@ qb200_status qb200_optimizer_apply(int32_t dtype, void* d_param, const void* d_g
 qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void* d_cots, int64_t rows,
                                    int32_t d_in, int32_t d_out, void* d_grad, void* cuda_stream);
 
+/* ------------------------------------------------------------------------
+ * qb200_weight_gradient for callers that cannot allocate device memory.
+ * No counterpart in the reference: its backend allocates freely from a pool.
+ *
+ * Meant for hosts where device allocation is not available at call time: a
+ * plugin inside a runtime that owns the memory pool, a latency-bound loop that
+ * may not take the allocator lock, a process that has already handed every
+ * free byte to something else.  Same arguments, same result (bit for bit) as
+ * qb200_weight_gradient, but the split scratch is a 16 MiB array built into
+ * the library (held on every GPU that loads the library until the process
+ * exits) and no cudaMalloc/cudaFree or other allocating call is made.
+ *
+ *  - Limit: ceil(rows / 4096) * d_in * d_out * sizeof(element) <= 16 MiB,
+ *    otherwise QB200_TOO_LARGE and nothing is launched.
+ *  - The first call on each device looks up the array's device address (with
+ *    that device current); make that first call before starting any stream
+ *    capture.
+ *  - All calls on a device share the one array: two calls whose kernels can
+ *    overlap on the GPU (different streams, no ordering) race; order them.
+ *    The array keeps the previous call's contents, which this function never
+ *    reads.
+ * ------------------------------------------------------------------------ */
+qb200_status qb200_weight_gradient_static(int32_t dtype, const void* d_acts, const void* d_cots, int64_t rows,
+                                          int32_t d_in, int32_t d_out, void* d_grad, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
