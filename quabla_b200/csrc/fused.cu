@@ -1,0 +1,70 @@
+// Instantiations of the fused engine.
+#include "fused.h"
+
+#include "fused_kernel.cuh"
+
+namespace qb {
+
+namespace {
+
+template <typename T, int W, int CODE>
+FusedEntry<T> make_entry() {
+    typedef FusedGeom<T, W, CODE> G;
+    FusedEntry<T> e;
+    e.kernel = fused_step_kernel<T, W, CODE>;
+    e.streams = G::S;
+    e.tile_points = G::TP;
+    e.smem_bytes = G::SMEM_BASE_BYTES;
+    e.scratch_per_layer = G::SCRATCH_PER_CTA;
+    return e;
+}
+
+}  // namespace
+
+// Signature codes: 0 = value only; 1 = {1}; 2 = {2}; 3 = {3}; 4 = {4}; 6 = {1,1};
+// 7 = {2,1}; 11 = {1,2}; 12 = {2,2}.
+#define QB_CASE(T, W, CODE)                           \
+    if (width == W && code == CODE) {                 \
+        *out = make_entry<T, W, CODE>();              \
+        return true;                                  \
+    }
+
+template <>
+bool fused_lookup<float>(int width, int code, FusedEntry<float>* out) {
+    QB_CASE(float, 64, 0) QB_CASE(float, 64, 1) QB_CASE(float, 64, 2) QB_CASE(float, 64, 4)
+    QB_CASE(float, 64, 7) QB_CASE(float, 64, 12)
+    QB_CASE(float, 32, 0) QB_CASE(float, 32, 1) QB_CASE(float, 32, 2) QB_CASE(float, 32, 12)
+    QB_CASE(float, 16, 0) QB_CASE(float, 16, 1) QB_CASE(float, 16, 2) QB_CASE(float, 16, 12)
+    return false;
+}
+
+template <>
+bool fused_lookup<double>(int width, int code, FusedEntry<double>* out) {
+    QB_CASE(double, 16, 0) QB_CASE(double, 16, 1) QB_CASE(double, 16, 2) QB_CASE(double, 16, 7)
+    QB_CASE(double, 16, 12)
+    QB_CASE(double, 32, 0) QB_CASE(double, 32, 1) QB_CASE(double, 32, 2)
+    return false;
+}
+
+template <typename T>
+cudaError_t fused_launch(const FusedEntry<T>& entry, int grid, cudaStream_t stream, const FusedArgs<T>& args) {
+    const size_t smem = fused_smem_bytes(entry, args.prog.n_instr);
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(entry.kernel),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    entry.kernel<<<grid, FUSED_THREADS, smem, stream>>>(args);
+    return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t fused_reduce_launch(const T* grad_cta, double* acc, int P, int ctas, cudaStream_t stream) {
+    fused_reduce_kernel<T><<<(P + 255) / 256, 256, 0, stream>>>(grad_cta, acc, P, ctas);
+    return cudaGetLastError();
+}
+
+template cudaError_t fused_launch<float>(const FusedEntry<float>&, int, cudaStream_t, const FusedArgs<float>&);
+template cudaError_t fused_launch<double>(const FusedEntry<double>&, int, cudaStream_t, const FusedArgs<double>&);
+template cudaError_t fused_reduce_launch<float>(const float*, double*, int, int, cudaStream_t);
+template cudaError_t fused_reduce_launch<double>(const double*, double*, int, int, cudaStream_t);
+
+}  // namespace qb

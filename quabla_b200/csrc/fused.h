@@ -1,0 +1,40 @@
+// Lookup of the fused-engine kernel instantiations (see fused_kernel.cuh).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace qb {
+
+template <typename T> struct FusedArgs;
+
+template <typename T>
+struct FusedEntry {
+    void (*kernel)(FusedArgs<T>);
+    int streams;                  // S
+    int tile_points;              // TP
+    size_t smem_bytes;            // dynamic shared memory per CTA, without the residual program
+    size_t scratch_per_layer;     // saved-jet elements per CTA per hidden layer (each of Z and H)
+};
+
+constexpr size_t FUSED_MAX_SMEM = 227 * 1024;
+
+// Dynamic shared memory of a launch: the regions plus the staged residual program.
+template <typename T>
+inline size_t fused_smem_bytes(const FusedEntry<T>& entry, int n_instr) {
+    return entry.smem_bytes + (size_t)n_instr * 16 + 16;
+}
+
+// True when a kernel exists for this dtype, hidden width and derivative
+// signature code (sum over directions j of order_j * 5^j).
+template <typename T>
+bool fused_lookup(int width, int code, FusedEntry<T>* out);
+
+// Launches entry.kernel; sets the shared-memory attribute on first use.
+template <typename T>
+cudaError_t fused_launch(const FusedEntry<T>& entry, int grid, cudaStream_t stream, const FusedArgs<T>& args);
+
+template <typename T>
+cudaError_t fused_reduce_launch(const T* grad_cta, double* acc, int P, int ctas, cudaStream_t stream);
+
+}  // namespace qb

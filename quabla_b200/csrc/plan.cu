@@ -6,6 +6,8 @@
 #include <cstring>
 #include <limits>
 
+#include "fused.h"
+#include "fused_kernel.cuh"
 #include "layer_kernels.cuh"
 #include "point_kernels.cuh"
 
@@ -196,6 +198,8 @@ class Plan final : public qb200_plan {
     qb200_status refresh_tables();
     qb200_status run(bool forward_only);
     qb200_status run_chunk(int si, long long point0, int C, int partial_slot, bool forward_only);
+    qb200_status run_fused(int si, bool forward_only);
+    bool choose_fused();
     qb200_status launched(const char* what) {
         ++launches_;
         cudaError_t e = cudaGetLastError();
@@ -232,6 +236,14 @@ class Plan final : public qb200_plan {
     T* Uhat_ = nullptr;
     T* wpartial_ = nullptr;
     size_t scratch_bytes_ = 0;
+    // fused engine (narrow networks): see fused_kernel.cuh
+    bool fused_ = false;
+    int fused_width_ = 0;
+    std::vector<FusedEntry<T>> fused_entries_;  // per set
+    std::vector<int> fused_grid_;               // per set
+    T* fused_z_ = nullptr;
+    T* fused_h_ = nullptr;
+    T* fused_grad_ = nullptr;
     int64_t launches_ = 0;
     int64_t steps_ = 0;
     bool executed_ = false;
@@ -276,7 +288,9 @@ qb200_status Plan<T>::init() {
         Leaf leaf;
         leaf.offset = offset;
         leaf.count = p.kind == QB200_WEIGHT ? (size_t)desc_.sizes[p.layer] * desc_.sizes[p.layer + 1] : (size_t)desc_.sizes[p.layer + 1];
-        offset += leaf.count;
+        // Leaves start on 4-element boundaries so that kernels may use vector loads; the
+        // padding stays zero (zero gradient, zero parameter, zero moments).
+        offset += (leaf.count + 3) / 4 * 4;
         leaves_.push_back(leaf);
         (p.kind == QB200_WEIGHT ? w_leaf_ : b_leaf_)[p.layer] = (int)i;
     }
@@ -288,6 +302,7 @@ qb200_status Plan<T>::init() {
     QB_TRY(dev_alloc(&d_loss_only_, 1));
     QB_TRY(dev_alloc(&d_clip_, 3));
     QB_CUDA(cudaMemsetAsync(d_flat_, 0, (1 + n_params_) * sizeof(T), stream_));
+    QB_CUDA(cudaMemsetAsync(d_params_, 0, n_params_ * sizeof(T), stream_));
     QB_CUDA(cudaMemsetAsync(d_clip_, 0, 3 * sizeof(double), stream_));
     const T one = T(1);
     QB_CUDA(cudaMemcpyAsync(d_ct_, &one, sizeof(T), cudaMemcpyHostToDevice, stream_));
@@ -297,6 +312,7 @@ qb200_status Plan<T>::init() {
     for (size_t i = 0; i < desc_.inputs.size(); ++i)
         QB_TRY(dev_alloc(&inputs_[i].dev, (size_t)(desc_.inputs[i].rows * desc_.inputs[i].cols)));
 
+    fused_ = choose_fused();
     // Saved-jet scratch: sized per set from a byte budget, then the maximum over sets.
     const int d0 = desc_.sizes[0];
     int dmax = 0;
@@ -377,10 +393,25 @@ qb200_status Plan<T>::init() {
         for (int k = 0; k < MAX_STREAMS; ++k) st.prog.grad_regs[k] = k < (int)s.grad_regs.size() ? s.grad_regs[k] : -1;
         const int chunks = (int)((s.n + chunk - 1) / chunk);
         st.partial_offset = total_partials_;
-        st.partial_count = chunks * (int)((chunk + 255) / 256);
+        st.partial_count = fused_ ? fused_grid_[si] : chunks * (int)((chunk + 255) / 256);
         total_partials_ += st.partial_count;
     }
     QB_TRY(dev_alloc(&d_partials_, (size_t)total_partials_));
+    if (fused_) {
+        // Per-CTA saved jets (rewritten every tile, so they stay in L2) and per-CTA
+        // gradient rows; the layer-wise scratch is not needed.
+        size_t jets = 0, rows = 0;
+        const int hidden = L_ - 1;
+        for (size_t si = 0; si < sets_.size(); ++si) {
+            jets = std::max(jets, (size_t)fused_grid_[si] * hidden * fused_entries_[si].scratch_per_layer);
+            rows = std::max(rows, (size_t)fused_grid_[si]);
+        }
+        QB_TRY(dev_alloc(&fused_z_, jets));
+        QB_TRY(dev_alloc(&fused_h_, jets));
+        QB_TRY(dev_alloc(&fused_grad_, rows * n_params_));
+        scratch_bytes_ = (2 * jets + rows * n_params_) * sizeof(T);
+        return QB200_OK;
+    }
     H_.assign(L_, nullptr);
     Z_.assign(L_, nullptr);
     scratch_bytes_ = 0;
@@ -474,6 +505,74 @@ qb200_status Plan<T>::refresh_tables() {
         gather_table_kernel<T><<<grid_for(n * st.ncols, 256), 256, 0, stream_>>>(a, st.table, n);
         QB_TRY(launched("gather_table_kernel"));
         st.table_dirty = false;
+    }
+    return QB200_OK;
+}
+
+template <typename T>
+bool Plan<T>::choose_fused() {
+    if (const char* env = getenv("QB200_ENGINE"))
+        if (std::string(env) == "layerwise") return false;
+    const int hidden = L_ - 1;
+    if (hidden < 1 || hidden > FUSED_MAX_LAYERS || desc_.sizes[0] > 4) return false;
+    const int W = desc_.sizes[1];
+    for (int l = 1; l <= hidden; ++l)
+        if (desc_.sizes[l] != W) return false;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_);
+    fused_entries_.resize(desc_.sets.size());
+    fused_grid_.resize(desc_.sets.size());
+    for (size_t si = 0; si < desc_.sets.size(); ++si) {
+        const auto& s = desc_.sets[si];
+        int code = 0, scale = 1;
+        for (int k : s.orders) {
+            code += k * scale;
+            scale *= 5;
+        }
+        if (!fused_lookup<T>(W, code, &fused_entries_[si])) return false;
+        if (fused_smem_bytes(fused_entries_[si], (int)s.code.size() / 4) > FUSED_MAX_SMEM) return false;
+        const long long tiles = (s.n + fused_entries_[si].tile_points - 1) / fused_entries_[si].tile_points;
+        fused_grid_[si] = (int)std::min<long long>(tiles, sms);
+    }
+    fused_width_ = W;
+    return true;
+}
+
+template <typename T>
+qb200_status Plan<T>::run_fused(int si, bool forward_only) {
+    SetState& st = sets_[si];
+    const auto& s = desc_.sets[si];
+    FusedArgs<T> a;
+    a.L = L_ - 1;
+    a.d0 = desc_.sizes[0];
+    a.P = (int)n_params_;
+    a.params = d_params_;
+    for (int l = 0; l <= FUSED_MAX_LAYERS; ++l) {
+        a.w_off[l] = l < L_ ? (int)leaves_[w_leaf_[l]].offset : 0;
+        a.b_off[l] = (l < L_ && b_leaf_[l] >= 0) ? (int)leaves_[b_leaf_[l]].offset : -1;
+    }
+    a.table = st.table;
+    a.ncols = st.ncols;
+    a.n_points = s.n;
+    for (int i = 0; i < MAX_DIRS * 4; ++i) a.dirs[i] = T(0);
+    for (size_t j = 0; j < s.dirs.size(); ++j)
+        for (int k = 0; k < a.d0; ++k) a.dirs[j * a.d0 + k] = (T)s.dirs[j][k];
+    a.prog = st.prog;
+    a.cotangent = d_ct_;
+    a.weight = (T)s.weight;
+    a.extra = (T)dp_scale_;
+    a.scratch_z = fused_z_;
+    a.scratch_h = fused_h_;
+    a.grad_cta = fused_grad_;
+    a.loss_cta = d_partials_ + st.partial_offset;
+    a.forward_only = forward_only ? 1 : 0;
+    cudaError_t e = fused_launch<T>(fused_entries_[si], fused_grid_[si], stream_, a);
+    ++launches_;
+    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of fused_step_kernel failed: %s", cudaGetErrorString(e));
+    if (!forward_only) {
+        e = fused_reduce_launch<T>(fused_grad_, d_acc_, (int)n_params_, fused_grid_[si], stream_);
+        ++launches_;
+        if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of fused_reduce_kernel failed: %s", cudaGetErrorString(e));
     }
     return QB200_OK;
 }
@@ -610,6 +709,13 @@ qb200_status Plan<T>::run(bool forward_only) {
         SetState& st = sets_[si];
         const long long n = desc_.sets[si].n;
         int slot = st.partial_offset;
+        if (fused_) {
+            QB_TRY(run_fused((int)si, forward_only));
+            la.offset[si] = st.partial_offset;
+            la.count[si] = fused_grid_[si];
+            la.weight[si] = desc_.sets[si].weight;
+            continue;
+        }
         for (long long p0 = 0; p0 < n; p0 += st.chunk) {
             const int C = (int)std::min<long long>(st.chunk, n - p0);
             QB_TRY(run_chunk((int)si, p0, C, slot, forward_only));
@@ -797,7 +903,7 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
         case QB200_Q_FLAT_DEVICE_PTR: *out = (int64_t)(intptr_t)d_flat_; return QB200_OK;
         case QB200_Q_SCRATCH_BYTES: *out = (int64_t)scratch_bytes_; return QB200_OK;
         case QB200_Q_STEP_COUNT: *out = steps_; return QB200_OK;
-        case QB200_Q_ENGINE: *out = 0; return QB200_OK;
+        case QB200_Q_ENGINE: *out = fused_ ? 1 : 0; return QB200_OK;
         default: return fail(QB200_INVALID, "unknown query key %d", key);
     }
 }

@@ -15,12 +15,22 @@ pytestmark = pytest.mark.gpu
 SMALL = {"poisson1d": 128, "poisson2d": 2048, "burgers": 1024, "heat3d": 512, "beam": 2048}
 
 
+FUSED = {"poisson1d", "poisson2d", "beam"}  # narrow networks take the fused engine by default
+
+
+@pytest.mark.parametrize("engine", ["default", "layerwise"])
 @pytest.mark.parametrize("name", workloads.ORDER)
-def test_value_and_grad_matches_the_oracle(cuda_device, name):
+def test_value_and_grad_matches_the_oracle(cuda_device, monkeypatch, name, engine):
+    if engine == "layerwise":
+        if name not in FUSED:
+            pytest.skip("the default engine of this workload is already the layer-wise one")
+        monkeypatch.setenv("QB200_ENGINE", "layerwise")
     w, compiled, inputs = traced(name, SMALL[name])
     expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
     step = qb.jit(qb.value_and_grad(w.loss), device="cuda:0")
     value, grads = step(w.params, *w.data)
+    used = next(iter(step._inner._cache.values())).plan.query(_lib.Q_ENGINE)
+    assert used == (1 if (name in FUSED and engine == "default") else 0)
     tol = TOLERANCE[np.dtype(w.dtype)]
     assert value.dtype == np.dtype(w.dtype)
     assert relative_error(value, expected_loss) <= tol
@@ -41,6 +51,30 @@ def test_forward_only_loss_matches_execute(cuda_device, name):
     plan.execute()
     tol = TOLERANCE[np.dtype(w.dtype)]
     assert relative_error(plan.loss(), plan.read_output(0)) <= tol
+    plan.close()
+
+
+@pytest.mark.parametrize("name,points", [("poisson2d", 33), ("poisson2d", 4999), ("beam", 1), ("beam", 31),
+                                         ("poisson1d", 127), ("poisson1d", 129), ("poisson1d", 1000)])
+def test_ragged_point_counts(cuda_device, name, points):
+    # Point counts that do not fill the last tile of the fused engine.
+    w, compiled, inputs = traced(name, points)
+    w.data = tuple(np.ascontiguousarray(a[:points]) if a.shape[0] > points else a for a in w.data)
+    args = (w.params, *w.data)
+    from quabla_b200._transforms import CompiledLoss
+
+    compiled = CompiledLoss(w.loss, args, (0,), 0, build_plan=False)
+    inputs = compiled.named_inputs(args)
+    expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    plan.execute()
+    outputs = plan.outputs()
+    tol = TOLERANCE[np.dtype(w.dtype)]
+    assert relative_error(outputs[0], expected_loss) <= tol
+    for got, expected, (pname, _, _) in zip(outputs[1:], expected_grads, compiled.spec.parameters):
+        assert relative_error(got.reshape(expected.shape), expected) <= tol, pname
     plan.close()
 
 
