@@ -1,0 +1,13 @@
+"""Literal oracle — TEST INFRASTRUCTURE, not product.
+
+A NumPy restatement of how the reference turns a Python loss into numbers:
+tracing into a tensor IR (ir.py), the graph transforms behind grad / vmap /
+hessian (transforms.py), and the CPU interpreter with float64 compute and one
+rounding per node (interp.py).  api.py exposes it with the reference's call
+shapes, so one loss function can be evaluated by this oracle and by the CUDA
+backend.  It materialises the [B, in, out] weight-gradient products exactly as
+the reference plan does, so it is meant for small point counts.
+"""
+
+from .api import (Tracer, array, cos, exp, grad, hessian, mean, sin, sum, tanh, trace, value_and_grad,  # noqa: F401,A004
+                  value_and_grad_data_parallel, vmap, zeros)

@@ -1,7 +1,8 @@
 """The five PINN training workloads the backend is measured and tested on.
 
 Each workload is written against the public surface exactly as a user of the
-reference would write it (a per-point network, `grad`/`hessian` under `vmap`,
+reference would write it (the surface module is a parameter, so the same
+source can be traced by another implementation of that surface) (a per-point network, `grad`/`hessian` under `vmap`,
 `mean` of squared residuals), with seeded synthetic inputs:
 
   weights  W_l = glorot_normal(split(key(seed), layers)[l], [d_l, d_{l+1}]),
@@ -62,17 +63,21 @@ def init_mlp(key, sizes, dtype=np.float64):
             for k, m, n in zip(keys, sizes[:-1], sizes[1:])]
 
 
-def mlp(params, x):
-    h = x
-    for layer in params[:-1]:
-        h = qb.tanh(h @ layer["w"] + layer["b"])
-    last = params[-1]
-    return h @ last["w"] + last["b"]
+def make_u(api):
+    """The network as a scalar function of one point (scalar or vector), written
+    against `api` (this package, or any module with the same surface)."""
 
+    def mlp(params, x):
+        h = x
+        for layer in params[:-1]:
+            h = api.tanh(h @ layer["w"] + layer["b"])
+        last = params[-1]
+        return h @ last["w"] + last["b"]
 
-def u(params, p):
-    """The network as a scalar function of one point (scalar or vector)."""
-    return mlp(params, p.reshape(1, -1)).reshape(())
+    def u(params, p):
+        return mlp(params, p.reshape(1, -1)).reshape(())
+
+    return u
 
 
 def _column(seed: int, set_index: int, j: int, n: int, lo: float, hi: float, dtype) -> np.ndarray:
@@ -90,15 +95,17 @@ def _scaled(n: int, points: int | None, full: int) -> int:
 
 
 # -- 1: 1-D Poisson, float64 ---------------------------------------------------
-def poisson1d(points: int | None = None) -> Workload:
+def poisson1d(points: int | None = None, api=None) -> Workload:
+    api = qb if api is None else api
+    u = make_u(api)
     sizes, dtype, seed = [1, 16, 16, 1], np.float64, 0
     n = _scaled(128, points, 128)
 
     def loss(params, x, xb):
-        u_xx = qb.vmap(qb.grad(qb.grad(lambda t: u(params, t))))
-        residual = u_xx(x) + math.pi**2 * qb.sin(math.pi * x)
-        boundary = qb.vmap(lambda t: u(params, t))(xb)
-        return qb.mean(residual**2) + qb.mean(boundary**2)
+        u_xx = api.vmap(api.grad(api.grad(lambda t: u(params, t))))
+        residual = u_xx(x) + math.pi**2 * api.sin(math.pi * x)
+        boundary = api.vmap(lambda t: u(params, t))(xb)
+        return api.mean(residual**2) + api.mean(boundary**2)
 
     x = _column(seed, 0, 0, n, -1.0, 1.0, dtype)
     xb = np.array([-1.0, 1.0], dtype=dtype)
@@ -107,17 +114,19 @@ def poisson1d(points: int | None = None) -> Workload:
 
 
 # -- 2: 2-D Poisson on the unit square, float32 -----------------------------------
-def poisson2d(points: int | None = None) -> Workload:
+def poisson2d(points: int | None = None, api=None) -> Workload:
+    api = qb if api is None else api
+    u = make_u(api)
     sizes, dtype, seed = [2, 64, 64, 64, 64, 1], np.float32, 1
     n = _scaled(65536, points, 65536)
     nb = _scaled(4096, points, 65536)
     nb -= nb % 4
 
     def loss(params, p, pb):
-        laplacian = qb.vmap(lambda q: qb.trace(qb.hessian(lambda s: u(params, s))(q)))(p)
-        forcing = 2.0 * math.pi**2 * qb.sin(math.pi * p[:, 0]) * qb.sin(math.pi * p[:, 1])
-        boundary = qb.vmap(lambda q: u(params, q))(pb)
-        return qb.mean((laplacian + forcing) ** 2) + qb.mean(boundary**2)
+        laplacian = api.vmap(lambda q: api.trace(api.hessian(lambda s: u(params, s))(q)))(p)
+        forcing = 2.0 * math.pi**2 * api.sin(math.pi * p[:, 0]) * api.sin(math.pi * p[:, 1])
+        boundary = api.vmap(lambda q: u(params, q))(pb)
+        return api.mean((laplacian + forcing) ** 2) + api.mean(boundary**2)
 
     p = _points(seed, 0, n, [(0.0, 1.0), (0.0, 1.0)], dtype)
     free = _column(seed, 1, 0, nb, 0.0, 1.0, dtype)
@@ -130,7 +139,9 @@ def poisson2d(points: int | None = None) -> Workload:
 
 
 # -- 3: viscous Burgers (x, t), float64 --------------------------------------------
-def burgers(points: int | None = None) -> Workload:
+def burgers(points: int | None = None, api=None) -> Workload:
+    api = qb if api is None else api
+    u = make_u(api)
     sizes, dtype, seed = [2] + [128] * 8 + [1], np.float64, 2
     n = _scaled(262144, points, 262144)
     n_ic = _scaled(8192, points, 262144)
@@ -140,14 +151,14 @@ def burgers(points: int | None = None) -> Workload:
 
     def loss(params, p, p_ic, target_ic, p_bc):
         def residual(q):
-            value, g = qb.value_and_grad(lambda s: u(params, s))(q)
-            u_xx = qb.hessian(lambda s: u(params, s))(q)[0, 0]
+            value, g = api.value_and_grad(lambda s: u(params, s))(q)
+            u_xx = api.hessian(lambda s: u(params, s))(q)[0, 0]
             return g[1] + value * g[0] - nu * u_xx
 
-        interior = qb.vmap(residual)(p)
-        initial = qb.vmap(lambda q: u(params, q))(p_ic) - target_ic
-        wall = qb.vmap(lambda q: u(params, q))(p_bc)
-        return qb.mean(interior**2) + qb.mean(initial**2) + qb.mean(wall**2)
+        interior = api.vmap(residual)(p)
+        initial = api.vmap(lambda q: u(params, q))(p_ic) - target_ic
+        wall = api.vmap(lambda q: u(params, q))(p_bc)
+        return api.mean(interior**2) + api.mean(initial**2) + api.mean(wall**2)
 
     p = _points(seed, 0, n, [(-1.0, 1.0), (0.0, 1.0)], dtype)
     p_ic = np.stack([_column(seed, 1, 0, n_ic, -1.0, 1.0, dtype), np.zeros(n_ic, dtype=dtype)], axis=1)
@@ -160,7 +171,9 @@ def burgers(points: int | None = None) -> Workload:
 
 
 # -- 4: 3-D heat equation (x, y, z, t), float32 -------------------------------------
-def heat3d(points: int | None = None) -> Workload:
+def heat3d(points: int | None = None, api=None) -> Workload:
+    api = qb if api is None else api
+    u = make_u(api)
     sizes, dtype, seed = [4] + [256] * 6 + [1], np.float32, 3
     n = _scaled(1048576, points, 1048576)
     alpha, decay = 0.1, 0.3 * math.pi**2
@@ -168,13 +181,13 @@ def heat3d(points: int | None = None) -> Workload:
 
     def loss(params, p):
         def residual(q):
-            g = qb.grad(lambda s: u(params, s))(q)
-            h = qb.hessian(lambda s: u(params, s))(q)
-            source = source_scale * qb.exp(-decay * q[3]) * qb.sin(math.pi * q[0]) * qb.sin(math.pi * q[1]) \
-                * qb.sin(math.pi * q[2])
+            g = api.grad(lambda s: u(params, s))(q)
+            h = api.hessian(lambda s: u(params, s))(q)
+            source = source_scale * api.exp(-decay * q[3]) * api.sin(math.pi * q[0]) * api.sin(math.pi * q[1]) \
+                * api.sin(math.pi * q[2])
             return g[3] - alpha * (h[0, 0] + h[1, 1] + h[2, 2]) - source
 
-        return qb.mean(qb.vmap(residual)(p) ** 2)
+        return api.mean(api.vmap(residual)(p) ** 2)
 
     p = _points(seed, 0, n, [(0.0, 1.0)] * 4, dtype)
     return Workload("heat3d", "3D heat equation (x,y,z,t), tanh MLP 4-256x6-1, float32", sizes, dtype, seed, loss,
@@ -182,17 +195,19 @@ def heat3d(points: int | None = None) -> Workload:
 
 
 # -- 5: Euler-Bernoulli beam, 4th order, float32 --------------------------------------
-def beam(points: int | None = None) -> Workload:
+def beam(points: int | None = None, api=None) -> Workload:
+    api = qb if api is None else api
+    u = make_u(api)
     sizes, dtype, seed = [1] + [64] * 4 + [1], np.float32, 4
     n = _scaled(1048576, points, 1048576)
 
     def loss(params, x, xb):
         f = lambda t: u(params, t)  # noqa: E731
-        u_xxxx = qb.vmap(qb.grad(qb.grad(qb.grad(qb.grad(f)))))
-        residual = u_xxxx(x) - math.pi**4 * qb.sin(math.pi * x)
-        value = qb.vmap(f)(xb)
-        slope = qb.vmap(qb.grad(f))(xb)
-        return qb.mean(residual**2) + qb.mean(value**2) + qb.mean(slope**2)
+        u_xxxx = api.vmap(api.grad(api.grad(api.grad(api.grad(f)))))
+        residual = u_xxxx(x) - math.pi**4 * api.sin(math.pi * x)
+        value = api.vmap(f)(xb)
+        slope = api.vmap(api.grad(f))(xb)
+        return api.mean(residual**2) + api.mean(value**2) + api.mean(slope**2)
 
     x = _column(seed, 0, 0, n, 0.0, 1.0, dtype)
     xb = np.array([0.0, 1.0], dtype=dtype)
@@ -204,5 +219,6 @@ WORKLOADS = {"poisson1d": poisson1d, "poisson2d": poisson2d, "burgers": burgers,
 ORDER = ["poisson1d", "poisson2d", "burgers", "heat3d", "beam"]
 
 
-def make(name: str, points: int | None = None) -> Workload:
-    return WORKLOADS[name](points)
+def make(name: str, points: int | None = None, api=None) -> Workload:
+    """`api` selects the module the loss is written against (default: this package)."""
+    return WORKLOADS[name](points, api)
