@@ -42,8 +42,4 @@ def linspace(start, stop, num, dtype=float64):
     return _np.linspace(start, stop, num, dtype=dtype)
 
 
-def __getattr__(name):
-    if name == "distributed":
-        from . import distributed
-        return distributed
-    raise AttributeError(name)
+from . import distributed  # noqa: E402,F401

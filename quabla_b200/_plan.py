@@ -215,3 +215,77 @@ def nccl_unique_id() -> bytes:
     buffer = C.create_string_buffer(128)
     _lib.check(_lib.load().qb200_nccl_unique_id(buffer))
     return buffer.raw
+
+
+class DataParallelPlan:
+    """A single-process data-parallel plan (qb200_dp*): one replica per device,
+    driven by one host thread, the shape of the reference's
+    CudaDataParallelExecutionPlan (crates/quabla-core/src/tensor_ir/cuda.rs:116-170, 621-866).
+    `spec` describes ONE shard."""
+
+    def __init__(self, spec: PlanSpec, ordinals) -> None:
+        self.spec = spec
+        self.dtype = np.dtype(spec.dtype)
+        self.ordinals = [int(o) for o in ordinals]
+        self._lib = _lib.load()
+        desc = build_desc(spec)
+        try:
+            handle = C.c_void_p()
+            _lib.check(self._lib.qb200_dp_create(desc, _int32_array(self.ordinals), len(self.ordinals),
+                                                 C.byref(handle)))
+        finally:
+            self._lib.qb200_desc_destroy(desc)
+        self._handle = handle
+        self.last_timing = None
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            self._lib.qb200_dp_destroy(self._handle)
+        self._handle = None
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def replica_count(self) -> int:
+        return self._lib.qb200_dp_replica_count(self._handle)
+
+    def _host(self, value) -> np.ndarray:
+        return np.ascontiguousarray(np.asarray(value), dtype=self.dtype)
+
+    def bind_sharded(self, name: str, value) -> None:
+        host = self._host(value)
+        _lib.check(self._lib.qb200_dp_bind_sharded(self._handle, name.encode(), host.ctypes.data, host.nbytes))
+
+    def bind_replicated(self, name: str, value) -> None:
+        host = self._host(value)
+        _lib.check(self._lib.qb200_dp_bind_replicated(self._handle, name.encode(), host.ctypes.data, host.nbytes))
+
+    def step(self, reduction: str = "mean") -> dict:
+        timing = _lib.DpTiming()
+        code = {"sum": _lib.REDUCE_SUM, "mean": _lib.REDUCE_MEAN}[reduction]
+        _lib.check(self._lib.qb200_dp_step(self._handle, code, C.byref(timing)))
+        self.last_timing = {"replica_enqueue": timing.replica_enqueue, "collective": timing.collective,
+                            "output_readback": timing.output_readback}
+        return self.last_timing
+
+    def read_output(self, index: int) -> np.ndarray:
+        shape = () if index == 0 else self.spec.parameter_shape(index - 1)
+        out = np.empty(shape, dtype=self.dtype)
+        _lib.check(self._lib.qb200_dp_read_output(self._handle, index, out.ctypes.data, out.nbytes))
+        return out
+
+    def optimizer_step(self, config: _lib.OptConfig) -> None:
+        _lib.check(self._lib.qb200_dp_optimizer_step(self._handle, C.byref(config)))
+
+    def replica(self, rank: int) -> Plan:
+        handle = self._lib.qb200_dp_replica(self._handle, rank)
+        if not handle:
+            raise IndexError(f"replica {rank} of {self.replica_count}")
+        return Plan(self.spec, _handle=C.c_void_p(handle))
+
+    def inject_host_failure(self, rank: int) -> None:
+        _lib.check(self._lib.qb200_dp_inject_host_failure(self._handle, rank))
