@@ -88,7 +88,9 @@ def test_distributed_value_and_grad_over_two_devices(cuda_device):
         pytest.skip("needs two GPUs")
     w = workloads.make("poisson2d", 512)
     p, pb = w.data
-    step = qb.distributed.value_and_grad(w.loss, devices=["cuda:0", "cuda:1"], shard_argnums=(1, 2))
+    # Mapped leaves must share one batch size (python/quabla/distributed.py:107-111): the
+    # interior points are sharded, the small boundary set is replicated.
+    step = qb.distributed.value_and_grad(w.loss, devices=["cuda:0", "cuda:1"], shard_argnums=1)
     value, grads = step(w.params, p, pb)
     single_value, single_grads = qb.jit(qb.value_and_grad(w.loss), device="cuda:0")(w.params, p, pb)
     assert relative_error(value, single_value) <= 1e-5
