@@ -48,6 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         _nvcc(), *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17",
         "-Xcompiler", "-fPIC",
     ]
+    common += os.environ.get("QB200_NVCC_FLAGS", "").split()
     if verbose:
         common += ["-Xptxas", "-v"]
     procs = []

@@ -1,7 +1,12 @@
 // Instantiations of the fused engine.
 #include "fused.h"
 
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
 #include "fused_kernel.cuh"
+#include "fused_mma_kernel.cuh"
 
 namespace qb {
 
@@ -16,10 +21,37 @@ FusedEntry<T> make_entry() {
     e.tile_points = G::TP;
     e.smem_bytes = G::SMEM_BASE_BYTES;
     e.scratch_per_layer = G::SCRATCH_PER_CTA;
+    e.tensor_core = false;
     return e;
 }
 
+template <int CODE>
+FusedEntry<float> make_mma_entry() {
+    typedef MmaGeom<CODE> G;
+    FusedEntry<float> e;
+    e.kernel = fused_mma_kernel<CODE>;
+    e.streams = G::S;
+    e.tile_points = G::TP;
+    e.smem_bytes = G::SMEM_BASE_BYTES;
+    e.scratch_per_layer = G::SCRATCH_PER_CTA;
+    e.tensor_core = true;
+    return e;
+}
+
+// QB200_FUSED=simt keeps the FP32-pipe variant for float32 width-64 networks
+// (for comparisons); the default is the tensor-core (3xTF32) variant.
+bool want_simt() {
+    const char* env = getenv("QB200_FUSED");
+    return env != nullptr && strcmp(env, "simt") == 0;
+}
+
 }  // namespace
+
+#define QB_MMA_CASE(CODE)                             \
+    if (width == 64 && code == CODE && !want_simt()) { \
+        *out = make_mma_entry<CODE>();                \
+        return true;                                  \
+    }
 
 // Signature codes: 0 = value only; 1 = {1}; 2 = {2}; 3 = {3}; 4 = {4}; 6 = {1,1};
 // 7 = {2,1}; 11 = {1,2}; 12 = {2,2}.
@@ -31,6 +63,7 @@ FusedEntry<T> make_entry() {
 
 template <>
 bool fused_lookup<float>(int width, int code, FusedEntry<float>* out) {
+    QB_MMA_CASE(0) QB_MMA_CASE(1) QB_MMA_CASE(2) QB_MMA_CASE(4) QB_MMA_CASE(7) QB_MMA_CASE(12)
     QB_CASE(float, 64, 0) QB_CASE(float, 64, 1) QB_CASE(float, 64, 2) QB_CASE(float, 64, 4)
     QB_CASE(float, 64, 7) QB_CASE(float, 64, 12)
     QB_CASE(float, 32, 0) QB_CASE(float, 32, 1) QB_CASE(float, 32, 2) QB_CASE(float, 32, 12)
@@ -53,6 +86,20 @@ cudaError_t fused_launch(const FusedEntry<T>& entry, int grid, cudaStream_t stre
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     entry.kernel<<<grid, FUSED_THREADS, smem, stream>>>(args);
+    return cudaGetLastError();
+}
+
+size_t fused_weight_image_bytes(int hidden_to_hidden) {
+    return (size_t)std::max(hidden_to_hidden, 1) * 4 * WIMG_PLANE * sizeof(uint32_t);
+}
+
+cudaError_t fused_prep_launch(const float* params, const int* w_off, int hidden_to_hidden, void* images,
+                              cudaStream_t stream) {
+    if (hidden_to_hidden < 1) return cudaSuccess;
+    PrepArgs p;
+    p.layers = hidden_to_hidden;
+    for (int i = 0; i <= FUSED_MAX_LAYERS; ++i) p.w_off[i] = i < hidden_to_hidden ? w_off[i] : 0;
+    prep_weights_kernel<<<dim3(4, hidden_to_hidden), 256, 0, stream>>>(params, p, static_cast<uint32_t*>(images));
     return cudaGetLastError();
 }
 

@@ -15,6 +15,7 @@ struct FusedEntry {
     int tile_points;              // TP
     size_t smem_bytes;            // dynamic shared memory per CTA, without the residual program
     size_t scratch_per_layer;     // saved-jet elements per CTA per hidden layer (each of Z and H)
+    bool tensor_core;             // 3xTF32 variant: needs the pre-split weight images
 };
 
 constexpr size_t FUSED_MAX_SMEM = 227 * 1024;
@@ -33,6 +34,12 @@ bool fused_lookup(int width, int code, FusedEntry<T>* out);
 // Launches entry.kernel; sets the shared-memory attribute on first use.
 template <typename T>
 cudaError_t fused_launch(const FusedEntry<T>& entry, int grid, cudaStream_t stream, const FusedArgs<T>& args);
+
+// Bytes of the pre-split weight images of `hidden_to_hidden` layers of width 64.
+size_t fused_weight_image_bytes(int hidden_to_hidden);
+// Writes the images from the flat float32 parameters; w_off[i] is the offset of network layer 1 + i.
+cudaError_t fused_prep_launch(const float* params, const int* w_off, int hidden_to_hidden, void* images,
+                              cudaStream_t stream);
 
 template <typename T>
 cudaError_t fused_reduce_launch(const T* grad_cta, double* acc, int P, int ctas, cudaStream_t stream);

@@ -70,6 +70,8 @@ struct FusedArgs {
     T* grad_cta;        // [gridDim.x][P]
     double* loss_cta;   // [gridDim.x]
     int forward_only;
+    const void* weight_images;  // tensor-core variant: pre-split weight images (prep_weights_kernel)
+    int* error;                 // set to 1 when a bounded wait inside the kernel gave up
 };
 
 template <typename T> struct Pack2;

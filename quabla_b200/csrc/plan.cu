@@ -199,6 +199,8 @@ class Plan final : public qb200_plan {
     qb200_status run(bool forward_only);
     qb200_status run_chunk(int si, long long point0, int C, int partial_slot, bool forward_only);
     qb200_status run_fused(int si, bool forward_only);
+    qb200_status prepare_weight_images();
+    qb200_status check_device_error();
     bool choose_fused();
     qb200_status launched(const char* what) {
         ++launches_;
@@ -244,6 +246,9 @@ class Plan final : public qb200_plan {
     T* fused_z_ = nullptr;
     T* fused_h_ = nullptr;
     T* fused_grad_ = nullptr;
+    void* fused_images_ = nullptr;   // tensor-core variant: pre-split weight images
+    int* d_error_ = nullptr;         // device flag set by a bounded wait that gave up
+    bool fused_tensor_core_ = false;
     int64_t launches_ = 0;
     int64_t steps_ = 0;
     bool executed_ = false;
@@ -301,6 +306,8 @@ qb200_status Plan<T>::init() {
     QB_TRY(dev_alloc(&d_ct_, 1));
     QB_TRY(dev_alloc(&d_loss_only_, 1));
     QB_TRY(dev_alloc(&d_clip_, 3));
+    QB_TRY(dev_alloc(&d_error_, 1));
+    QB_CUDA(cudaMemsetAsync(d_error_, 0, sizeof(int), stream_));
     QB_CUDA(cudaMemsetAsync(d_flat_, 0, (1 + n_params_) * sizeof(T), stream_));
     QB_CUDA(cudaMemsetAsync(d_params_, 0, n_params_ * sizeof(T), stream_));
     QB_CUDA(cudaMemsetAsync(d_clip_, 0, 3 * sizeof(double), stream_));
@@ -410,6 +417,12 @@ qb200_status Plan<T>::init() {
         QB_TRY(dev_alloc(&fused_h_, jets));
         QB_TRY(dev_alloc(&fused_grad_, rows * n_params_));
         scratch_bytes_ = (2 * jets + rows * n_params_) * sizeof(T);
+        for (const auto& e : fused_entries_) fused_tensor_core_ = fused_tensor_core_ || e.tensor_core;
+        if (fused_tensor_core_) {
+            unsigned char* raw = nullptr;
+            QB_TRY(dev_alloc(&raw, fused_weight_image_bytes(hidden - 1)));
+            fused_images_ = raw;
+        }
         return QB200_OK;
     }
     H_.assign(L_, nullptr);
@@ -539,6 +552,38 @@ bool Plan<T>::choose_fused() {
 }
 
 template <typename T>
+qb200_status Plan<T>::prepare_weight_images() {
+    return fail(QB200_UNSUPPORTED, "the tensor-core fused engine is float32 only");
+}
+
+template <>
+qb200_status Plan<float>::prepare_weight_images() {
+    const int hidden_to_hidden = L_ - 2;
+    if (hidden_to_hidden < 1) return QB200_OK;
+    int w_off[FUSED_MAX_LAYERS + 1];
+    for (int i = 0; i < hidden_to_hidden; ++i) w_off[i] = (int)leaves_[w_leaf_[1 + i]].offset;
+    cudaError_t e = fused_prep_launch(d_params_, w_off, hidden_to_hidden, fused_images_, stream_);
+    ++launches_;
+    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of prep_weights_kernel failed: %s", cudaGetErrorString(e));
+    return QB200_OK;
+}
+
+// Reads the device flag that a bounded wait sets when it gives up; called after a stream
+// synchronisation.
+template <typename T>
+qb200_status Plan<T>::check_device_error() {
+    int flag = 0;
+    QB_CUDA(cudaMemcpyAsync(&flag, d_error_, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    QB_CUDA(cudaStreamSynchronize(stream_));
+    if (flag != 0) {
+        QB_CUDA(cudaMemsetAsync(d_error_, 0, sizeof(int), stream_));
+        return fail(QB200_CUDA_ERROR, "a staged copy inside the fused kernel did not complete within its wait limit; "
+                                      "the results of that step are invalid");
+    }
+    return QB200_OK;
+}
+
+template <typename T>
 qb200_status Plan<T>::run_fused(int si, bool forward_only) {
     SetState& st = sets_[si];
     const auto& s = desc_.sets[si];
@@ -566,6 +611,8 @@ qb200_status Plan<T>::run_fused(int si, bool forward_only) {
     a.grad_cta = fused_grad_;
     a.loss_cta = d_partials_ + st.partial_offset;
     a.forward_only = forward_only ? 1 : 0;
+    a.weight_images = fused_images_;
+    a.error = d_error_;
     cudaError_t e = fused_launch<T>(fused_entries_[si], fused_grid_[si], stream_, a);
     ++launches_;
     if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of fused_step_kernel failed: %s", cudaGetErrorString(e));
@@ -703,6 +750,7 @@ qb200_status Plan<T>::run(bool forward_only) {
     QB_TRY(check_bound());
     QB_TRY(refresh_tables());
     if (!forward_only) QB_CUDA(cudaMemsetAsync(d_acc_, 0, n_params_ * sizeof(double), stream_));
+    if (fused_ && fused_tensor_core_) QB_TRY(prepare_weight_images());
     LossArgs la;
     la.n_sets = (int)sets_.size();
     for (size_t si = 0; si < sets_.size(); ++si) {
@@ -768,6 +816,7 @@ qb200_status Plan<T>::read_output(int index, void* host, size_t nbytes) {
     if (nbytes != count * sizeof(T)) return fail(QB200_INVALID, "output %d has %zu bytes, got a buffer of %zu", index, count * sizeof(T), nbytes);
     QB_CUDA(cudaMemcpyAsync(host, d_flat_ + offset, nbytes, cudaMemcpyDeviceToHost, stream_));
     QB_CUDA(cudaStreamSynchronize(stream_));
+    if (index == 0 && fused_tensor_core_) QB_TRY(check_device_error());
     return QB200_OK;
 }
 
