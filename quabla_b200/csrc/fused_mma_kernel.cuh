@@ -32,9 +32,20 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
     return r;
 }
 
+// hi = x with the 13 low mantissa bits cleared (a valid tf32), lo = tf32 part of the exact
+// remainder x - hi.  hi + lo reproduces x to 2^-21 relative.
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-    hi = to_tf32(x);
-    lo = to_tf32(x - __uint_as_float(hi));
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;
+}
+
+// Four 8x8 matrices of 16-bit pairs = four 8x4 tiles of 32-bit words: thread (g, t) of the
+// warp receives word t of row g of each tile, which is exactly the m16n8k8 tf32 fragment
+// layout when rows are contiguous in the fragment's k index.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row_ptr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(row_ptr)));
 }
 
 // d += a (16x8, row) * b (8x8, col), tf32 operands, float32 accumulate.
@@ -82,9 +93,10 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // Weight images written by prep_weights_kernel, one per hidden-to-hidden layer:
-// [4][64][LDH] tf32 words = {W hi, W lo, W^T hi, W^T lo}, rows padded to LDH, i.e.
-// exactly the shared-memory layout of the B operand.
-constexpr int WIMG_LDH = 72;
+// [4][64][WIMG_LDH] tf32 words = {forward hi, forward lo, transposed hi, transposed lo}.
+// An image is the B operand stored [n][k] (k contiguous, rows padded), exactly as it sits
+// in shared memory: forward B(k, n) = W[k][n], transposed B(k, n) = W[n][k].
+constexpr int WIMG_LDH = 68;
 constexpr int WIMG_PLANE = 64 * WIMG_LDH;            // words per plane
 constexpr int WIMG_PAIR_BYTES = 2 * WIMG_PLANE * 4;  // hi + lo of one orientation
 
@@ -102,10 +114,10 @@ __global__ void prep_weights_kernel(const float* __restrict__ params, PrepArgs p
         const int k = e >> 6, n = e & 63;
         uint32_t hi, lo;
         split_tf32(w[e], hi, lo);
-        img[0 * WIMG_PLANE + k * WIMG_LDH + n] = hi;
-        img[1 * WIMG_PLANE + k * WIMG_LDH + n] = lo;
-        img[2 * WIMG_PLANE + n * WIMG_LDH + k] = hi;
-        img[3 * WIMG_PLANE + n * WIMG_LDH + k] = lo;
+        img[0 * WIMG_PLANE + n * WIMG_LDH + k] = hi;
+        img[1 * WIMG_PLANE + n * WIMG_LDH + k] = lo;
+        img[2 * WIMG_PLANE + k * WIMG_LDH + n] = hi;
+        img[3 * WIMG_PLANE + k * WIMG_LDH + n] = lo;
     }
 }
 
@@ -116,12 +128,15 @@ struct MmaGeom {
     static constexpr int S = sig::S;
     static constexpr int TP = 32;
     static constexpr int ROWS = S * TP;
-    static constexpr int LDA = 68;  // activations as an A operand: stride = 4 (mod 32), conflict-free fragments
-    static constexpr int LDH = 72;  // operands read k-major (B, transposed A): stride = 8 (mod 32)
+    // Every operand row is 16-byte aligned and its stride is 4 (mod 32) words, so the eight
+    // row addresses of an ldmatrix tile fall into distinct bank groups.
+    static constexpr int LDA = 68;        // activations / cotangents, row-major [row][unit]
+    static constexpr int LDT = ROWS + 4;  // transposed operands of the weight gradient, [unit][row]
     static constexpr int OFF_ACT = 0;                       // [ROWS][LDA]
-    static constexpr int OFF_HR = OFF_ACT + ROWS * LDA;     // [ROWS][LDH]
-    static constexpr int OFF_WB = OFF_HR + ROWS * LDH;      // 2 buffers x {hi, lo} x [64][LDH]
-    static constexpr int OFF_RED = OFF_WB + 4 * W * LDH;    // [5][2][64] column reductions / [4][S][TP] head partials
+    static constexpr int OFF_HT = OFF_ACT + ROWS * LDA;     // [64][LDT] previous layer's jets, transposed
+    static constexpr int OFF_ZT = OFF_HT + W * LDT;         // [64][LDT] pre-activation cotangents, transposed
+    static constexpr int OFF_WB = OFF_ZT + W * LDT;         // 2 buffers x {hi, lo} x [64][WIMG_LDH]
+    static constexpr int OFF_RED = OFF_WB + 4 * WIMG_PLANE; // [5][2][64] column reductions / [4][S][TP] head partials
     static constexpr int RED = (5 * 2 * W > 4 * ROWS) ? 5 * 2 * W : 4 * ROWS;
     static constexpr int OFF_U = OFF_RED + RED;             // [S][TP]
     static constexpr int OFF_UH = OFF_U + ROWS;             // [S][TP]
@@ -132,10 +147,10 @@ struct MmaGeom {
 };
 
 // acc[s][j] += A[rows of stream s][64] * B[64][16 columns of this warp], 3xTF32.
-// A: activations [ROWS][LDA] float32 (split here); B: pre-split weights [64][LDH].
-template <int S, int TP, int LDA, int LDH>
+// A: activations [ROWS][LDA] float32 (split here); B: pre-split weight image [n][k].
+template <int S, int TP, int LDA>
 __device__ __forceinline__ void warp_gemm_3xtf32(const float* __restrict__ A, const uint32_t* __restrict__ Bhi,
-                                                 const uint32_t* __restrict__ Blo, int row0, int col0, int g, int t,
+                                                 const uint32_t* __restrict__ Blo, int row0, int col0, int lane,
                                                  float (&acc)[S][2][4]) {
 #pragma unroll
     for (int s = 0; s < S; ++s)
@@ -143,30 +158,27 @@ __device__ __forceinline__ void warp_gemm_3xtf32(const float* __restrict__ A, co
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[s][j][c] = 0.0f;
+    const int mi = lane >> 3, rr = lane & 7;
+    // A tiles: (rows 0-7, k 0-3), (rows 8-15, k 0-3), (rows 0-7, k 4-7), (rows 8-15, k 4-7).
+    const float* a_lane = A + (row0 + rr + (mi & 1) * 8) * LDA + (mi >> 1) * 4;
+    // B tiles: (n 0-7, k 0-3), (n 0-7, k 4-7), (n 8-15, k 0-3), (n 8-15, k 4-7).
+    const int b_lane = (col0 + (mi >> 1) * 8 + rr) * WIMG_LDH + (mi & 1) * 4;
 #pragma unroll
     for (int kb = 0; kb < 8; ++kb) {
-        uint32_t bhi[2][2], blo[2][2];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int n = col0 + j * 8 + g;
-            bhi[j][0] = Bhi[(kb * 8 + t) * LDH + n];
-            bhi[j][1] = Bhi[(kb * 8 + t + 4) * LDH + n];
-            blo[j][0] = Blo[(kb * 8 + t) * LDH + n];
-            blo[j][1] = Blo[(kb * 8 + t + 4) * LDH + n];
-        }
+        uint32_t bhi[4], blo[4];
+        ldmatrix_x4(bhi, Bhi + b_lane + kb * 8);
+        ldmatrix_x4(blo, Blo + b_lane + kb * 8);
 #pragma unroll
         for (int s = 0; s < S; ++s) {
-            const float* base = A + (s * TP + row0 + g) * LDA + kb * 8 + t;
-            uint32_t ahi[4], alo[4];
-            split_tf32(base[0], ahi[0], alo[0]);
-            split_tf32(base[8 * LDA], ahi[1], alo[1]);
-            split_tf32(base[4], ahi[2], alo[2]);
-            split_tf32(base[8 * LDA + 4], ahi[3], alo[3]);
+            uint32_t raw[4], ahi[4], alo[4];
+            ldmatrix_x4(raw, a_lane + s * TP * LDA + kb * 8);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) split_tf32(__uint_as_float(raw[q]), ahi[q], alo[q]);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                mma_tf32(acc[s][j], alo, bhi[j][0], bhi[j][1]);
-                mma_tf32(acc[s][j], ahi, blo[j][0], blo[j][1]);
-                mma_tf32(acc[s][j], ahi, bhi[j][0], bhi[j][1]);
+                mma_tf32(acc[s][j], alo, bhi[2 * j], bhi[2 * j + 1]);
+                mma_tf32(acc[s][j], ahi, blo[2 * j], blo[2 * j + 1]);
+                mma_tf32(acc[s][j], ahi, bhi[2 * j], bhi[2 * j + 1]);
             }
         }
     }
@@ -208,11 +220,12 @@ template <int CODE>
 __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<float> a) {
     typedef MmaGeom<CODE> G;
     typedef Sig<CODE> SG;
-    constexpr int S = G::S, TP = G::TP, W = G::W, LDA = G::LDA, LDH = G::LDH, ROWS = G::ROWS;
+    constexpr int S = G::S, TP = G::TP, W = G::W, LDA = G::LDA, LDT = G::LDT, ROWS = G::ROWS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* smem = reinterpret_cast<float*>(smem_raw);
     float* act = smem + G::OFF_ACT;
-    float* hr = smem + G::OFF_HR;
+    float* ht = smem + G::OFF_HT;
+    float* zt = smem + G::OFF_ZT;
     uint32_t* wbuf = reinterpret_cast<uint32_t*>(smem + G::OFF_WB);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G::OFF_BAR);
     float* red = smem + G::OFF_RED;
@@ -315,7 +328,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                 mbar_wait(bars + (use & 1), (uint32_t)((use >> 1) & 1), a.error);
                 __syncthreads();  // the previous epilogue's activations are in place
                 QB_PHASE(0);      // wait for the weight image
-                warp_gemm_3xtf32<S, TP, LDA, LDH>(act, whi, whi + WIMG_PLANE, row0, col0, g, t, acc);
+                warp_gemm_3xtf32<S, TP, LDA>(act, whi, whi + WIMG_PLANE, row0, col0, lane, acc);
                 __syncthreads();
                 issue(use + 2);
                 ++use;
@@ -352,14 +365,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     for (int s = 0; s < S; ++s) acc[s][j][c] = v[s];
                 }
             if (backward && l + 1 < L) {
+                // Saved transposed, [unit][stream][point]: the layout the weight gradient reads.
 #pragma unroll
                 for (int s = 0; s < S; ++s)
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
-                        for (int i = 0; i < 2; ++i)
-                            st2(hl + ((size_t)s * TP + row0 + g + 8 * i) * W + col0 + j * 8 + 2 * t, acc[s][j][2 * i],
-                                acc[s][j][2 * i + 1]);
+                        for (int c = 0; c < 4; ++c)
+                            hl[(size_t)unit_of(j, c) * ROWS + s * TP + row0 + g + 8 * (c >> 1)] = acc[s][j][c];
             }
             if (l + 1 < L) {
 #pragma unroll
@@ -453,8 +466,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                 // Prefetch the previous layer's saved jets (weight-gradient operand) while the
                 // transposed jets are computed.
                 const float* hp = sh + (size_t)(l - 1) * G::SCRATCH_PER_CTA;
-                for (int e = tid; e < ROWS * 16; e += FUSED_THREADS)
-                    cp_async16(hr + (e >> 4) * LDH + 4 * (e & 15), hp + (size_t)(e >> 4) * W + 4 * (e & 15));
+                constexpr int CHUNKS = ROWS / 4;  // 16-byte chunks per unit row
+                for (int e = tid; e < W * CHUNKS; e += FUSED_THREADS)
+                    cp_async16(ht + (e / CHUNKS) * LDT + 4 * (e % CHUNKS), hp + (size_t)(e / CHUNKS) * ROWS + 4 * (e % CHUNKS));
                 cp_async_commit();
             }
 #pragma unroll
@@ -529,11 +543,18 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     for (int i = 0; i < 2; ++i)
                         st2(act + (s * TP + row0 + g + 8 * i) * LDA + col0 + j * 8 + 2 * t, acc[s][j][2 * i],
                             acc[s][j][2 * i + 1]);
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) zt[unit_of(j, c) * LDT + s * TP + row0 + g + 8 * (c >> 1)] = acc[s][j][c];
             cp_async_wait_all();
             __syncthreads();
             QB_PHASE(5);  // backward staging
             if (tid < W && a.b_off[l] >= 0) my_grad[a.b_off[l] + tid] += red[tid] + red[W + tid];
-            // Weight gradient: dW[k][n] += sum_rows hr[row][k] * zhat[row][n]; warp: 16 k x 32 n.
+            // Weight gradient: dW[k][n] += sum_rows H[row][k] * Zhat[row][n]; warp: 16 k x 32 n,
+            // both operands read from their transposed copies.
             {
                 const int k0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
                 float dw[4][4];
@@ -545,23 +566,27 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
                         ld2(gw + (k0 + g + 8 * i) * W + n0 + j * 8 + 2 * t, dw[j][2 * i], dw[j][2 * i + 1]);
+                const int mi = lane >> 3, rr = lane & 7;
+                const float* a_lane = ht + (k0 + rr + (mi & 1) * 8) * LDT + (mi >> 1) * 4;
+                const float* b_lane = zt + (n0 + (mi >> 1) * 8 + rr) * LDT + (mi & 1) * 4;
 #pragma unroll 4
                 for (int kb = 0; kb < ROWS / 8; ++kb) {
-                    const float* ha = hr + (kb * 8 + t) * LDH + k0 + g;
-                    uint32_t ahi[4], alo[4];
-                    split_tf32(ha[0], ahi[0], alo[0]);
-                    split_tf32(ha[8], ahi[1], alo[1]);
-                    split_tf32(ha[4 * LDH], ahi[2], alo[2]);
-                    split_tf32(ha[4 * LDH + 8], ahi[3], alo[3]);
+                    uint32_t raw[4], ahi[4], alo[4];
+                    ldmatrix_x4(raw, a_lane + kb * 8);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float* zb = act + (kb * 8 + t) * LDA + n0 + j * 8 + g;
-                        uint32_t bhi0, blo0, bhi1, blo1;
-                        split_tf32(zb[0], bhi0, blo0);
-                        split_tf32(zb[4 * LDA], bhi1, blo1);
-                        mma_tf32(dw[j], alo, bhi0, bhi1);
-                        mma_tf32(dw[j], ahi, blo0, blo1);
-                        mma_tf32(dw[j], ahi, bhi0, bhi1);
+                    for (int q = 0; q < 4; ++q) split_tf32(__uint_as_float(raw[q]), ahi[q], alo[q]);
+#pragma unroll
+                    for (int jj = 0; jj < 2; ++jj) {
+                        uint32_t braw[4], bhi[4], blo[4];
+                        ldmatrix_x4(braw, b_lane + jj * 16 * LDT + kb * 8);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) split_tf32(__uint_as_float(braw[q]), bhi[q], blo[q]);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            mma_tf32(dw[2 * jj + h], alo, bhi[2 * h], bhi[2 * h + 1]);
+                            mma_tf32(dw[2 * jj + h], ahi, blo[2 * h], blo[2 * h + 1]);
+                            mma_tf32(dw[2 * jj + h], ahi, bhi[2 * h], bhi[2 * h + 1]);
+                        }
                     }
                 }
 #pragma unroll
@@ -575,7 +600,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
             {
                 const uint32_t* whi = wbuf + (use & 1) * 2 * WIMG_PLANE;
                 mbar_wait(bars + (use & 1), (uint32_t)((use >> 1) & 1), a.error);
-                warp_gemm_3xtf32<S, TP, LDA, LDH>(act, whi, whi + WIMG_PLANE, row0, col0, g, t, acc);
+                warp_gemm_3xtf32<S, TP, LDA>(act, whi, whi + WIMG_PLANE, row0, col0, lane, acc);
             }
             __syncthreads();
             issue(use + 2);
@@ -591,7 +616,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
     }
 #endif
 
-    double* lred = reinterpret_cast<double*>(hr);
+    double* lred = reinterpret_cast<double*>(ht);
     __syncthreads();
     if (tid < TP) lred[tid] = loss_sum;
     __syncthreads();
