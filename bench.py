@@ -221,6 +221,8 @@ def main() -> None:
     stream = torch.cuda.ExternalStream(plan.query(_lib.Q_STREAM), device=device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # larger than the 126 MB L2
 
+    kernel_ns: list = []  # device time of the interior point set's kernels, one entry per timed step
+
     def barrier():
         if world > 1:
             torch.distributed.barrier()
@@ -238,6 +240,7 @@ def main() -> None:
             step_fn()
             stops[i].record(stream)
             stops[i].synchronize()
+            kernel_ns.append(plan.query(_lib.Q_SET0_NANOSECONDS))
         return sum(a.elapsed_time(b) for a, b in zip(starts, stops))
 
     def device_step():
@@ -288,8 +291,11 @@ def main() -> None:
 
     peaks, peak_kind = measured_peaks()
     dtype_name = "f32" if np.dtype(w.dtype) == np.float32 else "f64"
-    flops = w.flops_per_step  # per GPU
-    achieved_tflops = flops / (ms_per_step * 1e-3) / 1e12
+    # Roofline of the dominant kernel: the kernels of the interior point set (one fused launch on
+    # narrow networks), timed live with CUDA events on the plan's stream inside the timed steps.
+    kernel_s = float(np.mean(kernel_ns)) * 1e-9
+    flops = w.flops_per_point(w.streams) * per_gpu  # algorithmic matmul FLOPs of one launch
+    achieved_tflops = flops / kernel_s / 1e12
     if dtype_name == "f32":
         # 3xTF32 on the tensor pipe: TF32 runs at half the bf16 rate, three passes per product.
         peak_tflops = peaks["bf16_tflops"] / 2.0 / 3.0
@@ -298,21 +304,25 @@ def main() -> None:
         peak_tflops = 40.0
         peak_note = "nominal B200 FP64 (no measured FP64 peak on this pool yet)"
     engine = plan.query(_lib.Q_ENGINE)
+    engine_name = {0: "layerwise", 1: "fused (FP32 pipe)", 2: "fused (tensor cores, 3xTF32 mma)"}[engine]
+    kernel_name = {0: "layer-wise kernels of the interior point set",
+                   1: "fused_step_kernel (interior point set)",
+                   2: "fused_mma_kernel (interior point set)"}[engine]
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
         "config": {"workload": w.name, "description": w.description, "interior_points_per_gpu": per_gpu,
                    "other_sets": w.extra, "optimizer": "adam lr=1e-3", "parameters": w.parameter_count,
-                   "engine": "fused" if engine == 1 else "layerwise",
+                   "engine": engine_name,
                    "l2": "256 MB written between timed steps, outside the per-step event brackets"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s",
                      "frac": achieved_tflops / peak_tflops, "traffic": None,
-                     "kernel": "whole step (all kernels of the step on one stream)",
-                     "flops_per_step": flops, "peak_source": peak_note},
+                     "kernel": kernel_name, "kernel_us": kernel_s * 1e6, "flops_per_launch": flops,
+                     "step_flops": w.flops_per_step, "peak_source": peak_note},
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

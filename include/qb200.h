@@ -85,7 +85,8 @@ typedef enum qb200_query {
     QB200_Q_FLAT_DEVICE_PTR = 6,     /* device address of the flat [loss, gradients...] buffer */
     QB200_Q_SCRATCH_BYTES = 7,       /* bytes of saved-jet scratch the plan holds */
     QB200_Q_STEP_COUNT = 8,          /* optimizer updates applied so far */
-    QB200_Q_ENGINE = 9               /* 0: layer-wise engine, 1: fused narrow-network engine */
+    QB200_Q_ENGINE = 9,              /* 0: layer-wise, 1: fused (FP32 pipe), 2: fused (tensor cores, 3xTF32) */
+    QB200_Q_SET0_NANOSECONDS = 10    /* device time of the last execute's kernels for point set 0 (events) */
 } qb200_query;
 
 /* Opcodes of the per-point residual program (see qb200_desc_set_program). */

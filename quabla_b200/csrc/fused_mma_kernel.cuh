@@ -32,11 +32,12 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
     return r;
 }
 
-// hi = x with the 13 low mantissa bits cleared (a valid tf32), lo = tf32 part of the exact
-// remainder x - hi.  hi + lo reproduces x to 2^-21 relative.
+// hi = x with the 13 low mantissa bits cleared (a valid tf32; the remainder x - hi is exact),
+// lo = that remainder ROUNDED to tf32.  Rounding matters: truncating lo leaves a one-sided
+// error of up to 2^-21 |x| that accumulates linearly over the contraction.
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
     hi = __float_as_uint(x) & 0xffffe000u;
-    lo = __float_as_uint(x - __uint_as_float(hi)) & 0xffffe000u;
+    lo = to_tf32(x - __uint_as_float(hi));
 }
 
 // Four 8x8 matrices of 16-bit pairs = four 8x4 tiles of 32-bit words: thread (g, t) of the
@@ -50,8 +51,9 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* row_pt
 
 // d += a (16x8, row) * b (8x8, col), tf32 operands, float32 accumulate.
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    // Not volatile: the accumulator operands carry the dependencies, the compiler may interleave
+    // independent chains.
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -133,8 +135,9 @@ struct MmaGeom {
     static constexpr int LDA = 68;        // activations / cotangents, row-major [row][unit]
     static constexpr int LDT = ROWS + 4;  // transposed operands of the weight gradient, [unit][row]
     static constexpr int OFF_ACT = 0;                       // [ROWS][LDA]
-    static constexpr int OFF_HT = OFF_ACT + ROWS * LDA;     // [64][LDT] previous layer's jets, transposed
-    static constexpr int OFF_ZT = OFF_HT + W * LDT;         // [64][LDT] pre-activation cotangents, transposed
+    static constexpr int LDH = 72;        // previous layer's jets [row][unit], read k-major: stride 8 (mod 32)
+    static constexpr int OFF_HT = OFF_ACT + ROWS * LDA;     // [ROWS][LDH] previous layer's jets
+    static constexpr int OFF_ZT = OFF_HT + ROWS * LDH;      // [64][LDT] pre-activation cotangents, transposed
     static constexpr int OFF_WB = OFF_ZT + W * LDT;         // 2 buffers x {hi, lo} x [64][WIMG_LDH]
     static constexpr int OFF_RED = OFF_WB + 4 * WIMG_PLANE; // [5][2][64] column reductions / [4][S][TP] head partials
     static constexpr int RED = (5 * 2 * W > 4 * ROWS) ? 5 * 2 * W : 4 * ROWS;
@@ -163,11 +166,15 @@ __device__ __forceinline__ void warp_gemm_3xtf32(const float* __restrict__ A, co
     const float* a_lane = A + (row0 + rr + (mi & 1) * 8) * LDA + (mi >> 1) * 4;
     // B tiles: (n 0-7, k 0-3), (n 0-7, k 4-7), (n 8-15, k 0-3), (n 8-15, k 4-7).
     const int b_lane = (col0 + (mi >> 1) * 8 + rr) * WIMG_LDH + (mi & 1) * 4;
-#pragma unroll
+#pragma unroll 2
     for (int kb = 0; kb < 8; ++kb) {
         uint32_t bhi[4], blo[4];
         ldmatrix_x4(bhi, Bhi + b_lane + kb * 8);
         ldmatrix_x4(blo, Blo + b_lane + kb * 8);
+        // The tensor core adds into its accumulator with truncation, which biases a long chain
+        // (measured: 5e-6 relative on the gradients against 1e-6 with this scheme).  So the three
+        // products of one k-block chain from zero, and the block's partial is added to the running
+        // sum with a round-to-nearest float add.
 #pragma unroll
         for (int s = 0; s < S; ++s) {
             uint32_t raw[4], ahi[4], alo[4];
@@ -176,9 +183,12 @@ __device__ __forceinline__ void warp_gemm_3xtf32(const float* __restrict__ A, co
             for (int q = 0; q < 4; ++q) split_tf32(__uint_as_float(raw[q]), ahi[q], alo[q]);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-                mma_tf32(acc[s][j], alo, bhi[2 * j], bhi[2 * j + 1]);
-                mma_tf32(acc[s][j], ahi, blo[2 * j], blo[2 * j + 1]);
-                mma_tf32(acc[s][j], ahi, bhi[2 * j], bhi[2 * j + 1]);
+                float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                mma_tf32(part, alo, bhi[2 * j], bhi[2 * j + 1]);
+                mma_tf32(part, ahi, blo[2 * j], blo[2 * j + 1]);
+                mma_tf32(part, ahi, bhi[2 * j], bhi[2 * j + 1]);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[s][j][c] += part[c];
             }
         }
     }
@@ -220,7 +230,7 @@ template <int CODE>
 __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<float> a) {
     typedef MmaGeom<CODE> G;
     typedef Sig<CODE> SG;
-    constexpr int S = G::S, TP = G::TP, W = G::W, LDA = G::LDA, LDT = G::LDT, ROWS = G::ROWS;
+    constexpr int S = G::S, TP = G::TP, W = G::W, LDA = G::LDA, LDT = G::LDT, LDH = G::LDH, ROWS = G::ROWS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* smem = reinterpret_cast<float*>(smem_raw);
     float* act = smem + G::OFF_ACT;
@@ -365,14 +375,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     for (int s = 0; s < S; ++s) acc[s][j][c] = v[s];
                 }
             if (backward && l + 1 < L) {
-                // Saved transposed, [unit][stream][point]: the layout the weight gradient reads.
 #pragma unroll
                 for (int s = 0; s < S; ++s)
 #pragma unroll
                     for (int j = 0; j < 2; ++j)
 #pragma unroll
-                        for (int c = 0; c < 4; ++c)
-                            hl[(size_t)unit_of(j, c) * ROWS + s * TP + row0 + g + 8 * (c >> 1)] = acc[s][j][c];
+                        for (int i = 0; i < 2; ++i)
+                            st2(hl + ((size_t)s * TP + row0 + g + 8 * i) * W + col0 + j * 8 + 2 * t, acc[s][j][2 * i],
+                                acc[s][j][2 * i + 1]);
             }
             if (l + 1 < L) {
 #pragma unroll
@@ -466,9 +476,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                 // Prefetch the previous layer's saved jets (weight-gradient operand) while the
                 // transposed jets are computed.
                 const float* hp = sh + (size_t)(l - 1) * G::SCRATCH_PER_CTA;
-                constexpr int CHUNKS = ROWS / 4;  // 16-byte chunks per unit row
-                for (int e = tid; e < W * CHUNKS; e += FUSED_THREADS)
-                    cp_async16(ht + (e / CHUNKS) * LDT + 4 * (e % CHUNKS), hp + (size_t)(e / CHUNKS) * ROWS + 4 * (e % CHUNKS));
+                for (int e = tid; e < ROWS * 16; e += FUSED_THREADS)
+                    cp_async16(ht + (e >> 4) * LDH + 4 * (e & 15), hp + (size_t)(e >> 4) * W + 4 * (e & 15));
                 cp_async_commit();
             }
 #pragma unroll
@@ -554,27 +563,29 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
             QB_PHASE(5);  // backward staging
             if (tid < W && a.b_off[l] >= 0) my_grad[a.b_off[l] + tid] += red[tid] + red[W + tid];
             // Weight gradient: dW[k][n] += sum_rows H[row][k] * Zhat[row][n]; warp: 16 k x 32 n,
-            // both operands read from their transposed copies.
+            // the cotangents read from their transposed copy.
             {
                 const int k0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
-                float dw[4][4];
                 float* gw = my_grad + a.w_off[l];
-                // Start from the running per-CTA sums (loaded before the loop, so the latency
-                // of the read-modify-write hides behind the contraction).
+                // Starts from the running per-CTA sums, loaded before the loop so that the latency of
+                // the read-modify-write hides behind the contraction.
+                float dw[4][4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
                         ld2(gw + (k0 + g + 8 * i) * W + n0 + j * 8 + 2 * t, dw[j][2 * i], dw[j][2 * i + 1]);
                 const int mi = lane >> 3, rr = lane & 7;
-                const float* a_lane = ht + (k0 + rr + (mi & 1) * 8) * LDT + (mi >> 1) * 4;
                 const float* b_lane = zt + (n0 + (mi >> 1) * 8 + rr) * LDT + (mi & 1) * 4;
-#pragma unroll 4
+#pragma unroll 2
                 for (int kb = 0; kb < ROWS / 8; ++kb) {
-                    uint32_t raw[4], ahi[4], alo[4];
-                    ldmatrix_x4(raw, a_lane + kb * 8);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) split_tf32(__uint_as_float(raw[q]), ahi[q], alo[q]);
+                    // A(m = unit, k = row) from the row-major jets: element (g, t) = H[kb*8 + t][k0 + g].
+                    const float* ha = ht + (kb * 8 + t) * LDH + k0 + g;
+                    uint32_t ahi[4], alo[4];
+                    split_tf32(ha[0], ahi[0], alo[0]);
+                    split_tf32(ha[8], ahi[1], alo[1]);
+                    split_tf32(ha[4 * LDH], ahi[2], alo[2]);
+                    split_tf32(ha[4 * LDH + 8], ahi[3], alo[3]);
 #pragma unroll
                     for (int jj = 0; jj < 2; ++jj) {
                         uint32_t braw[4], bhi[4], blo[4];
@@ -583,9 +594,12 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                         for (int q = 0; q < 4; ++q) split_tf32(__uint_as_float(braw[q]), bhi[q], blo[q]);
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            mma_tf32(dw[2 * jj + h], alo, bhi[2 * h], bhi[2 * h + 1]);
-                            mma_tf32(dw[2 * jj + h], ahi, blo[2 * h], blo[2 * h + 1]);
-                            mma_tf32(dw[2 * jj + h], ahi, bhi[2 * h], bhi[2 * h + 1]);
+                            float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            mma_tf32(part, alo, bhi[2 * h], bhi[2 * h + 1]);
+                            mma_tf32(part, ahi, blo[2 * h], blo[2 * h + 1]);
+                            mma_tf32(part, ahi, bhi[2 * h], bhi[2 * h + 1]);
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) dw[2 * jj + h][c] += part[c];
                         }
                     }
                 }

@@ -249,6 +249,8 @@ class Plan final : public qb200_plan {
     void* fused_images_ = nullptr;   // tensor-core variant: pre-split weight images
     int* d_error_ = nullptr;         // device flag set by a bounded wait that gave up
     bool fused_tensor_core_ = false;
+    cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;  // around the kernels of point set 0
+    bool ev_valid_ = false;
     int64_t launches_ = 0;
     int64_t steps_ = 0;
     bool executed_ = false;
@@ -271,6 +273,9 @@ void Plan<T>::release() {
     if (stream_ != nullptr) cudaStreamSynchronize(stream_);
     for (void* p : buffers_) cudaFree(p);
     buffers_.clear();
+    if (ev_begin_ != nullptr) cudaEventDestroy(ev_begin_);
+    if (ev_end_ != nullptr) cudaEventDestroy(ev_end_);
+    ev_begin_ = ev_end_ = nullptr;
     if (stream_ != nullptr) cudaStreamDestroy(stream_);
     stream_ = nullptr;
 }
@@ -283,6 +288,8 @@ qb200_status Plan<T>::init() {
     if (device_ < 0 || device_ >= count) return fail(QB200_INVALID, "device ordinal %d of %d", device_, count);
     QB_TRY(use_device());
     QB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+    QB_CUDA(cudaEventCreate(&ev_begin_));
+    QB_CUDA(cudaEventCreate(&ev_end_));
 
     L_ = (int)desc_.sizes.size() - 1;
     w_leaf_.assign(L_, -1);
@@ -757,8 +764,13 @@ qb200_status Plan<T>::run(bool forward_only) {
         SetState& st = sets_[si];
         const long long n = desc_.sets[si].n;
         int slot = st.partial_offset;
+        if (si == 0 && !forward_only) QB_CUDA(cudaEventRecord(ev_begin_, stream_));
         if (fused_) {
             QB_TRY(run_fused((int)si, forward_only));
+            if (si == 0 && !forward_only) {
+                QB_CUDA(cudaEventRecord(ev_end_, stream_));
+                ev_valid_ = true;
+            }
             la.offset[si] = st.partial_offset;
             la.count[si] = fused_grid_[si];
             la.weight[si] = desc_.sets[si].weight;
@@ -768,6 +780,10 @@ qb200_status Plan<T>::run(bool forward_only) {
             const int C = (int)std::min<long long>(st.chunk, n - p0);
             QB_TRY(run_chunk((int)si, p0, C, slot, forward_only));
             slot += (C + 255) / 256;
+        }
+        if (si == 0 && !forward_only) {
+            QB_CUDA(cudaEventRecord(ev_end_, stream_));
+            ev_valid_ = true;
         }
         la.offset[si] = st.partial_offset;
         la.count[si] = slot - st.partial_offset;
@@ -952,7 +968,16 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
         case QB200_Q_FLAT_DEVICE_PTR: *out = (int64_t)(intptr_t)d_flat_; return QB200_OK;
         case QB200_Q_SCRATCH_BYTES: *out = (int64_t)scratch_bytes_; return QB200_OK;
         case QB200_Q_STEP_COUNT: *out = steps_; return QB200_OK;
-        case QB200_Q_ENGINE: *out = fused_ ? 1 : 0; return QB200_OK;
+        case QB200_Q_ENGINE: *out = fused_ ? (fused_tensor_core_ ? 2 : 1) : 0; return QB200_OK;
+        case QB200_Q_SET0_NANOSECONDS: {
+            if (!ev_valid_) return fail(QB200_INVALID, "no execute has run yet");
+            QB_TRY(use_device());
+            QB_CUDA(cudaEventSynchronize(ev_end_));
+            float ms = 0.0f;
+            QB_CUDA(cudaEventElapsedTime(&ms, ev_begin_, ev_end_));
+            *out = (int64_t)(ms * 1e6);
+            return QB200_OK;
+        }
         default: return fail(QB200_INVALID, "unknown query key %d", key);
     }
 }
