@@ -270,6 +270,16 @@ qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void
                                    int32_t d_in, int32_t d_out, void* d_grad, void* cuda_stream);
 
 /* ------------------------------------------------------------------------
+ * Stand-alone float32 matrix product on the tensor cores (tcgen05, 3xTF32 split):
+ *   C[M][N] = A[M][K] * W[K][N]  (+ bias[N] on the first bias_rows rows),
+ * the layer contraction h @ W (+ b) of the hot path (a1/a2: tensor_ir.rs:4968-4972,
+ * op/batch.rs:58-79) for all streams at once.  N % 16 == 0, 16 <= N <= 256,
+ * K % 32 == 0, all arrays row-major float32 on the device.  Synchronises the stream.
+ * ------------------------------------------------------------------------ */
+qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d_bias, void* d_c, int64_t M,
+                                 int32_t N, int32_t K, int64_t bias_rows, void* cuda_stream);
+
+/* ------------------------------------------------------------------------
  * qb200_weight_gradient for callers that cannot allocate device memory.
  * No counterpart in the reference: its backend allocates freely from a pool.
  *

@@ -14,7 +14,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIBRARY = os.path.join(_HERE, "libqb200.so")
-SOURCES = ["api.cu", "plan.cu", "static_scratch.cu", "fused.cu"]
+SOURCES = ["api.cu", "plan.cu", "static_scratch.cu", "fused.cu", "tc_gemm.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

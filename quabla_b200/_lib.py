@@ -100,6 +100,7 @@ SIGNATURES = {
     "qb200_optimizer_apply": (_I32, [_I32, _P, _P, _P, _P, _I64, C.POINTER(OptConfig), _I64, _P]),
     "qb200_weight_gradient": (_I32, [_I32, _P, _P, _I64, _I32, _I32, _P, _P]),
     "qb200_weight_gradient_static": (_I32, [_I32, _P, _P, _I64, _I32, _I32, _P, _P]),
+    "qb200_matmul_3xtf32": (_I32, [_P, _P, _P, _P, _I64, _I32, _I32, _I64, _P]),
 }
 
 _library = None

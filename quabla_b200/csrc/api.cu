@@ -12,6 +12,7 @@
 
 #include "layer_kernels.cuh"
 #include "plan.h"
+#include "tc_gemm.h"
 #include "point_kernels.cuh"
 
 namespace qb {
@@ -530,6 +531,30 @@ qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void
     if (dtype == QB200_F32) return weight_gradient_typed<float>(d_acts, d_cots, rows, d_in, d_out, d_grad, s);
     if (dtype == QB200_F64) return weight_gradient_typed<double>(d_acts, d_cots, rows, d_in, d_out, d_grad, s);
     return fail(QB200_INVALID, "unknown dtype %d", dtype);
+}
+
+qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d_bias, void* d_c, int64_t M,
+                                 int32_t N, int32_t K, int64_t bias_rows, void* cuda_stream) {
+    if (d_a == nullptr || d_w == nullptr || d_c == nullptr) return fail(QB200_INVALID, "matmul_3xtf32 needs A, W and C");
+    if (M < 1 || M > (int64_t)1 << 30) return fail(QB200_INVALID, "matmul_3xtf32: M = %lld out of range", (long long)M);
+    if (!qb::tc_rows_ok(N, K))
+        return fail(QB200_UNSUPPORTED, "matmul_3xtf32 needs N %% 16 == 0, 16 <= N <= 256 and K %% 32 == 0; got N = %d, K = %d", N, K);
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    uint32_t* image = nullptr;
+    QB_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&image), (qb::tc_image_words(K, N) + 4) * sizeof(uint32_t), s));
+    int* flag = reinterpret_cast<int*>(image + qb::tc_image_words(K, N));
+    QB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), s));
+    cudaError_t e = qb::tc_prep_launch(static_cast<const float*>(d_w), K, N, image, s);
+    if (e == cudaSuccess)
+        e = qb::tc_rows_launch(static_cast<const float*>(d_a), K, image, false, K, N, static_cast<float*>(d_c), N,
+                               static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, flag, s);
+    int host_flag = 0;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&host_flag, flag, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFreeAsync(image, s);
+    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "matmul_3xtf32 failed: %s", cudaGetErrorString(e));
+    if (host_flag != 0) return fail(QB200_CUDA_ERROR, "matmul_3xtf32: a bounded wait inside the kernel gave up");
+    return QB200_OK;
 }
 
 }  // extern "C"

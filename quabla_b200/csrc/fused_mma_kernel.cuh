@@ -107,7 +107,7 @@ struct PrepArgs {
     int w_off[FUSED_MAX_LAYERS + 1];  // parameter offset of network layer 1 + i
 };
 
-__global__ void prep_weights_kernel(const float* __restrict__ params, PrepArgs p, uint32_t* __restrict__ images) {
+static __global__ void prep_weights_kernel(const float* __restrict__ params, PrepArgs p, uint32_t* __restrict__ images) {
     const int layer = blockIdx.y;  // hidden-to-hidden layer index 0..layers-1 (network layer index - 1)
     if (layer >= p.layers) return;
     const float* w = params + p.w_off[layer];
