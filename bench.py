@@ -304,10 +304,12 @@ def main() -> None:
         peak_tflops = 40.0
         peak_note = "nominal B200 FP64 (no measured FP64 peak on this pool yet)"
     engine = plan.query(_lib.Q_ENGINE)
-    engine_name = {0: "layerwise", 1: "fused (FP32 pipe)", 2: "fused (tensor cores, 3xTF32 mma)"}[engine]
+    engine_name = {0: "layerwise", 1: "fused (FP32 pipe)", 2: "fused (tensor cores, 3xTF32 mma)",
+                   3: "layerwise (tcgen05 3xTF32 GEMMs)"}[engine]
     kernel_name = {0: "layer-wise kernels of the interior point set",
                    1: "fused_step_kernel (interior point set)",
-                   2: "fused_mma_kernel (interior point set)"}[engine]
+                   2: "fused_mma_kernel (interior point set)",
+                   3: "layer-wise kernels of the interior point set (tcgen05 GEMMs)"}[engine]
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",

@@ -85,7 +85,7 @@ typedef enum qb200_query {
     QB200_Q_FLAT_DEVICE_PTR = 6,     /* device address of the flat [loss, gradients...] buffer */
     QB200_Q_SCRATCH_BYTES = 7,       /* bytes of saved-jet scratch the plan holds */
     QB200_Q_STEP_COUNT = 8,          /* optimizer updates applied so far */
-    QB200_Q_ENGINE = 9,              /* 0: layer-wise, 1: fused (FP32 pipe), 2: fused (tensor cores, 3xTF32) */
+    QB200_Q_ENGINE = 9,              /* 0: layer-wise (FP pipe), 1: fused (FP32 pipe), 2: fused (mma 3xTF32), 3: layer-wise with tcgen05 GEMMs */
     QB200_Q_SET0_NANOSECONDS = 10    /* device time of the last execute's kernels for point set 0 (events) */
 } qb200_query;
 
@@ -273,7 +273,7 @@ qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void
  * Stand-alone float32 matrix product on the tensor cores (tcgen05, 3xTF32 split):
  *   C[M][N] = A[M][K] * W[K][N]  (+ bias[N] on the first bias_rows rows),
  * the layer contraction h @ W (+ b) of the hot path (a1/a2: tensor_ir.rs:4968-4972,
- * op/batch.rs:58-79) for all streams at once.  N % 16 == 0, 16 <= N <= 256,
+ * op/batch.rs:58-79) for all streams at once.  N % 64 == 0, 64 <= N <= 256,
  * K % 32 == 0, all arrays row-major float32 on the device.  Synchronises the stream.
  * ------------------------------------------------------------------------ */
 qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d_bias, void* d_c, int64_t M,

@@ -9,6 +9,7 @@
 #include <memory>
 #include <mutex>
 #include <set>
+#include <type_traits>
 
 #include "layer_kernels.cuh"
 #include "plan.h"
@@ -159,7 +160,23 @@ static qb200_status weight_gradient_typed(const void* acts, const void* cots, in
     const int slices = (int)((rows + qb::WGRAD_ROWS_PER_SLICE - 1) / qb::WGRAD_ROWS_PER_SLICE);
     const size_t count = (size_t)d_in * d_out;
     void* scratch = nullptr;
-    QB_CUDA(cudaMallocAsync(&scratch, (size_t)slices * count * sizeof(T), stream));
+    QB_CUDA(cudaMallocAsync(&scratch, ((size_t)slices * count + 4) * sizeof(T), stream));
+    if (std::is_same<T, float>::value && qb::tc_enabled() && qb::tc_wgrad_ok(d_in, d_out)) {
+        // Tensor-core contraction (tcgen05, 3xTF32); same slices, same reduction.
+        int* flag = reinterpret_cast<int*>(static_cast<float*>(scratch) + (size_t)slices * count);
+        cudaMemsetAsync(flag, 0, sizeof(int), stream);
+        cudaError_t e = qb::tc_wgrad_launch(static_cast<const float*>(acts), d_in, static_cast<const float*>(cots),
+                                            d_out, static_cast<float*>(scratch), (int)rows, d_in, d_out,
+                                            qb::WGRAD_ROWS_PER_SLICE, flag, stream);
+        if (e == cudaSuccess) {
+            qb::reduce_partials_kernel<T><<<((int)count + 255) / 256, 256, 0, stream>>>(
+                static_cast<const T*>(scratch), static_cast<T*>(grad), (int)count, slices);
+            e = cudaGetLastError();
+        }
+        cudaFreeAsync(scratch, stream);
+        if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "weight gradient launch failed: %s", cudaGetErrorString(e));
+        return QB200_OK;
+    }
     qb::GemmArgs<T> g;
     g.A = static_cast<const T*>(acts);
     g.B = static_cast<const T*>(cots);
@@ -538,7 +555,7 @@ qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d
     if (d_a == nullptr || d_w == nullptr || d_c == nullptr) return fail(QB200_INVALID, "matmul_3xtf32 needs A, W and C");
     if (M < 1 || M > (int64_t)1 << 30) return fail(QB200_INVALID, "matmul_3xtf32: M = %lld out of range", (long long)M);
     if (!qb::tc_rows_ok(N, K))
-        return fail(QB200_UNSUPPORTED, "matmul_3xtf32 needs N %% 16 == 0, 16 <= N <= 256 and K %% 32 == 0; got N = %d, K = %d", N, K);
+        return fail(QB200_UNSUPPORTED, "matmul_3xtf32 needs N %% 64 == 0, 64 <= N <= 256 and K %% 32 == 0; got N = %d, K = %d", N, K);
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     uint32_t* image = nullptr;
     QB_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&image), (qb::tc_image_words(K, N) + 4) * sizeof(uint32_t), s));

@@ -10,6 +10,7 @@
 #include "fused_kernel.cuh"
 #include "layer_kernels.cuh"
 #include "point_kernels.cuh"
+#include "tc_gemm.h"
 
 namespace qb {
 
@@ -200,6 +201,12 @@ class Plan final : public qb200_plan {
     qb200_status run_chunk(int si, long long point0, int C, int partial_slot, bool forward_only);
     qb200_status run_fused(int si, bool forward_only);
     qb200_status prepare_weight_images();
+    qb200_status tc_setup();
+    qb200_status tc_prepare();
+    // Each returns true when the tensor-core path took the launch.
+    bool tc_forward(int layer, const T* A, T* C, long long rows, int bias_rows, qb200_status* st);
+    bool tc_dgrad(int layer, const T* G, T* Gprev, long long rows, qb200_status* st);
+    bool tc_wgrad(int layer, const T* H, const T* G, long long rows, qb200_status* st);
     qb200_status check_device_error();
     bool choose_fused();
     qb200_status launched(const char* what) {
@@ -249,6 +256,10 @@ class Plan final : public qb200_plan {
     void* fused_images_ = nullptr;   // tensor-core variant: pre-split weight images
     int* d_error_ = nullptr;         // device flag set by a bounded wait that gave up
     bool fused_tensor_core_ = false;
+    // layer-wise engine, float32: tcgen05 GEMMs for the layers whose shapes allow it
+    std::vector<uint32_t*> tc_image_;   // per layer: pre-split weight images (null: not eligible)
+    std::vector<char> tc_fwd_, tc_bwd_, tc_wgrad_;
+    bool tc_any_ = false;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;  // around the kernels of point set 0
     bool ev_valid_ = false;
     int64_t launches_ = 0;
@@ -443,6 +454,7 @@ qb200_status Plan<T>::init() {
             scratch_bytes_ += z_elems[l] * sizeof(T);
         }
     }
+    QB_TRY(tc_setup());
     QB_TRY(dev_alloc(&G_[0], g_elems));
     QB_TRY(dev_alloc(&G_[1], g_elems));
     QB_TRY(dev_alloc(&U_, max_rows));
@@ -631,6 +643,72 @@ qb200_status Plan<T>::run_fused(int si, bool forward_only) {
     return QB200_OK;
 }
 
+// ---- tcgen05 GEMMs in the layer-wise engine (float32 plans only) -----------------------
+template <typename T> qb200_status Plan<T>::tc_setup() { return QB200_OK; }
+template <typename T> qb200_status Plan<T>::tc_prepare() { return QB200_OK; }
+template <typename T> bool Plan<T>::tc_forward(int, const T*, T*, long long, int, qb200_status*) { return false; }
+template <typename T> bool Plan<T>::tc_dgrad(int, const T*, T*, long long, qb200_status*) { return false; }
+template <typename T> bool Plan<T>::tc_wgrad(int, const T*, const T*, long long, qb200_status*) { return false; }
+
+template <>
+qb200_status Plan<float>::tc_setup() {
+    tc_image_.assign(L_, nullptr);
+    tc_fwd_.assign(L_, 0);
+    tc_bwd_.assign(L_, 0);
+    tc_wgrad_.assign(L_, 0);
+    if (!tc_enabled()) return QB200_OK;
+    for (int l = 0; l < L_; ++l) {
+        const int K = desc_.sizes[l], N = desc_.sizes[l + 1];
+        tc_fwd_[l] = tc_rows_ok(N, K);
+        tc_bwd_[l] = l > 0 && tc_rows_ok(K, N);
+        tc_wgrad_[l] = tc_wgrad_ok(K, N);
+        if (tc_fwd_[l] || tc_bwd_[l]) QB_TRY(dev_alloc(&tc_image_[l], tc_image_words(K, N)));
+        tc_any_ = tc_any_ || tc_fwd_[l] || tc_bwd_[l] || tc_wgrad_[l];
+    }
+    return QB200_OK;
+}
+
+template <>
+qb200_status Plan<float>::tc_prepare() {
+    for (int l = 0; l < L_; ++l) {
+        if (tc_image_[l] == nullptr) continue;
+        cudaError_t e = tc_prep_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], tc_image_[l], stream_);
+        ++launches_;
+        if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of tc_prep_weight_kernel failed: %s", cudaGetErrorString(e));
+    }
+    return QB200_OK;
+}
+
+template <>
+bool Plan<float>::tc_forward(int layer, const float* A, float* C, long long rows, int bias_rows, qb200_status* st) {
+    if (!tc_fwd_[layer]) return false;
+    const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
+    cudaError_t e = tc_rows_launch(A, K, tc_image_[layer], false, K, N, C, N, bias(layer), bias_rows, (int)rows, d_error_, stream_);
+    ++launches_;
+    *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(forward) failed: %s", cudaGetErrorString(e));
+    return true;
+}
+
+template <>
+bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long rows, qb200_status* st) {
+    if (!tc_bwd_[layer]) return false;
+    const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
+    cudaError_t e = tc_rows_launch(G, N, tc_image_[layer], true, K, N, Gprev, K, nullptr, 0, (int)rows, d_error_, stream_);
+    ++launches_;
+    *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(dgrad) failed: %s", cudaGetErrorString(e));
+    return true;
+}
+
+template <>
+bool Plan<float>::tc_wgrad(int layer, const float* H, const float* G, long long rows, qb200_status* st) {
+    if (layer < 0 || layer >= L_ || !tc_wgrad_[layer]) return false;
+    const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
+    cudaError_t e = tc_wgrad_launch(H, K, G, N, wpartial_, (int)rows, K, N, K_CHUNK_ROWS, d_error_, stream_);
+    ++launches_;
+    *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(wgrad) failed: %s", cudaGetErrorString(e));
+    return true;
+}
+
 template <typename T>
 qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slot, bool forward_only) {
     SetState& st = sets_[si];
@@ -660,9 +738,14 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         g.ldc = sz[l];
         g.bias_rows = C;
         g.k_chunk = g.K;
-        dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
-        gemm_kernel<T, true, true><<<grid, 256, 0, stream_>>>(g);
-        QB_TRY(launched("gemm_kernel(forward)"));
+        qb200_status tc_status = QB200_OK;
+        if (tc_forward(l - 1, H_[l - 1], Z_[l], rows, C, &tc_status)) {
+            QB_TRY(tc_status);
+        } else {
+            dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
+            gemm_kernel<T, true, true><<<grid, 256, 0, stream_>>>(g);
+            QB_TRY(launched("gemm_kernel(forward)"));
+        }
         const long long plane = (long long)C * sz[l];
         jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec);
         QB_TRY(launched("jet_forward_kernel"));
@@ -677,7 +760,18 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     QB_TRY(launched("residual_kernel"));
     if (forward_only) return QB200_OK;
 
-    auto wgrad = [&](const T* Hprev, const T* Gz, int d_in, int d_out, int leaf) -> qb200_status {
+    auto wgrad = [&](const T* Hprev, const T* Gz, int d_in, int d_out, int leaf, int layer) -> qb200_status {
+        {
+            qb200_status tc_status = QB200_OK;
+            if (tc_wgrad(layer, Hprev, Gz, rows, &tc_status)) {
+                QB_TRY(tc_status);
+                const int count = d_in * d_out;
+                const int slices = (int)((rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS);
+                accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(
+                    wpartial_, d_acc_ + leaves_[leaf].offset, count, slices);
+                return launched("accumulate_partials_kernel");
+            }
+        }
         GemmArgs<T> g;
         g.A = Hprev;
         g.B = Gz;
@@ -714,7 +808,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     };
 
     // Head: dW = H^T Uhat, db = sum of the primal cotangents, G = Uhat (x) w.
-    QB_TRY(wgrad(H_[head], Uhat_, sz[head], 1, w_leaf_[head]));
+    QB_TRY(wgrad(H_[head], Uhat_, sz[head], 1, w_leaf_[head], head));
     QB_TRY(bgrad(Uhat_, 1, b_leaf_[head]));
     int cur = 0;
     head_backward_kernel<T><<<grid_for(rows * sz[head], 256), 256, 0, stream_>>>(Uhat_, weight(head), G_[cur], rows,
@@ -724,7 +818,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         const long long plane = (long long)C * sz[l];
         jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec);
         QB_TRY(launched("jet_backward_kernel"));
-        QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1]));
+        QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1], l - 1));
         QB_TRY(bgrad(G_[cur], sz[l], b_leaf_[l - 1]));
         if (l > 1) {
             GemmArgs<T> g;
@@ -742,9 +836,14 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             g.ldc = sz[l - 1];
             g.bias_rows = 0;
             g.k_chunk = g.K;
-            dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
-            gemm_kernel<T, true, false><<<grid, 256, 0, stream_>>>(g);
-            QB_TRY(launched("gemm_kernel(dgrad)"));
+            qb200_status tc_status = QB200_OK;
+            if (tc_dgrad(l - 1, G_[cur], G_[cur ^ 1], rows, &tc_status)) {
+                QB_TRY(tc_status);
+            } else {
+                dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
+                gemm_kernel<T, true, false><<<grid, 256, 0, stream_>>>(g);
+                QB_TRY(launched("gemm_kernel(dgrad)"));
+            }
             cur ^= 1;
         }
     }
@@ -758,6 +857,7 @@ qb200_status Plan<T>::run(bool forward_only) {
     QB_TRY(refresh_tables());
     if (!forward_only) QB_CUDA(cudaMemsetAsync(d_acc_, 0, n_params_ * sizeof(double), stream_));
     if (fused_ && fused_tensor_core_) QB_TRY(prepare_weight_images());
+    if (!fused_ && tc_any_) QB_TRY(tc_prepare());
     LossArgs la;
     la.n_sets = (int)sets_.size();
     for (size_t si = 0; si < sets_.size(); ++si) {
@@ -832,7 +932,7 @@ qb200_status Plan<T>::read_output(int index, void* host, size_t nbytes) {
     if (nbytes != count * sizeof(T)) return fail(QB200_INVALID, "output %d has %zu bytes, got a buffer of %zu", index, count * sizeof(T), nbytes);
     QB_CUDA(cudaMemcpyAsync(host, d_flat_ + offset, nbytes, cudaMemcpyDeviceToHost, stream_));
     QB_CUDA(cudaStreamSynchronize(stream_));
-    if (index == 0 && fused_tensor_core_) QB_TRY(check_device_error());
+    if (index == 0 && (fused_tensor_core_ || tc_any_)) QB_TRY(check_device_error());
     return QB200_OK;
 }
 
@@ -968,7 +1068,7 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
         case QB200_Q_FLAT_DEVICE_PTR: *out = (int64_t)(intptr_t)d_flat_; return QB200_OK;
         case QB200_Q_SCRATCH_BYTES: *out = (int64_t)scratch_bytes_; return QB200_OK;
         case QB200_Q_STEP_COUNT: *out = steps_; return QB200_OK;
-        case QB200_Q_ENGINE: *out = fused_ ? (fused_tensor_core_ ? 2 : 1) : 0; return QB200_OK;
+        case QB200_Q_ENGINE: *out = fused_ ? (fused_tensor_core_ ? 2 : 1) : (tc_any_ ? 3 : 0); return QB200_OK;
         case QB200_Q_SET0_NANOSECONDS: {
             if (!ev_valid_) return fail(QB200_INVALID, "no execute has run yet");
             QB_TRY(use_device());

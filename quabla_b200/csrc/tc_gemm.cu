@@ -13,9 +13,9 @@ bool tc_enabled() {
     return !(env != nullptr && strcmp(env, "0") == 0);
 }
 
-bool tc_rows_ok(int N, int K) { return N % 16 == 0 && N >= 16 && N <= 256 && K % TC_BK == 0 && K >= TC_BK; }
+bool tc_rows_ok(int N, int K) { return N % 64 == 0 && N >= 64 && N <= 256 && K % TC_BK == 0 && K >= TC_BK; }
 
-bool tc_wgrad_ok(int Mw, int N) { return Mw % TC_BM == 0 && N % 16 == 0 && N >= 16 && N <= 256; }
+bool tc_wgrad_ok(int Mw, int N) { return Mw % TC_BM == 0 && N % 64 == 0 && N >= 64 && N <= 256; }
 
 size_t tc_image_words(int K, int N) { return (size_t)4 * K * N; }
 

@@ -9,7 +9,7 @@
 // (crates/quabla-core/src/tensor_ir/cuda.rs:4936-5035) and as a materialised
 // [B, in, out] product for every weight gradient (op/vjp.rs:176-209).
 //
-// Shapes.  A CTA of 128 threads computes a 128 x N tile (N <= 256, N % 16 == 0)
+// Shapes.  A CTA of 256 threads computes a 128 x N tile (N <= 256, N % 64 == 0)
 // over K in steps of 32:
 //   ROWS  C[m][n] = sum_k A[m][k] * Bimg[n][k] (+ bias[n] on the first bias_rows rows)
 //         A float32 row-major (split in registers on the way to shared memory),
@@ -31,7 +31,7 @@ namespace qb {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 32;
-constexpr int TC_THREADS = 128;
+constexpr int TC_THREADS = 256;
 constexpr int TC_CHUNKS = TC_BK / 4;  // 16-byte chunks per row of a k-step
 
 struct TcGemmArgs {
@@ -110,19 +110,28 @@ __device__ __forceinline__ void tc_store_split4(unsigned char* hi, unsigned char
     *reinterpret_cast<uint4*>(lo + offset) = make_uint4(l[0], l[1], l[2], l[3]);
 }
 
-// Dynamic shared memory: 2 stages x {A hi, A lo, B hi, B lo}, then 3 mbarriers and the TMEM address.
+// Dynamic shared memory: 2 stages x {A hi, A lo, B hi, B lo}, then 2 mbarriers and the TMEM address.
+//
+// Accuracy.  The tensor core adds into its accumulator with truncation; a chain of K/8 * 3
+// instructions on one accumulator biases the result by several 1e-6 relative, which the
+// derivative streams amplify.  So every k-tile (32 k = 12 instructions) accumulates from zero
+// into one of two tensor-memory buffers, and the threads drain that partial into float32
+// registers with round-to-nearest adds while the next k-tile's instructions run.
+// Thread (half, row): rows = accumulator lanes, half selects N/2 of the columns.
 template <bool WGRAD>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_gemm_kernel(TcGemmArgs a) {
     extern __shared__ __align__(128) unsigned char tc_smem[];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int N = a.N;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int half = tid >> 7, trow = tid & 127;
+    const int N = a.N, NH = N >> 1;  // N % 64 == 0: NH is a multiple of 32
     const int a_bytes = TC_BM * TC_BK * 4, b_bytes = N * TC_BK * 4;
     const int stage_bytes = 2 * a_bytes + 2 * b_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tc_smem + 2 * stage_bytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
 
-    int tmem_cols = 32;
-    while (tmem_cols < N) tmem_cols <<= 1;
+    int buf_cols = 64;
+    while (buf_cols < N) buf_cols <<= 1;
+    const int tmem_cols = 2 * buf_cols;
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -137,6 +146,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_gemm_kernel(TcGemmArgs a) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t idesc = tc_idesc(N);
+    // This thread's window of an accumulator buffer: its lane quarter, its half of the columns.
+    const uint32_t my_tmem = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * NH);
 
     int m0, k_begin, k_end;
     if (WGRAD) {
@@ -150,13 +161,33 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_gemm_kernel(TcGemmArgs a) {
     }
     const int k_tiles = (k_end - k_begin + TC_BK - 1) / TC_BK;
 
+    float acc[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+    auto drain = [&](int kt) {
+        // Partial of k-tile kt: wait for its instructions, add its buffer into the registers.
+        mbar_wait(bars + (kt & 1), (uint32_t)((kt >> 1) & 1), a.error);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t src = my_tmem + (uint32_t)((kt & 1) * buf_cols);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (c * 32 < NH) {
+                float v[32];
+                tc_load32(src + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    };
+
     for (int kt = 0; kt < k_tiles; ++kt) {
         const int s = kt & 1;
         unsigned char* a_hi = tc_smem + s * stage_bytes;
         unsigned char* a_lo = a_hi + a_bytes;
         unsigned char* b_hi = a_lo + a_bytes;
         unsigned char* b_lo = b_hi + b_bytes;
-        if (kt >= 2) mbar_wait(bars + s, (uint32_t)(((kt >> 1) - 1) & 1), a.error);  // the MMAs of tile kt-2 are done
+        // Stage s and buffer s are free: k-tile kt-2 was drained in the previous iteration.
         const int k0 = k_begin + kt * TC_BK;
         if (!WGRAD) {
             // A: 128 rows x 8 chunks of 4 floats, split in registers.
@@ -181,16 +212,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_gemm_kernel(TcGemmArgs a) {
             cp_async_commit();
             cp_async_wait_all();
         } else {
-            // A(m, k) = H[k0 + k][m0 + m]: thread = m, four consecutive k per 16-byte store.
+            // A(m, k) = H[k0 + k][m0 + m]: thread = (m, half of the chunks), four consecutive k per store.
 #pragma unroll
-            for (int c = 0; c < TC_CHUNKS; ++c) {
+            for (int cc = 0; cc < TC_CHUNKS / 2; ++cc) {
+                const int c = half * (TC_CHUNKS / 2) + cc;
                 float v[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int r = k0 + 4 * c + q;
-                    v[q] = (r < k_end && m0 + tid < a.M) ? a.A[(size_t)r * a.lda + m0 + tid] : 0.0f;
+                    v[q] = (r < k_end && m0 + trow < a.M) ? a.A[(size_t)r * a.lda + m0 + trow] : 0.0f;
                 }
-                tc_store_split4(a_hi, a_lo, tc_offset(tid, 4 * c), v);
+                tc_store_split4(a_hi, a_lo, tc_offset(trow, 4 * c), v);
             }
             // B(n, k) = G[k0 + k][n].
             for (int n = tid; n < N; n += TC_THREADS) {
@@ -213,53 +245,44 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_gemm_kernel(TcGemmArgs a) {
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t ah = smem_u32(a_hi), al = smem_u32(a_lo), bh = smem_u32(b_hi), bl = smem_u32(b_lo);
+            const uint32_t dst = tmem_base + (uint32_t)(s * buf_cols);
+            // The small correction products first (they add onto a small accumulator without
+            // loss), the four full-magnitude products last: four significant truncations per tile.
 #pragma unroll
             for (int kb = 0; kb < TC_BK / 8; ++kb) {
                 const uint32_t step = kb * 2 * 128;  // two core matrices per k = 8
-                const uint32_t first = (kt == 0 && kb == 0) ? 0u : 1u;
-                tc_mma(tmem_base, tc_desc(al + step), tc_desc(bh + step), idesc, first);
-                tc_mma(tmem_base, tc_desc(ah + step), tc_desc(bl + step), idesc, 1u);
-                tc_mma(tmem_base, tc_desc(ah + step), tc_desc(bh + step), idesc, 1u);
+                tc_mma(dst, tc_desc(al + step), tc_desc(bh + step), idesc, kb == 0 ? 0u : 1u);
+                tc_mma(dst, tc_desc(ah + step), tc_desc(bl + step), idesc, 1u);
+            }
+#pragma unroll
+            for (int kb = 0; kb < TC_BK / 8; ++kb) {
+                const uint32_t step = kb * 2 * 128;
+                tc_mma(dst, tc_desc(ah + step), tc_desc(bh + step), idesc, 1u);
             }
             tc_commit(bars + s);
         }
+        if (kt >= 1) drain(kt - 1);  // overlaps with the instructions just issued
     }
-    // The last commit covers every MMA issued before it.
-    if (k_tiles > 0) {
-        const int last = k_tiles - 1;
-        mbar_wait(bars + (last & 1), (uint32_t)((last >> 1) & 1), a.error);
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (k_tiles > 0) drain(k_tiles - 1);
 
-    // Epilogue: thread = accumulator row (TMEM lane), 32 columns at a time.
-    const int row = m0 + tid;
-    float* out;
-    if (WGRAD) {
-        out = a.C + ((size_t)blockIdx.x * a.M + row) * a.ldc;
-    } else {
-        out = a.C + (size_t)row * a.ldc;
-    }
-    for (int c0 = 0; c0 < N; c0 += 32) {
-        float v[32];
-        tc_load32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-        if (k_tiles == 0) {
+    // Epilogue from registers: thread = (row, half of the columns).
+    const int row = m0 + trow;
+    if (row < a.M) {
+        float* out = WGRAD ? a.C + ((size_t)blockIdx.x * a.M + row) * a.ldc : a.C + (size_t)row * a.ldc;
+        out += half * NH;
+        const bool biased = !WGRAD && a.bias != nullptr && row < a.bias_rows;
+        const float* bias = a.bias + half * NH;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-        }
-        if (row < a.M) {
-            const bool biased = !WGRAD && a.bias != nullptr && row < a.bias_rows;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                if (c0 + i < N) {
-                    float4 q = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                    if (biased) {
-                        q.x += a.bias[c0 + i];
-                        q.y += a.bias[c0 + i + 1];
-                        q.z += a.bias[c0 + i + 2];
-                        q.w += a.bias[c0 + i + 3];
-                    }
-                    *reinterpret_cast<float4*>(out + c0 + i) = q;
+        for (int i = 0; i < 128; i += 4) {
+            if (i < NH) {
+                float4 q = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                if (biased) {
+                    q.x += bias[i];
+                    q.y += bias[i + 1];
+                    q.z += bias[i + 2];
+                    q.w += bias[i + 3];
                 }
+                *reinterpret_cast<float4*>(out + i) = q;
             }
         }
     }

@@ -8,7 +8,7 @@
 namespace qb {
 
 // Shapes the tensor-core kernels accept.
-bool tc_rows_ok(int N, int K);     // C[M][N] = A[M][K] * W: N % 16 == 0, 16 <= N <= 256, K % 32 == 0
+bool tc_rows_ok(int N, int K);     // C[M][N] = A[M][K] * W: N % 64 == 0, 64 <= N <= 256, K % 32 == 0
 bool tc_wgrad_ok(int Mw, int N);   // P = H^T G with H [rows][Mw], G [rows][N]: Mw % 128 == 0, N as above
 bool tc_enabled();                 // QB200_TC=0 switches the tensor-core GEMMs off
 

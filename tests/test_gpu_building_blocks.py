@@ -71,3 +71,48 @@ def test_optimizer_apply_matches_the_host_rule_bit_for_bit(cuda_device, dtype_na
         assert dp.cpu().numpy().tobytes() == p.tobytes()
         assert dm.cpu().numpy().tobytes() == m.tobytes()
         assert dv.cpu().numpy().tobytes() == v.tobytes()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 32), (127, 64, 64), (129, 128, 96), (1000, 192, 64), (4096, 256, 256)])
+def test_matmul_3xtf32_keeps_float32_accuracy(cuda_device, M, N, K):
+    import torch
+
+    lib = _lib.load()
+    generator = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=generator)
+    w = torch.randn(K, N, device="cuda", generator=generator) / K**0.5
+    bias = torch.randn(N, device="cuda", generator=generator)
+    out = torch.full((M, N), float("nan"), device="cuda")
+    biased = M // 2
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.qb200_matmul_3xtf32(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, biased, stream))
+    expected = a.double() @ w.double()
+    expected[:biased] += bias.double()
+    error = (out.double() - expected).abs().max().item() / expected.abs().max().item()
+    assert error <= 2e-6  # plain TF32 would be ~1e-3
+
+
+def test_matmul_3xtf32_rejects_unsupported_shapes(cuda_device):
+    lib = _lib.load()
+    eight = C.c_void_p(8)
+    assert lib.qb200_matmul_3xtf32(eight, eight, None, eight, 4, 48, 32, 0, None) == _lib.UNSUPPORTED
+    assert lib.qb200_matmul_3xtf32(eight, eight, None, eight, 4, 64, 20, 0, None) == _lib.UNSUPPORTED
+    assert lib.qb200_matmul_3xtf32(None, eight, None, eight, 4, 64, 32, 0, None) == _lib.INVALID
+
+
+@pytest.mark.parametrize("rows,d_in,d_out", [(4096, 128, 64), (10000, 256, 256), (33, 128, 128)])
+def test_weight_gradient_on_the_tensor_cores(cuda_device, rows, d_in, d_out):
+    # Shapes with d_in % 128 == 0 and d_out % 64 == 0 take the tcgen05 kernel in float32.
+    import torch
+
+    lib = _lib.load()
+    generator = torch.Generator(device="cuda").manual_seed(rows)
+    acts = torch.randn(rows, d_in, device="cuda", generator=generator)
+    cots = torch.randn(rows, d_out, device="cuda", generator=generator)
+    grad = torch.full((d_in, d_out), float("nan"), device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.qb200_weight_gradient(_lib.F32, _ptr(acts), _ptr(cots), rows, d_in, d_out, _ptr(grad), stream))
+    torch.cuda.synchronize()
+    expected = acts.double().T @ cots.double()
+    error = (grad.double() - expected).abs().max().item() / expected.abs().max().item()
+    assert error <= 2e-6
