@@ -312,6 +312,16 @@ def main() -> None:
                    1: "fused_step_kernel (interior point set)",
                    2: "fused_mma_kernel (interior point set)",
                    3: "layer-wise kernels of the interior point set (tcgen05 GEMMs)"}[engine]
+    # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under profiles/
+    # (dram__bytes read + write); known for the default workload's fused kernel only.
+    traffic = None
+    if w.name == "poisson2d" and engine == 2 and per_gpu == 65536:
+        traffic = 54.9e6
+    extra_peaks = {}
+    if dtype_name == "f32":
+        # Also measured on this pool (torch.matmul 8192^3, best of 10): TF32 GEMM 756.5, SGEMM 63.9 TFLOP/s.
+        extra_peaks = {"frac_of_tf32_gemm_over_3": achieved_tflops / (756.5 / 3.0),
+                       "frac_of_sgemm": achieved_tflops / 63.9}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -324,7 +334,7 @@ def main() -> None:
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s",
-                     "frac": achieved_tflops / peak_tflops, "traffic": None,
+                     "frac": achieved_tflops / peak_tflops, "traffic": traffic, **extra_peaks,
                      "kernel": kernel_name, "kernel_us": kernel_s * 1e6, "flops_per_launch": flops,
                      "step_flops": w.flops_per_step, "peak_source": peak_note},
     }
