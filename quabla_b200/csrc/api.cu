@@ -166,9 +166,9 @@ static qb200_status weight_gradient_typed(const void* acts, const void* cots, in
         // Tensor-core contraction (tcgen05, 3xTF32); same slices, same reduction.
         int* flag = reinterpret_cast<int*>(static_cast<float*>(scratch) + (size_t)slices * count);
         cudaMemsetAsync(flag, 0, sizeof(int), stream);
-        cudaError_t e = qb::tc_wgrad_launch(static_cast<const float*>(acts), d_in, static_cast<const float*>(cots),
-                                            d_out, static_cast<float*>(scratch), (int)rows, d_in, d_out,
-                                            qb::WGRAD_ROWS_PER_SLICE, flag, stream);
+        cudaError_t e = (qb::tc_generation() == 2 ? qb::tc2_wgrad_launch : qb::tc_wgrad_launch)(
+            static_cast<const float*>(acts), d_in, static_cast<const float*>(cots), d_out, static_cast<float*>(scratch),
+            (int)rows, d_in, d_out, qb::WGRAD_ROWS_PER_SLICE, flag, stream);
         if (e == cudaSuccess) {
             qb::reduce_partials_kernel<T><<<((int)count + 255) / 256, 256, 0, stream>>>(
                 static_cast<const T*>(scratch), static_cast<T*>(grad), (int)count, slices);
@@ -561,10 +561,21 @@ qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d
     QB_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&image), (qb::tc_image_words(K, N) + 4) * sizeof(uint32_t), s));
     int* flag = reinterpret_cast<int*>(image + qb::tc_image_words(K, N));
     QB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), s));
-    cudaError_t e = qb::tc_prep_launch(static_cast<const float*>(d_w), K, N, image, s);
-    if (e == cudaSuccess)
-        e = qb::tc_rows_launch(static_cast<const float*>(d_a), K, image, false, K, N, static_cast<float*>(d_c), N,
-                               static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, flag, s);
+    cudaError_t e;
+    if (qb::tc_generation() == 2) {
+        // TMA kernel: the K-major operand is W transposed, unsplit.
+        float* wt = reinterpret_cast<float*>(image);
+        e = qb::tc2_transpose_launch(static_cast<const float*>(d_w), K, N, wt, s);
+        if (e == cudaSuccess)
+            e = qb::tc2_rows_launch(static_cast<const float*>(d_a), K, wt, K, static_cast<float*>(d_c), N,
+                                    static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, N, K,
+                                    flag, s);
+    } else {
+        e = qb::tc_prep_launch(static_cast<const float*>(d_w), K, N, image, s);
+        if (e == cudaSuccess)
+            e = qb::tc_rows_launch(static_cast<const float*>(d_a), K, image, false, K, N, static_cast<float*>(d_c), N,
+                                   static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, flag, s);
+    }
     int host_flag = 0;
     if (e == cudaSuccess) e = cudaMemcpyAsync(&host_flag, flag, sizeof(int), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);

@@ -688,7 +688,11 @@ template <>
 qb200_status Plan<float>::tc_prepare() {
     for (int l = 0; l < L_; ++l) {
         if (tc_image_[l] == nullptr) continue;
-        cudaError_t e = tc_prep_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], tc_image_[l], stream_);
+        // TMA kernels take the weight unsplit: W itself for the data gradient, W^T for the forward product.
+        cudaError_t e = tc_generation() == 2
+                            ? tc2_transpose_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1],
+                                                   reinterpret_cast<float*>(tc_image_[l]), stream_)
+                            : tc_prep_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], tc_image_[l], stream_);
         ++launches_;
         if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of tc_prep_weight_kernel failed: %s", cudaGetErrorString(e));
     }
@@ -699,7 +703,11 @@ template <>
 bool Plan<float>::tc_forward(int layer, const float* A, float* C, long long rows, int bias_rows, qb200_status* st) {
     if (!tc_fwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc_rows_launch(A, K, tc_image_[layer], false, K, N, C, N, bias(layer), bias_rows, (int)rows, d_error_, stream_);
+    cudaError_t e = tc_generation() == 2
+                        ? tc2_rows_launch(A, K, reinterpret_cast<const float*>(tc_image_[layer]), K, C, N, bias(layer),
+                                          bias_rows, (int)rows, N, K, d_error_, stream_)
+                        : tc_rows_launch(A, K, tc_image_[layer], false, K, N, C, N, bias(layer), bias_rows, (int)rows,
+                                         d_error_, stream_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(forward) failed: %s", cudaGetErrorString(e));
     return true;
@@ -709,7 +717,10 @@ template <>
 bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long rows, qb200_status* st) {
     if (!tc_bwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc_rows_launch(G, N, tc_image_[layer], true, K, N, Gprev, K, nullptr, 0, (int)rows, d_error_, stream_);
+    cudaError_t e = tc_generation() == 2
+                        ? tc2_rows_launch(G, N, weight(layer), N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, stream_)
+                        : tc_rows_launch(G, N, tc_image_[layer], true, K, N, Gprev, K, nullptr, 0, (int)rows, d_error_,
+                                         stream_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(dgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -720,7 +731,8 @@ bool Plan<float>::tc_wgrad(int layer, const float* H, const float* G, long long 
                            qb200_status* st) {
     if (layer < 0 || layer >= L_ || !tc_wgrad_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc_wgrad_launch(H, K, G, N, wpartial_, (int)rows, K, N, rows_per_slice, d_error_, stream_);
+    cudaError_t e = (tc_generation() == 2 ? tc2_wgrad_launch : tc_wgrad_launch)(H, K, G, N, wpartial_, (int)rows, K, N,
+                                                                                rows_per_slice, d_error_, stream_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(wgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -780,7 +792,9 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     auto wgrad = [&](const T* Hprev, const T* Gz, int d_in, int d_out, int leaf, int layer) -> qb200_status {
         {
             qb200_status tc_status = QB200_OK;
-            const int tc_chunk = slice_rows(rows, std::max(1, d_in / 128), 32);
+            // Output tiles of the tensor-core kernel: 128 rows of dW by all (first generation) or 128/64 columns.
+            const int tc_col_tiles = tc_generation() == 2 ? d_out / (d_out % 128 == 0 ? 128 : 64) : 1;
+            const int tc_chunk = slice_rows(rows, std::max(1, d_in / 128) * std::max(1, tc_col_tiles), 32);
             if (tc_wgrad(layer, Hprev, Gz, rows, tc_chunk, &tc_status)) {
                 QB_TRY(tc_status);
                 const int count = d_in * d_out;

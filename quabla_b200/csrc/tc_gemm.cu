@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "tc_gemm.cuh"
+#include "tc_tma_gemm.cuh"
 
 namespace qb {
 
@@ -76,6 +77,106 @@ cudaError_t tc_wgrad_launch(const float* H, int ldh, const float* G, int ldg, fl
     const int slices = (rows + rows_per_slice - 1) / rows_per_slice;
     tc_gemm_kernel<true><<<dim3(slices, Mw / TC_BM), TC_THREADS, smem_bytes(N), stream>>>(a);
     return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Second generation: tensor-map (TMA) operand loads.
+// ---------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) != cudaSuccess ||
+            status != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+int tc_generation() {
+    static const int generation = [] {
+        const char* env = getenv("QB200_TC");
+        if (env != nullptr && strcmp(env, "0") == 0) return 0;
+        if (env != nullptr && strcmp(env, "1") == 0) return 1;
+        return encode_tiled() != nullptr ? 2 : 1;
+    }();
+    return generation;
+}
+
+// Row-major float32 matrix [rows][cols] with leading dimension ld, boxes of box_cols x box_rows,
+// the given 128-byte swizzle, zero fill outside the matrix.
+static bool make_map(CUtensorMap* map, const float* base, long long rows, int cols, int ld, int box_cols, int box_rows,
+                     CUtensorMapSwizzle swizzle) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode_tiled()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaStream_t stream) {
+    t2_transpose_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), dim3(32, 8), 0, stream>>>(w, K, N, wt);
+    return cudaGetLastError();
+}
+
+template <bool WGRAD, int BN>
+static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const TcTmaArgs& a, dim3 grid, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN>),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, T2Geom<BN>::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    tc_tma_gemm_kernel<WGRAD, BN><<<grid, T2_THREADS, T2Geom<BN>::SMEM_BYTES, stream>>>(ma, mb, a);
+    return cudaGetLastError();
+}
+
+cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, int ldb, float* C, int ldc, const float* bias,
+                            int bias_rows, int M, int N, int K, int* error, cudaStream_t stream) {
+    const int BN = N % 128 == 0 ? 128 : 64;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        return cudaErrorInvalidValue;
+    TcTmaArgs a;
+    memset(&a, 0, sizeof(a));
+    a.C = C;
+    a.bias = bias;
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.ldc = ldc;
+    a.bias_rows = bias_rows;
+    a.units = ((M + T2_BM - 1) / T2_BM) * (N / BN);
+    a.error = error;
+    const dim3 grid(a.units < 148 ? a.units : 148);
+    return BN == 128 ? launch2<false, 128>(ma, mb, a, grid, stream) : launch2<false, 64>(ma, mb, a, grid, stream);
+}
+
+cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,
+                             int rows_per_slice, int* error, cudaStream_t stream) {
+    const int BN = N % 128 == 0 ? 128 : 64;
+    CUtensorMap ma, mb;
+    if (!make_map(&ma, H, rows, Mw, ldh, 32, T2_BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) ||
+        !make_map(&mb, G, rows, N, ldg, 32, T2_BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        return cudaErrorInvalidValue;
+    TcTmaArgs a;
+    memset(&a, 0, sizeof(a));
+    a.C = partials;
+    a.M = Mw;
+    a.N = N;
+    a.K = rows;
+    a.ldc = N;
+    a.k_slice = rows_per_slice;
+    a.error = error;
+    const int slices = (rows + rows_per_slice - 1) / rows_per_slice;
+    const dim3 grid(slices, Mw / T2_BM, N / BN);
+    return BN == 128 ? launch2<true, 128>(ma, mb, a, grid, stream) : launch2<true, 64>(ma, mb, a, grid, stream);
 }
 
 }  // namespace qb

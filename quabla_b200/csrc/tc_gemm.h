@@ -25,4 +25,16 @@ cudaError_t tc_rows_launch(const float* A, int lda, const uint32_t* image, bool 
 cudaError_t tc_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw,
                             int N, int rows_per_slice, int* error, cudaStream_t stream);
 
+// Second generation (tc_tma_gemm.cuh): operands by TMA tensor maps, no pre-split images.
+// 0: tensor-core GEMMs off (QB200_TC=0); 1: first generation (QB200_TC=1, or no driver entry point
+// for tensor maps); 2: TMA kernels.
+int tc_generation();
+// wt[n][k] = w[k][n]: the K-major operand of the forward GEMM.
+cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaStream_t stream);
+// C[M][N] = A[M][K] * Bt^T (+ bias on the first bias_rows rows), Bt row-major [N][K].
+cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, int ldb, float* C, int ldc, const float* bias,
+                            int bias_rows, int M, int N, int K, int* error, cudaStream_t stream);
+cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,
+                             int rows_per_slice, int* error, cudaStream_t stream);
+
 }  // namespace qb

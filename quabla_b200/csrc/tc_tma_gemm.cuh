@@ -1,0 +1,298 @@
+// float32 GEMMs of the layer-wise engine, second generation: operands arrive by TMA tensor-map
+// loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a ring of shared-memory
+// stages, the products run on tcgen05.mma (kind::tf32) with accumulators in tensor memory, and
+// completion is tracked by mbarriers with bounded waits.
+//
+// 3xTF32 without pre-split operands.  The tensor core reads the upper 19 bits of a float32
+// operand, so the tile as loaded IS the hi operand (hi = x & 0xffffe000).  The CTA's threads
+// compute lo = tf32(x - hi) element by element from shared memory into a second buffer at the
+// same offsets (any swizzle carries over), and a product is A_lo.B_hi + A_hi.B_lo + A_hi.B_hi.
+//
+// Accuracy.  The tensor core adds into its accumulator with truncation, so a k-tile of 32
+// accumulates from zero into one of two tensor-memory buffers and the threads add that partial to
+// float32 registers with round-to-nearest adds while the next k-tile's instructions run.
+//
+// Work of one CTA (256 threads): 128 x BN output tiles, k-tiles of 32 floats (one 128-byte
+// swizzle span).
+//   ROWS   C[m][n] = sum_k A[m][k] * Bt[n][k] (+ bias[n] on rows < bias_rows).  Both operands are
+//          K-major: a stage holds A [128 rows][128 B] and Bt [BN rows][128 B].  The CTA is
+//          persistent over output tiles (tile = blockIdx.x + i * gridDim.x, n-tile fastest), and
+//          the stage ring runs ahead across tile boundaries.
+//   WGRAD  P[z][m][n] = sum over the rows r of slice z of H[r][m] * G[r][n].  Both operands are
+//          MN-major: a stage holds 4 atoms [32 r][32 m] of H and BN/32 atoms [32 r][32 n] of G,
+//          each 4 KB, exactly as a tensor-map box of the row-major matrices lands them.
+#pragma once
+#include <cuda.h>
+
+#include <cstdint>
+
+#include "fused_mma_kernel.cuh"  // split_tf32, mbarrier helpers
+#include "tc_gemm.cuh"           // tc_mma, tc_commit, tc_load32
+
+namespace qb {
+
+constexpr int T2_BM = 128;
+constexpr int T2_BK = 32;
+constexpr int T2_THREADS = 256;
+constexpr int T2_STAGES = 4;
+constexpr int T2_A_BYTES = T2_BM * T2_BK * 4;  // 16 KB
+
+struct TcTmaArgs {
+    float* C;           // ROWS: [M][ldc];  WGRAD: partials [slices][Mw][N]
+    const float* bias;
+    int M, N, K;        // ROWS: M rows, K inner;  WGRAD: M = width of H, K = rows
+    int ldc;
+    int bias_rows;
+    int k_slice;        // WGRAD: rows per slice (multiple of T2_BK)
+    int units;          // ROWS: output tiles in total
+    int* error;
+};
+
+template <int BN>
+struct T2Geom {
+    static constexpr int B_BYTES = BN * T2_BK * 4;
+    static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES;            // multiple of 1024
+    static constexpr int LO_OFFSET = T2_STAGES * STAGE_BYTES;
+    static constexpr int BAR_OFFSET = LO_OFFSET + 2 * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = BAR_OFFSET + 128 + 1024;          // barriers, TMEM slot, alignment slack
+    static constexpr int VECTORS = STAGE_BYTES / 16;                    // 16-byte vectors per stage
+};
+
+// Matrix descriptors for 128-byte-swizzled operand tiles (descriptor version 1, layout type 2).
+// K-major: rows of 128 bytes, 8-row groups 1024 bytes apart (stride byte offset); the leading
+// byte offset is fixed to 1 by the format.  MN-major tf32 operands exist only in the "128-byte
+// swizzle with 32-byte atoms" layout (type 1; the tensor map uses SWIZZLE_128B_ATOM_32B): rows of
+// 128 bytes along M/N, 4-k-row groups 512 bytes apart (stride), atoms of 32 elements along M/N
+// 4096 bytes apart (leading).
+__device__ __forceinline__ uint64_t t2_desc_kmajor(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t t2_desc_mnmajor(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)(4096 >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)1 << 61);
+}
+
+// Instruction descriptor: float32 accumulator, tf32 operands, M = 128, N = BN; bits 15 and 16
+// select MN-major A and B.
+__device__ __forceinline__ uint32_t t2_idesc(int N, bool mn_major) {
+    uint32_t d = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(T2_BM >> 4) << 24);
+    if (mn_major) d |= (1u << 15) | (1u << 16);
+    return d;
+}
+
+// One box of a 2-D tensor map into shared memory; completion is counted in bytes on `bar`.
+__device__ __forceinline__ void t2_tma_load(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+template <bool WGRAD, int BN>
+__global__ void __launch_bounds__(T2_THREADS, 1)
+    tc_tma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcTmaArgs a) {
+    typedef T2Geom<BN> G;
+    extern __shared__ unsigned char t2_smem_raw[];
+    // Swizzled tiles need 1024-byte alignment.
+    unsigned char* const smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t2_smem_raw) + 1023) &
+                                                                 ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint64_t* const full = reinterpret_cast<uint64_t*>(smem + G::BAR_OFFSET);  // [T2_STAGES]
+    uint64_t* const done = full + T2_STAGES;                                   // [2]
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
+    constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers; a power of two >= 32
+    constexpr int NH = BN / 2;         // columns drained by one thread
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < T2_STAGES; ++s) mbar_init(full + s, 1);
+        mbar_init(done, 1);
+        mbar_init(done + 1, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t idesc = t2_idesc(BN, WGRAD);
+    const int half = warp >> 2;  // which BN/2 columns this thread drains
+    const uint32_t my_tmem = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * NH);
+    const int trow = (warp & 3) * 32 + lane;  // accumulator lane = output row within the tile
+
+    // Work list of this CTA.
+    const int n_tiles = a.N / BN;
+    int units, k_tiles, k_begin = 0;
+    if (WGRAD) {
+        units = 1;
+        k_begin = blockIdx.x * a.k_slice;
+        const int k_end = min(a.K, k_begin + a.k_slice);
+        k_tiles = (k_end - k_begin + T2_BK - 1) / T2_BK;
+    } else {
+        units = ((int)blockIdx.x < a.units) ? (a.units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        k_tiles = a.K / T2_BK;
+    }
+    const int items = units * k_tiles;
+    // Tile coordinates of unit u of this CTA.
+    auto unit_m0 = [&](int u) { return WGRAD ? (int)blockIdx.y * T2_BM : (((int)blockIdx.x + u * (int)gridDim.x) / n_tiles) * T2_BM; };
+    auto unit_n0 = [&](int u) { return WGRAD ? (int)blockIdx.z * BN : (((int)blockIdx.x + u * (int)gridDim.x) % n_tiles) * BN; };
+
+    // Producer (thread 0): tensor-map loads of item p into stage p % T2_STAGES.
+    auto produce = [&](int p) {
+        const int u = p / k_tiles, kt = p - u * k_tiles;
+        const int m0 = unit_m0(u), n0 = unit_n0(u), k0 = k_begin + kt * T2_BK;
+        unsigned char* stage = smem + (p % T2_STAGES) * G::STAGE_BYTES;
+        uint64_t* bar = full + (p % T2_STAGES);
+        mbar_expect_tx(bar, G::STAGE_BYTES);
+        if (!WGRAD) {
+            t2_tma_load(stage, &map_a, k0, m0, bar);               // box {32 k, 128 rows}
+            t2_tma_load(stage + T2_A_BYTES, &map_b, k0, n0, bar);  // box {32 k, BN rows}
+        } else {
+#pragma unroll
+            for (int j = 0; j < T2_BM / 32; ++j) t2_tma_load(stage + j * 4096, &map_a, m0 + 32 * j, k0, bar);
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j) t2_tma_load(stage + T2_A_BYTES + j * 4096, &map_b, n0 + 32 * j, k0, bar);
+        }
+    };
+    int produced = 0;
+    if (tid == 0)
+        for (; produced < items && produced < T2_STAGES; ++produced) produce(produced);
+
+    float acc[NH];
+#pragma unroll
+    for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
+
+    // Partial of item q: wait for its instructions, add its buffer into the registers.
+    auto drain = [&](int q) {
+        mbar_wait(done + (q & 1), (uint32_t)((q >> 1) & 1), a.error);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t src = my_tmem + (uint32_t)((q & 1) * BN);
+#pragma unroll
+        for (int c = 0; c < NH / 32; ++c) {
+            float v[32];
+            tc_load32(src + c * 32, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    };
+    // Output of unit u from the registers: thread = (row, half of the columns).
+    auto write_out = [&](int u) {
+        const int row = unit_m0(u) + trow, col = unit_n0(u) + half * NH;
+        if (row < a.M) {
+            float* out = WGRAD ? a.C + ((size_t)blockIdx.x * a.M + row) * a.ldc + col : a.C + (size_t)row * a.ldc + col;
+            const bool biased = !WGRAD && a.bias != nullptr && row < a.bias_rows;
+#pragma unroll
+            for (int i = 0; i < NH; i += 4) {
+                float4 v = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                if (biased) {
+                    const float4 b = *reinterpret_cast<const float4*>(a.bias + col + i);
+                    v.x += b.x;
+                    v.y += b.y;
+                    v.z += b.z;
+                    v.w += b.w;
+                }
+                *reinterpret_cast<float4*>(out + i) = v;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
+    };
+
+    for (int it = 0; it < items; ++it) {
+        const int s = it % T2_STAGES, b = it & 1;
+        unsigned char* const hi = smem + s * G::STAGE_BYTES;
+        unsigned char* const lo = smem + G::LO_OFFSET + b * G::STAGE_BYTES;
+        mbar_wait(full + s, (uint32_t)((it / T2_STAGES) & 1), a.error);
+        // lo = tf32(x - hi) at the same offsets.  The lo buffer and the accumulator buffer b were
+        // last used by item it-2, whose completion every thread saw in the previous iteration.
+#pragma unroll
+        for (int i = 0; i < G::VECTORS / T2_THREADS; ++i) {
+            const int v = tid + i * T2_THREADS;
+            const uint4 x = *reinterpret_cast<const uint4*>(hi + 16 * v);
+            uint4 l;
+            uint32_t h;
+            split_tf32(__uint_as_float(x.x), h, l.x);
+            split_tf32(__uint_as_float(x.y), h, l.y);
+            split_tf32(__uint_as_float(x.z), h, l.z);
+            split_tf32(__uint_as_float(x.w), h, l.w);
+            *reinterpret_cast<uint4*>(lo + 16 * v) = l;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t ah = smem_u32(hi), al = smem_u32(lo);
+            const uint32_t bh = ah + T2_A_BYTES, bl = al + T2_A_BYTES;
+            const uint32_t dst = tmem_base + (uint32_t)(b * BN);
+            // k = 8 per instruction: 32 bytes along a K-major row, one 8-row group (1024 bytes) of
+            // an MN-major atom.  The small correction products go first (they add onto a small
+            // accumulator without loss), the full-magnitude products last.
+            constexpr uint32_t STEP = WGRAD ? 1024 : 32;
+#pragma unroll
+            for (int kb = 0; kb < T2_BK / 8; ++kb) {
+                const uint32_t o = kb * STEP;
+                if (WGRAD) {
+                    tc_mma(dst, t2_desc_mnmajor(al + o), t2_desc_mnmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
+                    tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bl + o), idesc, 1u);
+                } else {
+                    tc_mma(dst, t2_desc_kmajor(al + o), t2_desc_kmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
+                    tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bl + o), idesc, 1u);
+                }
+            }
+#pragma unroll
+            for (int kb = 0; kb < T2_BK / 8; ++kb) {
+                const uint32_t o = kb * STEP;
+                if (WGRAD)
+                    tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bh + o), idesc, 1u);
+                else
+                    tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bh + o), idesc, 1u);
+            }
+            tc_commit(done + b);
+        }
+        if (it >= 1) {
+            drain(it - 1);  // overlaps with the instructions just issued
+            // Item it-1 is complete: its stage can take the item T2_STAGES further on.
+            if (tid == 0 && produced < items) {
+                produce(produced);
+                ++produced;
+            }
+            if (it % k_tiles == 0) write_out(it / k_tiles - 1);  // item it-1 closed a unit
+        }
+    }
+    if (items > 0) {
+        drain(items - 1);
+        write_out(units - 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+    }
+}
+
+// Bt[n][k] = W[k][n]: the K-major forward operand of a weight stored [K][N] row-major.
+__global__ void t2_transpose_kernel(const float* __restrict__ w, int K, int N, float* __restrict__ wt) {
+    __shared__ float tile[32][33];
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int k = k0 + r, n = n0 + threadIdx.x;
+        tile[r][threadIdx.x] = (k < K && n < N) ? w[(size_t)k * N + n] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int n = n0 + r, k = k0 + threadIdx.x;
+        if (n < N && k < K) wt[(size_t)n * K + k] = tile[threadIdx.x][r];
+    }
+}
+
+}  // namespace qb
