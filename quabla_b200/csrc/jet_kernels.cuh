@@ -1,0 +1,180 @@
+// Vectorised tanh-jet kernels of the layer-wise engine for the common derivative signatures.
+//
+// Activations are [S][C][d] (stream-major planes of `plane` = C*d elements).  A thread owns 16 bytes
+// of every plane (4 floats or 2 doubles of consecutive units): it issues the S (forward) or 2S+1
+// (backward) 16-byte loads up front, runs the Faa di Bruno composition with the signature known at
+// compile time (all stream loops unroll, no local memory), and stores 16 bytes per plane.  The
+// generic jet_forward_kernel / jet_backward_kernel (layer_kernels.cuh) remain for other signatures
+// and for planes that are not a multiple of 16 bytes.
+//
+// These kernels are HBM-bound: 2*S*plane elements of traffic forward, (3S+1)*plane backward.
+#pragma once
+#include "fused_kernel.cuh"  // Sig<CODE>, jet_apply
+#include "jet_math.cuh"
+
+namespace qb {
+
+template <typename T>
+struct JetVec;
+template <>
+struct JetVec<float> {
+    static constexpr int V = 4;
+    typedef float4 type;
+    static __device__ __forceinline__ void unpack(const float4& q, float (&v)[4]) {
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    }
+    static __device__ __forceinline__ float4 pack(const float (&v)[4]) { return make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <>
+struct JetVec<double> {
+    static constexpr int V = 2;
+    typedef double2 type;
+    static __device__ __forceinline__ void unpack(const double2& q, double (&v)[2]) {
+        v[0] = q.x; v[1] = q.y;
+    }
+    static __device__ __forceinline__ double2 pack(const double (&v)[2]) { return make_double2(v[0], v[1]); }
+};
+
+// Transposed jet composition with the primal activation t = tanh(z_0) given (saved by the forward pass).
+template <typename T, typename SG>
+__device__ __forceinline__ void jet_apply_transposed_saved(T t, const T (&z)[SG::S], T (&g)[SG::S]) {
+    const TanhD<T> d(t);
+    T z0bar = d.t1 * g[0];
+#pragma unroll
+    for (int j = 0; j < SG::ndirs; ++j) {
+        T zz[MAX_ORDER], gg[MAX_ORDER], gz[MAX_ORDER];
+        const int K = SG::order(j);
+        const int b = SG::base(j);
+#pragma unroll
+        for (int m = 0; m < MAX_ORDER; ++m) {
+            zz[m] = m < K ? z[b + m] : T(0);
+            gg[m] = m < K ? g[b + m] : T(0);
+        }
+        switch (K) {
+            case 1: z0bar += jet_compose_transposed<T, 1>(d, zz, gg, gz); break;
+            case 2: z0bar += jet_compose_transposed<T, 2>(d, zz, gg, gz); break;
+            case 3: z0bar += jet_compose_transposed<T, 3>(d, zz, gg, gz); break;
+            default: z0bar += jet_compose_transposed<T, 4>(d, zz, gg, gz); break;
+        }
+#pragma unroll
+        for (int m = 0; m < MAX_ORDER; ++m)
+            if (m < K) g[b + m] = gz[m];
+    }
+    g[0] = z0bar;
+}
+
+// H = tanh-jet(Z), all streams.
+template <typename T, int CODE>
+__global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane) {
+    typedef Sig<CODE> SG;
+    typedef JetVec<T> JV;
+    typedef typename JV::type VT;
+    constexpr int S = SG::S, V = JV::V;
+    const long long nvec = plane / V;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < nvec; e += (long long)gridDim.x * blockDim.x) {
+        VT q[S];
+#pragma unroll
+        for (int s = 0; s < S; ++s) q[s] = reinterpret_cast<const VT*>(Z + (long long)s * plane)[e];
+        T lanes[S][V];
+#pragma unroll
+        for (int s = 0; s < S; ++s) JV::unpack(q[s], lanes[s]);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            T v[S];
+#pragma unroll
+            for (int s = 0; s < S; ++s) v[s] = lanes[s][i];
+            jet_apply<T, SG>(v);
+#pragma unroll
+            for (int s = 0; s < S; ++s) lanes[s][i] = v[s];
+        }
+#pragma unroll
+        for (int s = 0; s < S; ++s) reinterpret_cast<VT*>(H + (long long)s * plane)[e] = JV::pack(lanes[s]);
+    }
+}
+
+// In place: G (cotangents of H) becomes the cotangents of Z.
+template <typename T, int CODE>
+__global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
+                                                               T* __restrict__ G, long long plane) {
+    typedef Sig<CODE> SG;
+    typedef JetVec<T> JV;
+    typedef typename JV::type VT;
+    constexpr int S = SG::S, V = JV::V;
+    const long long nvec = plane / V;
+    for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < nvec; e += (long long)gridDim.x * blockDim.x) {
+        VT qz[S], qg[S];
+        const VT qt = reinterpret_cast<const VT*>(Hprimal)[e];
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            // The transposed composition never reads z_0 itself (t replaces it).
+            if (s > 0) qz[s] = reinterpret_cast<const VT*>(Z + (long long)s * plane)[e];
+            qg[s] = reinterpret_cast<const VT*>(G + (long long)s * plane)[e];
+        }
+        T t[V], zl[S][V], gl[S][V];
+        JV::unpack(qt, t);
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            if (s > 0) JV::unpack(qz[s], zl[s]);
+            JV::unpack(qg[s], gl[s]);
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            T z[S], g[S];
+            z[0] = T(0);
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                if (s > 0) z[s] = zl[s][i];
+                g[s] = gl[s][i];
+            }
+            jet_apply_transposed_saved<T, SG>(t[i], z, g);
+#pragma unroll
+            for (int s = 0; s < S; ++s) gl[s][i] = g[s];
+        }
+#pragma unroll
+        for (int s = 0; s < S; ++s) reinterpret_cast<VT*>(G + (long long)s * plane)[e] = JV::pack(gl[s]);
+    }
+}
+
+// Launchers: true when a compile-time signature exists for `code` and the planes can be read
+// 16 bytes at a time.
+template <typename T>
+inline bool jet_sig_eligible(int code, long long plane, const void* a, const void* b, const void* c) {
+    const bool known = code == 0 || code == 1 || code == 2 || code == 4 || code == 7 || code == 12 || code == 187;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
+    return known && plane % JetVec<T>::V == 0 && (bits & 15) == 0;
+}
+
+inline int jet_sig_grid(long long vectors) {
+    const long long blocks = (vectors + 255) / 256;
+    return (int)(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16);
+}
+
+template <typename T>
+inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, cudaStream_t stream) {
+    const int grid = jet_sig_grid(plane / JetVec<T>::V);
+    switch (code) {
+        case 0: jet_forward_sig_kernel<T, 0><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+        case 1: jet_forward_sig_kernel<T, 1><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+        case 2: jet_forward_sig_kernel<T, 2><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+        case 4: jet_forward_sig_kernel<T, 4><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+        case 7: jet_forward_sig_kernel<T, 7><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+        case 12: jet_forward_sig_kernel<T, 12><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+        default: jet_forward_sig_kernel<T, 187><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+    }
+}
+
+template <typename T>
+inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, cudaStream_t stream) {
+    const int grid = jet_sig_grid(plane / JetVec<T>::V);
+    switch (code) {
+        case 0: jet_backward_sig_kernel<T, 0><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
+        case 1: jet_backward_sig_kernel<T, 1><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
+        case 2: jet_backward_sig_kernel<T, 2><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
+        case 4: jet_backward_sig_kernel<T, 4><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
+        case 7: jet_backward_sig_kernel<T, 7><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
+        case 12: jet_backward_sig_kernel<T, 12><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
+        default: jet_backward_sig_kernel<T, 187><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
+    }
+}
+
+}  // namespace qb

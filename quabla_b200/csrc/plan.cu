@@ -8,6 +8,7 @@
 
 #include "fused.h"
 #include "fused_kernel.cuh"
+#include "jet_kernels.cuh"
 #include "dmma_gemm.cuh"
 #include "layer_kernels.cuh"
 #include "point_kernels.cuh"
@@ -172,6 +173,7 @@ class Plan final : public qb200_plan {
     };
     struct SetState {
         JetSpec spec;
+        int sig_code = 0;          // sum of order_j * 5^j (-1: more than 8 digits would overflow)
         int ncols = 0;
         T* table = nullptr;
         T* dirs = nullptr;
@@ -384,6 +386,14 @@ qb200_status Plan<T>::init() {
         SetState& st = sets_[si];
         st.spec.S = s.streams();
         st.spec.ndirs = (int)s.dirs.size();
+        {
+            long long code = 0, scale = 1;
+            for (int k : s.orders) {
+                code += k * scale;
+                scale *= 5;
+            }
+            st.sig_code = code < 1000000 ? (int)code : -1;
+        }
         int base = 1;
         for (int j = 0; j < MAX_DIRS; ++j) {
             st.spec.order[j] = j < st.spec.ndirs ? s.orders[j] : 0;
@@ -776,7 +786,10 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             QB_TRY(launched("gemm_kernel(forward)"));
         }
         const long long plane = (long long)C * sz[l];
-        jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec);
+        if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], nullptr))
+            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, stream_);
+        else
+            jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec);
         QB_TRY(launched("jet_forward_kernel"));
     }
     head_forward_kernel<T><<<grid_for(rows * 32, 256), 256, 0, stream_>>>(H_[head], weight(head), bias(head), U_, rows,
@@ -854,7 +867,10 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     QB_TRY(launched("head_backward_kernel"));
     for (int l = head; l >= 1; --l) {
         const long long plane = (long long)C * sz[l];
-        jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec);
+        if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], G_[cur]))
+            jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, stream_);
+        else
+            jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec);
         QB_TRY(launched("jet_backward_kernel"));
         QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1], l - 1));
         QB_TRY(bgrad(G_[cur], sz[l], b_leaf_[l - 1]));

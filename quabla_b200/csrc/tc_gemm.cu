@@ -132,7 +132,7 @@ static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const T
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN>),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, T2Geom<BN>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    tc_tma_gemm_kernel<WGRAD, BN><<<grid, T2_THREADS, T2Geom<BN>::SMEM_BYTES, stream>>>(ma, mb, a);
+    tc_tma_gemm_kernel<WGRAD, BN><<<grid, T2_THREADS_TOTAL, T2Geom<BN>::SMEM_BYTES, stream>>>(ma, mb, a);
     return cudaGetLastError();
 }
 

@@ -12,7 +12,7 @@
 // accumulates from zero into one of two tensor-memory buffers and the threads add that partial to
 // float32 registers with round-to-nearest adds while the next k-tile's instructions run.
 //
-// Work of one CTA (256 threads): 128 x BN output tiles, k-tiles of 32 floats (one 128-byte
+// Work of one CTA (eight consumer warps, a loading warp and an issuing warp): 128 x BN output tiles, k-tiles of 32 floats (one 128-byte
 // swizzle span).
 //   ROWS   C[m][n] = sum_k A[m][k] * Bt[n][k] (+ bias[n] on rows < bias_rows).  Both operands are
 //          K-major: a stage holds A [128 rows][128 B] and Bt [BN rows][128 B].  The CTA is
@@ -33,7 +33,8 @@ namespace qb {
 
 constexpr int T2_BM = 128;
 constexpr int T2_BK = 32;
-constexpr int T2_THREADS = 256;
+constexpr int T2_THREADS = 256;                    // consumer threads
+constexpr int T2_THREADS_TOTAL = T2_THREADS + 64;  // + the loading warp and the issuing warp
 constexpr int T2_STAGES = 4;
 constexpr int T2_A_BYTES = T2_BM * T2_BK * 4;  // 16 KB
 
@@ -90,8 +91,30 @@ __device__ __forceinline__ void t2_tma_load(void* dst, const CUtensorMap* map, i
         : "memory");
 }
 
+// lo operand of x: x - (x & 0xffffe000) is exact in float32; adding half a tf32 ulp to its bit
+// pattern makes the tensor core's truncation of the low 13 bits a round-to-nearest.  Three
+// full-rate ALU instructions per element (cvt.rna.tf32 issues at a fraction of that rate).
+__device__ __forceinline__ uint32_t t2_lo_bits(uint32_t x) {
+    const float d = __uint_as_float(x) - __uint_as_float(x & 0xffffe000u);
+    return __float_as_uint(d) + 0x1000u;
+}
+
+__device__ __forceinline__ void t2_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Warp roles: warps 0-7 (256 threads) are consumers: they compute the lo planes, drain the
+// accumulator partials and write the output; warp 8 issues the tensor-map loads; warp 9 owns
+// tensor memory and issues the MMAs.  Hand-offs per item (one k-tile of one output tile), all
+// through mbarriers with bounded waits:
+//   full[stage]   loads landed                     producer's TMA  -> consumers
+//   ready[buf]    lo plane written                 consumers (256) -> issuer
+//   done[buf]     the item's MMAs completed        tcgen05.commit  -> consumers (drain)
+//   empty[stage]  the item's MMAs completed        tcgen05.commit  -> producer (stage reusable)
+// A consumer arrives on ready[buf] of item i only after it drained item i-2, so that arrival
+// also tells the issuer that accumulator buffer `buf` is free.
 template <bool WGRAD, int BN>
-__global__ void __launch_bounds__(T2_THREADS, 1)
+__global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     tc_tma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcTmaArgs a) {
     typedef T2Geom<BN> G;
     extern __shared__ unsigned char t2_smem_raw[];
@@ -100,33 +123,36 @@ __global__ void __launch_bounds__(T2_THREADS, 1)
                                                                  ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint64_t* const full = reinterpret_cast<uint64_t*>(smem + G::BAR_OFFSET);  // [T2_STAGES]
-    uint64_t* const done = full + T2_STAGES;                                   // [2]
+    uint64_t* const empty = full + T2_STAGES;                                  // [T2_STAGES]
+    uint64_t* const ready = empty + T2_STAGES;                                 // [2]
+    uint64_t* const done = ready + 2;                                          // [2]
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
     constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers; a power of two >= 32
-    constexpr int NH = BN / 2;         // columns drained by one thread
+    constexpr int NH = BN / 2;         // columns drained by one consumer thread
+    constexpr int ISSUE_WARP = T2_THREADS / 32 + 1, LOAD_WARP = T2_THREADS / 32;
 
-    if (warp == 0) {
+    if (warp == ISSUE_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                      "r"(TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < T2_STAGES; ++s) mbar_init(full + s, 1);
-        mbar_init(done, 1);
-        mbar_init(done + 1, 1);
+        for (int s = 0; s < T2_STAGES; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(ready + b, T2_THREADS);
+            mbar_init(done + b, 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t idesc = t2_idesc(BN, WGRAD);
-    const int half = warp >> 2;  // which BN/2 columns this thread drains
-    const uint32_t my_tmem = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * NH);
-    const int trow = (warp & 3) * 32 + lane;  // accumulator lane = output row within the tile
 
     // Work list of this CTA.
     const int n_tiles = a.N / BN;
@@ -145,137 +171,152 @@ __global__ void __launch_bounds__(T2_THREADS, 1)
     auto unit_m0 = [&](int u) { return WGRAD ? (int)blockIdx.y * T2_BM : (((int)blockIdx.x + u * (int)gridDim.x) / n_tiles) * T2_BM; };
     auto unit_n0 = [&](int u) { return WGRAD ? (int)blockIdx.z * BN : (((int)blockIdx.x + u * (int)gridDim.x) % n_tiles) * BN; };
 
-    // Producer (thread 0): tensor-map loads of item p into stage p % T2_STAGES.
-    auto produce = [&](int p) {
-        const int u = p / k_tiles, kt = p - u * k_tiles;
-        const int m0 = unit_m0(u), n0 = unit_n0(u), k0 = k_begin + kt * T2_BK;
-        unsigned char* stage = smem + (p % T2_STAGES) * G::STAGE_BYTES;
-        uint64_t* bar = full + (p % T2_STAGES);
-        mbar_expect_tx(bar, G::STAGE_BYTES);
-        if (!WGRAD) {
-            t2_tma_load(stage, &map_a, k0, m0, bar);               // box {32 k, 128 rows}
-            t2_tma_load(stage + T2_A_BYTES, &map_b, k0, n0, bar);  // box {32 k, BN rows}
-        } else {
+    if (warp == LOAD_WARP) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            int u = 0, kt = 0, m0 = unit_m0(0), n0 = unit_n0(0);
+            for (int p = 0; p < items; ++p) {
+                const int s = p % T2_STAGES;
+                if (p >= T2_STAGES) mbar_wait(empty + s, (uint32_t)((p / T2_STAGES - 1) & 1), a.error);
+                unsigned char* stage = smem + s * G::STAGE_BYTES;
+                const int k0 = k_begin + kt * T2_BK;
+                mbar_expect_tx(full + s, G::STAGE_BYTES);
+                if (!WGRAD) {
+                    t2_tma_load(stage, &map_a, k0, m0, full + s);               // box {32 k, 128 rows}
+                    t2_tma_load(stage + T2_A_BYTES, &map_b, k0, n0, full + s);  // box {32 k, BN rows}
+                } else {
 #pragma unroll
-            for (int j = 0; j < T2_BM / 32; ++j) t2_tma_load(stage + j * 4096, &map_a, m0 + 32 * j, k0, bar);
+                    for (int j = 0; j < T2_BM / 32; ++j) t2_tma_load(stage + j * 4096, &map_a, m0 + 32 * j, k0, full + s);
 #pragma unroll
-            for (int j = 0; j < BN / 32; ++j) t2_tma_load(stage + T2_A_BYTES + j * 4096, &map_b, n0 + 32 * j, k0, bar);
-        }
-    };
-    int produced = 0;
-    if (tid == 0)
-        for (; produced < items && produced < T2_STAGES; ++produced) produce(produced);
-
-    float acc[NH];
-#pragma unroll
-    for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
-
-    // Partial of item q: wait for its instructions, add its buffer into the registers.
-    auto drain = [&](int q) {
-        mbar_wait(done + (q & 1), (uint32_t)((q >> 1) & 1), a.error);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t src = my_tmem + (uint32_t)((q & 1) * BN);
-#pragma unroll
-        for (int c = 0; c < NH / 32; ++c) {
-            float v[32];
-            tc_load32(src + c * 32, v);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    };
-    // Output of unit u from the registers: thread = (row, half of the columns).
-    auto write_out = [&](int u) {
-        const int row = unit_m0(u) + trow, col = unit_n0(u) + half * NH;
-        if (row < a.M) {
-            float* out = WGRAD ? a.C + ((size_t)blockIdx.x * a.M + row) * a.ldc + col : a.C + (size_t)row * a.ldc + col;
-            const bool biased = !WGRAD && a.bias != nullptr && row < a.bias_rows;
-#pragma unroll
-            for (int i = 0; i < NH; i += 4) {
-                float4 v = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-                if (biased) {
-                    const float4 b = *reinterpret_cast<const float4*>(a.bias + col + i);
-                    v.x += b.x;
-                    v.y += b.y;
-                    v.z += b.z;
-                    v.w += b.w;
+                    for (int j = 0; j < BN / 32; ++j)
+                        t2_tma_load(stage + T2_A_BYTES + j * 4096, &map_b, n0 + 32 * j, k0, full + s);
                 }
-                *reinterpret_cast<float4*>(out + i) = v;
+                if (++kt == k_tiles) {
+                    kt = 0;
+                    ++u;
+                    m0 = unit_m0(u);
+                    n0 = unit_n0(u);
+                }
             }
         }
+    } else if (warp == ISSUE_WARP) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = t2_idesc(BN, WGRAD);
+            for (int it = 0; it < items; ++it) {
+                const int s = it % T2_STAGES, b = it & 1;
+                mbar_wait(ready + b, (uint32_t)((it >> 1) & 1), a.error);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t ah = smem_u32(smem + s * G::STAGE_BYTES);
+                const uint32_t al = smem_u32(smem + G::LO_OFFSET + b * G::STAGE_BYTES);
+                const uint32_t bh = ah + T2_A_BYTES, bl = al + T2_A_BYTES;
+                const uint32_t dst = tmem_base + (uint32_t)(b * BN);
+                // k = 8 per instruction: 32 bytes along a K-major row, two 4-row groups (1024 bytes)
+                // of an MN-major atom.  The small correction products go first (they add onto a
+                // small accumulator without loss), the full-magnitude products last.
+                constexpr uint32_t STEP = WGRAD ? 1024 : 32;
+#pragma unroll
+                for (int kb = 0; kb < T2_BK / 8; ++kb) {
+                    const uint32_t o = kb * STEP;
+                    if (WGRAD) {
+                        tc_mma(dst, t2_desc_mnmajor(al + o), t2_desc_mnmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
+                        tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bl + o), idesc, 1u);
+                    } else {
+                        tc_mma(dst, t2_desc_kmajor(al + o), t2_desc_kmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
+                        tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bl + o), idesc, 1u);
+                    }
+                }
+#pragma unroll
+                for (int kb = 0; kb < T2_BK / 8; ++kb) {
+                    const uint32_t o = kb * STEP;
+                    if (WGRAD)
+                        tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bh + o), idesc, 1u);
+                    else
+                        tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bh + o), idesc, 1u);
+                }
+                tc_commit(done + b);
+                tc_commit(empty + s);
+            }
+        }
+    } else {
+        // ------------------------------ consumers ------------------------------
+        const int half = warp >> 2;  // which BN/2 columns this thread drains
+        const uint32_t my_tmem = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * NH);
+        const int trow = (warp & 3) * 32 + lane;  // accumulator lane = output row within the tile
+        float acc[NH];
 #pragma unroll
         for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
-    };
 
-    for (int it = 0; it < items; ++it) {
-        const int s = it % T2_STAGES, b = it & 1;
-        unsigned char* const hi = smem + s * G::STAGE_BYTES;
-        unsigned char* const lo = smem + G::LO_OFFSET + b * G::STAGE_BYTES;
-        mbar_wait(full + s, (uint32_t)((it / T2_STAGES) & 1), a.error);
-        // lo = tf32(x - hi) at the same offsets.  The lo buffer and the accumulator buffer b were
-        // last used by item it-2, whose completion every thread saw in the previous iteration.
-#pragma unroll
-        for (int i = 0; i < G::VECTORS / T2_THREADS; ++i) {
-            const int v = tid + i * T2_THREADS;
-            const uint4 x = *reinterpret_cast<const uint4*>(hi + 16 * v);
-            uint4 l;
-            uint32_t h;
-            split_tf32(__uint_as_float(x.x), h, l.x);
-            split_tf32(__uint_as_float(x.y), h, l.y);
-            split_tf32(__uint_as_float(x.z), h, l.z);
-            split_tf32(__uint_as_float(x.w), h, l.w);
-            *reinterpret_cast<uint4*>(lo + 16 * v) = l;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
+        // Partial of item q: wait for its instructions, add its buffer into the registers.
+        auto drain = [&](int q) {
+            mbar_wait(done + (q & 1), (uint32_t)((q >> 1) & 1), a.error);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t ah = smem_u32(hi), al = smem_u32(lo);
-            const uint32_t bh = ah + T2_A_BYTES, bl = al + T2_A_BYTES;
-            const uint32_t dst = tmem_base + (uint32_t)(b * BN);
-            // k = 8 per instruction: 32 bytes along a K-major row, one 8-row group (1024 bytes) of
-            // an MN-major atom.  The small correction products go first (they add onto a small
-            // accumulator without loss), the full-magnitude products last.
-            constexpr uint32_t STEP = WGRAD ? 1024 : 32;
+            const uint32_t src = my_tmem + (uint32_t)((q & 1) * BN);
 #pragma unroll
-            for (int kb = 0; kb < T2_BK / 8; ++kb) {
-                const uint32_t o = kb * STEP;
-                if (WGRAD) {
-                    tc_mma(dst, t2_desc_mnmajor(al + o), t2_desc_mnmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
-                    tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bl + o), idesc, 1u);
-                } else {
-                    tc_mma(dst, t2_desc_kmajor(al + o), t2_desc_kmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
-                    tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bl + o), idesc, 1u);
+            for (int c = 0; c < NH / 32; ++c) {
+                float v[32];
+                tc_load32(src + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        };
+        // Output of unit u from the registers: thread = (row, half of the columns).
+        auto write_out = [&](int u) {
+            const int row = unit_m0(u) + trow, col = unit_n0(u) + half * NH;
+            if (row < a.M) {
+                float* out = WGRAD ? a.C + ((size_t)blockIdx.x * a.M + row) * a.ldc + col : a.C + (size_t)row * a.ldc + col;
+                const bool biased = !WGRAD && a.bias != nullptr && row < a.bias_rows;
+#pragma unroll
+                for (int i = 0; i < NH; i += 4) {
+                    float4 v = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                    if (biased) {
+                        const float4 bv = *reinterpret_cast<const float4*>(a.bias + col + i);
+                        v.x += bv.x;
+                        v.y += bv.y;
+                        v.z += bv.z;
+                        v.w += bv.w;
+                    }
+                    *reinterpret_cast<float4*>(out + i) = v;
                 }
             }
 #pragma unroll
-            for (int kb = 0; kb < T2_BK / 8; ++kb) {
-                const uint32_t o = kb * STEP;
-                if (WGRAD)
-                    tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bh + o), idesc, 1u);
-                else
-                    tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bh + o), idesc, 1u);
+            for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
+        };
+
+        for (int it = 0; it < items; ++it) {
+            const int s = it % T2_STAGES, b = it & 1;
+            const unsigned char* hi = smem + s * G::STAGE_BYTES;
+            unsigned char* lo = smem + G::LO_OFFSET + b * G::STAGE_BYTES;
+            mbar_wait(full + s, (uint32_t)((it / T2_STAGES) & 1), a.error);
+            // The lo buffer b was last read by item it-2, which this thread has drained.
+#pragma unroll
+            for (int i = 0; i < G::VECTORS / T2_THREADS; ++i) {
+                const int v = tid + i * T2_THREADS;
+                const uint4 x = *reinterpret_cast<const uint4*>(hi + 16 * v);
+                *reinterpret_cast<uint4*>(lo + 16 * v) =
+                    make_uint4(t2_lo_bits(x.x), t2_lo_bits(x.y), t2_lo_bits(x.z), t2_lo_bits(x.w));
             }
-            tc_commit(done + b);
-        }
-        if (it >= 1) {
-            drain(it - 1);  // overlaps with the instructions just issued
-            // Item it-1 is complete: its stage can take the item T2_STAGES further on.
-            if (tid == 0 && produced < items) {
-                produce(produced);
-                ++produced;
+            // Generic-proxy writes must be visible to the tensor core (async proxy) before the
+            // issuer is told; the tcgen05 fence orders the drain of item it-2 before that too.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            t2_arrive(ready + b);
+            if (it >= 1) {
+                drain(it - 1);
+                if (it % k_tiles == 0) write_out(it / k_tiles - 1);  // item it-1 closed a unit
             }
-            if (it % k_tiles == 0) write_out(it / k_tiles - 1);  // item it-1 closed a unit
         }
-    }
-    if (items > 0) {
-        drain(items - 1);
-        write_out(units - 1);
+        if (items > 0) {
+            drain(items - 1);
+            write_out(units - 1);
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
+    if (warp == ISSUE_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
     }
 }
