@@ -92,10 +92,14 @@ __global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restric
     }
 }
 
-// In place: G (cotangents of H) becomes the cotangents of Z.
-template <typename T, int CODE>
+// In place: G (cotangents of H) becomes the cotangents of Z.  With HEAD the incoming cotangents are
+// not read but formed on the fly as Uhat[s][point] * w_head[unit] (the head layer's data gradient),
+// which saves writing and re-reading that [S][C][d] array.
+template <typename T, int CODE, bool HEAD>
 __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
-                                                               T* __restrict__ G, long long plane) {
+                                                               T* __restrict__ G, long long plane,
+                                                               const T* __restrict__ Uhat, const T* __restrict__ w_head,
+                                                               int d, long long C) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
@@ -108,14 +112,25 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
         for (int s = 0; s < S; ++s) {
             // The transposed composition never reads z_0 itself (t replaces it).
             if (s > 0) qz[s] = reinterpret_cast<const VT*>(Z + (long long)s * plane)[e];
-            qg[s] = reinterpret_cast<const VT*>(G + (long long)s * plane)[e];
+            if (!HEAD) qg[s] = reinterpret_cast<const VT*>(G + (long long)s * plane)[e];
         }
         T t[V], zl[S][V], gl[S][V];
         JV::unpack(qt, t);
+        if (HEAD) {
+            const long long elem = e * V, point = elem / d;
+            T wv[V];
+            JV::unpack(reinterpret_cast<const VT*>(w_head)[(elem - point * d) / V], wv);
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                const T u = Uhat[(long long)s * C + point];
+#pragma unroll
+                for (int i = 0; i < V; ++i) gl[s][i] = u * wv[i];
+            }
+        }
 #pragma unroll
         for (int s = 0; s < S; ++s) {
             if (s > 0) JV::unpack(qz[s], zl[s]);
-            JV::unpack(qg[s], gl[s]);
+            if (!HEAD) JV::unpack(qg[s], gl[s]);
         }
 #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -163,18 +178,35 @@ inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, 
     }
 }
 
+template <typename T, bool HEAD>
+inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
+                                         const T* w_head, int d, long long C, cudaStream_t stream) {
+    const int grid = jet_sig_grid(plane / JetVec<T>::V);
+#define QB_JET_BWD(CODE) \
+    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C)
+    switch (code) {
+        case 0: QB_JET_BWD(0); break;
+        case 1: QB_JET_BWD(1); break;
+        case 2: QB_JET_BWD(2); break;
+        case 4: QB_JET_BWD(4); break;
+        case 7: QB_JET_BWD(7); break;
+        case 12: QB_JET_BWD(12); break;
+        default: QB_JET_BWD(187); break;
+    }
+#undef QB_JET_BWD
+}
+
 template <typename T>
 inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, cudaStream_t stream) {
-    const int grid = jet_sig_grid(plane / JetVec<T>::V);
-    switch (code) {
-        case 0: jet_backward_sig_kernel<T, 0><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
-        case 1: jet_backward_sig_kernel<T, 1><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
-        case 2: jet_backward_sig_kernel<T, 2><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
-        case 4: jet_backward_sig_kernel<T, 4><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
-        case 7: jet_backward_sig_kernel<T, 7><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
-        case 12: jet_backward_sig_kernel<T, 12><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
-        default: jet_backward_sig_kernel<T, 187><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane); break;
-    }
+    jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, 1, 1, stream);
+}
+
+// Last hidden layer: the cotangents of H are Uhat (x) w_head, formed inside the kernel; d % V == 0
+// and w_head 16-byte aligned are the caller's to check.
+template <typename T>
+inline void jet_backward_head_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
+                                     const T* w_head, int d, long long C, cudaStream_t stream) {
+    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, stream);
 }
 
 }  // namespace qb

@@ -114,6 +114,39 @@ __global__ void __launch_bounds__(256) gemm_kernel(GemmArgs<T> g) {
     }
 }
 
+// Weight gradient with one narrow side (the first layer's d_in <= 8 coordinates, the head's single
+// output): P[z][m][n] = sum over the rows r of slice z of A[r][m] * B[r][n].  One thread per element
+// of the wide side streams its column (coalesced across the CTA) and keeps NARROW accumulators; the
+// narrow operand is a broadcast load.  HBM-bound: the wide matrix is read once.
+template <typename T, int NARROW, bool NARROW_A>
+__global__ void __launch_bounds__(256) skinny_wgrad_kernel(const T* __restrict__ A, const T* __restrict__ B,
+                                                           T* __restrict__ P, long long rows, int M, int N, int k_chunk) {
+    const int wide = NARROW_A ? N : M;
+    const int col = blockIdx.x * 256 + threadIdx.x;
+    if (col >= wide) return;
+    const T* __restrict__ wide_ptr = NARROW_A ? B : A;
+    const T* __restrict__ narrow_ptr = NARROW_A ? A : B;
+    const long long r0 = (long long)blockIdx.y * k_chunk;
+    const long long r1 = min(rows, r0 + (long long)k_chunk);
+    T acc[NARROW];
+#pragma unroll
+    for (int i = 0; i < NARROW; ++i) acc[i] = T(0);
+#pragma unroll 8
+    for (long long r = r0; r < r1; ++r) {
+        const T w = wide_ptr[r * wide + col];
+#pragma unroll
+        for (int i = 0; i < NARROW; ++i) acc[i] += narrow_ptr[r * NARROW + i] * w;
+    }
+    T* out = P + (long long)blockIdx.y * M * N;
+#pragma unroll
+    for (int i = 0; i < NARROW; ++i) {
+        if (NARROW_A)
+            out[(long long)i * N + col] = acc[i];
+        else
+            out[(long long)col * N + i] = acc[i];
+    }
+}
+
 // Column sums of the first `rows` rows of G[rows][N] (bias gradients), split
 // over rows: slice z writes partial[z][n].
 template <typename T>

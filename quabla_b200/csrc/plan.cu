@@ -269,6 +269,7 @@ class Plan final : public qb200_plan {
     int64_t steps_ = 0;
     bool executed_ = false;
     bool moments_ready_ = false;
+    size_t wpartial_elems_ = 0;  // capacity of wpartial_ in elements
     double dp_scale_ = 1.0;
     ncclComm_t comm_ = nullptr;
     int world_ = 1;
@@ -487,6 +488,7 @@ qb200_status Plan<T>::init() {
     // Weight-gradient slices, or the (at most BIAS_SLICES) row slices of a bias gradient.
     const size_t partial_elems = std::max(slices * std::max<size_t>(wmax, (size_t)dmax), (size_t)BIAS_SLICES * dmax);
     QB_TRY(dev_alloc(&wpartial_, partial_elems));
+    wpartial_elems_ = partial_elems;
     scratch_bytes_ += (2 * g_elems + 2 * max_rows + partial_elems) * sizeof(T);
     return QB200_OK;
 }
@@ -817,6 +819,32 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                 return launched("accumulate_partials_kernel");
             }
         }
+        if ((d_in <= 4 && d_out >= 32) || (d_out == 1 && d_in >= 32)) {
+            // One narrow side: stream the wide matrix once (HBM-bound) instead of a 64 x 64 tile GEMM.
+            const int count = d_in * d_out;
+            long long chunk = (rows + 4 * SM_COUNT - 1) / (4 * SM_COUNT);
+            chunk = std::min<long long>(K_CHUNK_ROWS, std::max<long long>(256, (chunk + 7) / 8 * 8));
+            const long long room = (long long)(wpartial_elems_ / (size_t)count);
+            if ((rows + chunk - 1) / chunk > room) chunk = ((rows + room - 1) / room + 7) / 8 * 8;
+            const int slices = (int)((rows + chunk - 1) / chunk);
+            if (chunk <= K_CHUNK_ROWS) {
+                const dim3 grid((std::max(d_in, d_out) + 255) / 256, slices);
+                if (d_out == 1)
+                    skinny_wgrad_kernel<T, 1, false><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                else if (d_in == 1)
+                    skinny_wgrad_kernel<T, 1, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                else if (d_in == 2)
+                    skinny_wgrad_kernel<T, 2, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                else if (d_in == 3)
+                    skinny_wgrad_kernel<T, 3, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                else
+                    skinny_wgrad_kernel<T, 4, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                QB_TRY(launched("skinny_wgrad_kernel"));
+                accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(
+                    wpartial_, d_acc_ + leaves_[leaf].offset, count, slices);
+                return launched("accumulate_partials_kernel");
+            }
+        }
         GemmArgs<T> g;
         g.A = Hprev;
         g.B = Gz;
@@ -862,12 +890,22 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     QB_TRY(wgrad(H_[head], Uhat_, sz[head], 1, w_leaf_[head], head));
     QB_TRY(bgrad(Uhat_, 1, b_leaf_[head]));
     int cur = 0;
-    head_backward_kernel<T><<<grid_for(rows * sz[head], 256), 256, 0, stream_>>>(Uhat_, weight(head), G_[cur], rows,
-                                                                                 sz[head]);
-    QB_TRY(launched("head_backward_kernel"));
+    // The head's data gradient G = Uhat (x) w is formed inside the last hidden layer's jet kernel when
+    // that kernel has a compile-time signature; otherwise it is materialised here.
+    const bool head_fused = head >= 1 && sz[head] % JetVec<T>::V == 0 &&
+                            jet_sig_eligible<T>(st.sig_code, (long long)C * sz[head], Z_[head], H_[head], G_[cur]) &&
+                            (reinterpret_cast<uintptr_t>(weight(head)) & 15) == 0;
+    if (!head_fused) {
+        head_backward_kernel<T><<<grid_for(rows * sz[head], 256), 256, 0, stream_>>>(Uhat_, weight(head), G_[cur], rows,
+                                                                                     sz[head]);
+        QB_TRY(launched("head_backward_kernel"));
+    }
     for (int l = head; l >= 1; --l) {
         const long long plane = (long long)C * sz[l];
-        if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], G_[cur]))
+        if (l == head && head_fused)
+            jet_backward_head_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, Uhat_, weight(head), sz[head], C,
+                                        stream_);
+        else if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], G_[cur]))
             jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, stream_);
         else
             jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec);
