@@ -116,3 +116,38 @@ def test_weight_gradient_on_the_tensor_cores(cuda_device, rows, d_in, d_out):
     expected = acts.double().T @ cots.double()
     error = (grad.double() - expected).abs().max().item() / expected.abs().max().item()
     assert error <= 2e-6
+
+
+@pytest.mark.parametrize("rows,d_in,d_out", [(20000, 128, 128), (5001, 256, 64), (33, 64, 128), (70000, 2, 128),
+                                             (70000, 128, 1)])
+def test_float64_weight_gradient_variants(cuda_device, rows, d_in, d_out):
+    # 128-wide shapes run on the FP64 tensor-core kernel, narrow sides on the SIMT kernel.
+    import torch
+
+    lib = _lib.load()
+    generator = torch.Generator(device="cuda").manual_seed(rows)
+    acts = torch.randn(rows, d_in, dtype=torch.float64, device="cuda", generator=generator)
+    cots = torch.randn(rows, d_out, dtype=torch.float64, device="cuda", generator=generator)
+    grad = torch.full((d_in, d_out), float("nan"), dtype=torch.float64, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.qb200_weight_gradient(_lib.F64, _ptr(acts), _ptr(cots), rows, d_in, d_out, _ptr(grad), stream))
+    torch.cuda.synchronize()
+    expected = (acts.T @ cots).cpu().numpy()
+    assert np.max(np.abs(grad.cpu().numpy() - expected)) <= 1e-14 * np.sqrt(rows) * 8
+
+
+@pytest.mark.parametrize("M,N,K", [(300000, 256, 256), (70001, 128, 64)])
+def test_matmul_3xtf32_over_many_tiles(cuda_device, M, N, K):
+    # Persistent CTAs walk several output tiles each; the stage ring runs across tile boundaries.
+    import torch
+
+    lib = _lib.load()
+    generator = torch.Generator(device="cuda").manual_seed(M)
+    a = torch.randn(M, K, device="cuda", generator=generator)
+    w = torch.randn(K, N, device="cuda", generator=generator) / K ** 0.5
+    c = torch.full((M, N), float("nan"), device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.qb200_matmul_3xtf32(_ptr(a), _ptr(w), None, _ptr(c), M, N, K, 0, stream))
+    expected = a.double() @ w.double()
+    error = (c.double() - expected).abs().max().item() / expected.abs().max().item()
+    assert error <= 2e-6
