@@ -34,10 +34,16 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
 
 // hi = x with the 13 low mantissa bits cleared (a valid tf32; the remainder x - hi is exact),
 // lo = that remainder ROUNDED to tf32.  Rounding matters: truncating lo leaves a one-sided
-// error of up to 2^-21 |x| that accumulates linearly over the contraction.
+// error of up to 2^-21 |x| that accumulates linearly over the contraction.  The tensor core
+// ignores the 13 low bits of an operand, so adding half a tf32 ulp (bit 12) to the remainder's
+// bit pattern rounds it to nearest with one integer add instead of a cvt.rna.tf32.
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
     hi = __float_as_uint(x) & 0xffffe000u;
+#ifdef QB_SPLIT_CVT
     lo = to_tf32(x - __uint_as_float(hi));
+#else
+    lo = __float_as_uint(x - __uint_as_float(hi)) + 0x1000u;
+#endif
 }
 
 // Four 8x8 matrices of 16-bit pairs = four 8x4 tiles of 32-bit words: thread (g, t) of the

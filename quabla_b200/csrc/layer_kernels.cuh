@@ -179,6 +179,7 @@ __global__ void accumulate_partials_kernel(const T* __restrict__ partial, double
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     double s = 0.0;
+#pragma unroll 8
     for (int z = 0; z < slices; ++z) s += (double)partial[(long long)z * count + i];
     acc[i] += s;
 }
@@ -189,6 +190,7 @@ __global__ void reduce_partials_kernel(const T* __restrict__ partial, T* __restr
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) return;
     double s = 0.0;
+#pragma unroll 8
     for (int z = 0; z < slices; ++z) s += (double)partial[(long long)z * count + i];
     out[i] = (T)s;
 }

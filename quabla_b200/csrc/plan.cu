@@ -822,8 +822,8 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         if ((d_in <= 4 && d_out >= 32) || (d_out == 1 && d_in >= 32)) {
             // One narrow side: stream the wide matrix once (HBM-bound) instead of a 64 x 64 tile GEMM.
             const int count = d_in * d_out;
-            long long chunk = (rows + 4 * SM_COUNT - 1) / (4 * SM_COUNT);
-            chunk = std::min<long long>(K_CHUNK_ROWS, std::max<long long>(256, (chunk + 7) / 8 * 8));
+            long long chunk = (rows + 2 * SM_COUNT - 1) / (2 * SM_COUNT);
+            chunk = std::min<long long>(K_CHUNK_ROWS, std::max<long long>(64, (chunk + 7) / 8 * 8));
             const long long room = (long long)(wpartial_elems_ / (size_t)count);
             if ((rows + chunk - 1) / chunk > room) chunk = ((rows + room - 1) / room + 7) / 8 * 8;
             const int slices = (int)((rows + chunk - 1) / chunk);

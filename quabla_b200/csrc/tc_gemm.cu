@@ -175,7 +175,7 @@ cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, f
     a.k_slice = rows_per_slice;
     a.error = error;
     const int slices = (rows + rows_per_slice - 1) / rows_per_slice;
-    const dim3 grid(slices, Mw / T2_BM, N / BN);
+    const dim3 grid(Mw / T2_BM, N / BN, slices);  // the tiles of one slice run together and share its rows in L2
     return BN == 128 ? launch2<true, 128>(ma, mb, a, grid, stream) : launch2<true, 64>(ma, mb, a, grid, stream);
 }
 

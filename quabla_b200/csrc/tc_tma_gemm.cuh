@@ -99,6 +99,19 @@ __device__ __forceinline__ uint32_t t2_lo_bits(uint32_t x) {
     return __float_as_uint(d) + 0x1000u;
 }
 
+// 32 lanes x 32 consecutive columns into registers; the caller waits (tcgen05.wait::ld) once for
+// all loads it issued.
+__device__ __forceinline__ void t2_load32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
 __device__ __forceinline__ void t2_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -159,7 +172,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     int units, k_tiles, k_begin = 0;
     if (WGRAD) {
         units = 1;
-        k_begin = blockIdx.x * a.k_slice;
+        k_begin = blockIdx.z * a.k_slice;
         const int k_end = min(a.K, k_begin + a.k_slice);
         k_tiles = (k_end - k_begin + T2_BK - 1) / T2_BK;
     } else {
@@ -168,8 +181,8 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     }
     const int items = units * k_tiles;
     // Tile coordinates of unit u of this CTA.
-    auto unit_m0 = [&](int u) { return WGRAD ? (int)blockIdx.y * T2_BM : (((int)blockIdx.x + u * (int)gridDim.x) / n_tiles) * T2_BM; };
-    auto unit_n0 = [&](int u) { return WGRAD ? (int)blockIdx.z * BN : (((int)blockIdx.x + u * (int)gridDim.x) % n_tiles) * BN; };
+    auto unit_m0 = [&](int u) { return WGRAD ? (int)blockIdx.x * T2_BM : (((int)blockIdx.x + u * (int)gridDim.x) / n_tiles) * T2_BM; };
+    auto unit_n0 = [&](int u) { return WGRAD ? (int)blockIdx.y * BN : (((int)blockIdx.x + u * (int)gridDim.x) % n_tiles) * BN; };
 
     if (warp == LOAD_WARP) {
         // ------------------------------ producer ------------------------------
@@ -254,32 +267,35 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             mbar_wait(done + (q & 1), (uint32_t)((q >> 1) & 1), a.error);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t src = my_tmem + (uint32_t)((q & 1) * BN);
+            uint32_t v[NH];
 #pragma unroll
-            for (int c = 0; c < NH / 32; ++c) {
-                float v[32];
-                tc_load32(src + c * 32, v);
+            for (int c = 0; c < NH / 32; ++c) t2_load32_nowait(src + c * 32, v + c * 32);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
-            }
+            for (int i = 0; i < NH; ++i) acc[i] += __uint_as_float(v[i]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         };
         // Output of unit u from the registers: thread = (row, half of the columns).
         auto write_out = [&](int u) {
             const int row = unit_m0(u) + trow, col = unit_n0(u) + half * NH;
             if (row < a.M) {
-                float* out = WGRAD ? a.C + ((size_t)blockIdx.x * a.M + row) * a.ldc + col : a.C + (size_t)row * a.ldc + col;
+                float* out = WGRAD ? a.C + ((size_t)blockIdx.z * a.M + row) * a.ldc + col : a.C + (size_t)row * a.ldc + col;
                 const bool biased = !WGRAD && a.bias != nullptr && row < a.bias_rows;
+                // 32 bytes per store: a thread writes whole sectors of its row.
 #pragma unroll
-                for (int i = 0; i < NH; i += 4) {
-                    float4 v = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                for (int i = 0; i < NH; i += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = acc[i + j];
                     if (biased) {
-                        const float4 bv = *reinterpret_cast<const float4*>(a.bias + col + i);
-                        v.x += bv.x;
-                        v.y += bv.y;
-                        v.z += bv.z;
-                        v.w += bv.w;
+                        const float4 b0 = *reinterpret_cast<const float4*>(a.bias + col + i);
+                        const float4 b1 = *reinterpret_cast<const float4*>(a.bias + col + i + 4);
+                        v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                        v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
                     }
-                    *reinterpret_cast<float4*>(out + i) = v;
+                    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out + i), "f"(v[0]),
+                                 "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+                                 : "memory");
                 }
             }
 #pragma unroll
