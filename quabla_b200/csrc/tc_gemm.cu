@@ -128,20 +128,22 @@ cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaSt
 }
 
 template <bool WGRAD, int BN>
-static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const TcTmaArgs& a, dim3 grid, cudaStream_t stream) {
+static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcTmaArgs& a,
+                           dim3 grid, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN>),
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, T2Geom<BN>::SMEM_BYTES);
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, T2Geom<WGRAD, BN>::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    tc_tma_gemm_kernel<WGRAD, BN><<<grid, T2_THREADS_TOTAL, T2Geom<BN>::SMEM_BYTES, stream>>>(ma, mb, a);
+    tc_tma_gemm_kernel<WGRAD, BN><<<grid, T2_THREADS_TOTAL, T2Geom<WGRAD, BN>::SMEM_BYTES, stream>>>(ma, mb, mc, a);
     return cudaGetLastError();
 }
 
 cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, int ldb, float* C, int ldc, const float* bias,
                             int bias_rows, int M, int N, int K, int* error, cudaStream_t stream) {
     const int BN = N % 128 == 0 ? 128 : 64;
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mb, mc;
     if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+        !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&mc, C, M, N, ldc, 32, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     TcTmaArgs a;
     memset(&a, 0, sizeof(a));
@@ -155,15 +157,17 @@ cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, int ldb, f
     a.units = ((M + T2_BM - 1) / T2_BM) * (N / BN);
     a.error = error;
     const dim3 grid(a.units < 148 ? a.units : 148);
-    return BN == 128 ? launch2<false, 128>(ma, mb, a, grid, stream) : launch2<false, 64>(ma, mb, a, grid, stream);
+    return BN == 128 ? launch2<false, 128>(ma, mb, mc, a, grid, stream) : launch2<false, 64>(ma, mb, mc, a, grid, stream);
 }
 
 cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,
                              int rows_per_slice, int* error, cudaStream_t stream) {
     const int BN = N % 128 == 0 ? 128 : 64;
-    CUtensorMap ma, mb;
+    const int slices = (rows + rows_per_slice - 1) / rows_per_slice;
+    CUtensorMap ma, mb, mc;
     if (!make_map(&ma, H, rows, Mw, ldh, 32, T2_BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) ||
-        !make_map(&mb, G, rows, N, ldg, 32, T2_BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+        !make_map(&mb, G, rows, N, ldg, 32, T2_BK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) ||
+        !make_map(&mc, partials, (long long)slices * Mw, N, N, 32, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     TcTmaArgs a;
     memset(&a, 0, sizeof(a));
@@ -174,9 +178,8 @@ cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, f
     a.ldc = N;
     a.k_slice = rows_per_slice;
     a.error = error;
-    const int slices = (rows + rows_per_slice - 1) / rows_per_slice;
     const dim3 grid(Mw / T2_BM, N / BN, slices);  // the tiles of one slice run together and share its rows in L2
-    return BN == 128 ? launch2<true, 128>(ma, mb, a, grid, stream) : launch2<true, 64>(ma, mb, a, grid, stream);
+    return BN == 128 ? launch2<true, 128>(ma, mb, mc, a, grid, stream) : launch2<true, 64>(ma, mb, mc, a, grid, stream);
 }
 
 }  // namespace qb

@@ -49,14 +49,21 @@ struct TcTmaArgs {
     int* error;
 };
 
-template <int BN>
+template <bool WGRAD, int BN>
 struct T2Geom {
     static constexpr int B_BYTES = BN * T2_BK * 4;
     static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES;            // multiple of 1024
     static constexpr int LO_OFFSET = T2_STAGES * STAGE_BYTES;
-    static constexpr int BAR_OFFSET = LO_OFFSET + 2 * STAGE_BYTES;
+    // ROWS keeps the activation operand in tensor memory, so only the weight tile has a lo plane here.
+    static constexpr int LO_BYTES = WGRAD ? STAGE_BYTES : B_BYTES;
+    // Output staging for the tensor-map store: BN/32 boxes of [128 rows][128 bytes].  WGRAD writes
+    // once, after its last MMA, and reuses the stage ring; ROWS overlaps the store with the next tile.
+    static constexpr int OUT_BYTES = T2_BM * BN * 4;
+    static constexpr int OUT_OFFSET = WGRAD ? 0 : LO_OFFSET + 2 * LO_BYTES;
+    static constexpr int BAR_OFFSET = LO_OFFSET + 2 * LO_BYTES + (WGRAD ? 0 : OUT_BYTES);
     static constexpr int SMEM_BYTES = BAR_OFFSET + 128 + 1024;          // barriers, TMEM slot, alignment slack
     static constexpr int VECTORS = STAGE_BYTES / 16;                    // 16-byte vectors per stage
+    static_assert(!WGRAD || OUT_BYTES <= LO_OFFSET, "the output staging must fit in the stage ring");
 };
 
 // Matrix descriptors for 128-byte-swizzled operand tiles (descriptor version 1, layout type 2).
@@ -112,6 +119,28 @@ __device__ __forceinline__ void t2_load32_nowait(uint32_t taddr, uint32_t* r) {
         : "r"(taddr));
 }
 
+// 32 lanes x 16 consecutive columns from registers into tensor memory (thread i writes lane base + i).
+__device__ __forceinline__ void t2_store16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// D (+)= A * B with A [128 lanes][8 columns] in tensor memory and B described in shared memory.
+__device__ __forceinline__ void t2_mma_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
 __device__ __forceinline__ void t2_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -128,8 +157,9 @@ __device__ __forceinline__ void t2_arrive(uint64_t* bar) {
 // also tells the issuer that accumulator buffer `buf` is free.
 template <bool WGRAD, int BN>
 __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
-    tc_tma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcTmaArgs a) {
-    typedef T2Geom<BN> G;
+    tc_tma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_c, TcTmaArgs a) {
+    typedef T2Geom<WGRAD, BN> G;
     extern __shared__ unsigned char t2_smem_raw[];
     // Swizzled tiles need 1024-byte alignment.
     unsigned char* const smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t2_smem_raw) + 1023) &
@@ -140,7 +170,11 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     uint64_t* const ready = empty + T2_STAGES;                                 // [2]
     uint64_t* const done = ready + 2;                                          // [2]
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
-    constexpr int TMEM_COLS = 2 * BN;  // two accumulator buffers; a power of two >= 32
+    // ROWS keeps the activation operand (hi and lo, 32 columns each, two buffers) in tensor memory
+    // behind the two accumulator buffers, so an MMA reads only the weight operand from shared memory.
+    constexpr bool A_TMEM = !WGRAD;
+    constexpr int A_COL0 = 2 * BN;                               // first column of the operand buffers
+    constexpr int TMEM_COLS = A_TMEM ? (BN == 128 ? 512 : 256) : 2 * BN;  // a power of two >= 32
     constexpr int NH = BN / 2;         // columns drained by one consumer thread
     constexpr int ISSUE_WARP = T2_THREADS / 32 + 1, LOAD_WARP = T2_THREADS / 32;
 
@@ -223,8 +257,8 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                 mbar_wait(ready + b, (uint32_t)((it >> 1) & 1), a.error);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ah = smem_u32(smem + s * G::STAGE_BYTES);
-                const uint32_t al = smem_u32(smem + G::LO_OFFSET + b * G::STAGE_BYTES);
-                const uint32_t bh = ah + T2_A_BYTES, bl = al + T2_A_BYTES;
+                const uint32_t al = smem_u32(smem + G::LO_OFFSET + b * G::LO_BYTES);  // WGRAD only: lo of A, then of B
+                const uint32_t bh = ah + T2_A_BYTES, bl = WGRAD ? al + T2_A_BYTES : al;
                 const uint32_t dst = tmem_base + (uint32_t)(b * BN);
                 // k = 8 per instruction: 32 bytes along a K-major row, two 4-row groups (1024 bytes)
                 // of an MN-major atom.  The small correction products go first (they add onto a
@@ -237,8 +271,9 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                         tc_mma(dst, t2_desc_mnmajor(al + o), t2_desc_mnmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
                         tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bl + o), idesc, 1u);
                     } else {
-                        tc_mma(dst, t2_desc_kmajor(al + o), t2_desc_kmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
-                        tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bl + o), idesc, 1u);
+                        const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + b * 64 + kb * 8);  // hi; lo is 32 columns on
+                        t2_mma_tmem_a(dst, ta + 32, t2_desc_kmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
+                        t2_mma_tmem_a(dst, ta, t2_desc_kmajor(bl + o), idesc, 1u);
                     }
                 }
 #pragma unroll
@@ -247,7 +282,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                     if (WGRAD)
                         tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bh + o), idesc, 1u);
                     else
-                        tc_mma(dst, t2_desc_kmajor(ah + o), t2_desc_kmajor(bh + o), idesc, 1u);
+                        t2_mma_tmem_a(dst, tmem_base + (uint32_t)(A_COL0 + b * 64 + kb * 8), t2_desc_kmajor(bh + o), idesc, 1u);
                 }
                 tc_commit(done + b);
                 tc_commit(empty + s);
@@ -275,45 +310,87 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             for (int i = 0; i < NH; ++i) acc[i] += __uint_as_float(v[i]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         };
-        // Output of unit u from the registers: thread = (row, half of the columns).
+        // Output of unit u: registers -> staging in shared memory (boxes of [128 rows][32 columns],
+        // 128-byte swizzle: chunk c of row r at c ^ (r & 7), conflict-free for a warp's 32 rows) ->
+        // one tensor-map store per box, issued by one thread and left in flight while the next
+        // unit's k-tiles run.  Rows outside the matrix are clipped by the store.
+        unsigned char* const staging = smem + G::OUT_OFFSET;
         auto write_out = [&](int u) {
-            const int row = unit_m0(u) + trow, col = unit_n0(u) + half * NH;
-            if (row < a.M) {
-                float* out = WGRAD ? a.C + ((size_t)blockIdx.z * a.M + row) * a.ldc + col : a.C + (size_t)row * a.ldc + col;
-                const bool biased = !WGRAD && a.bias != nullptr && row < a.bias_rows;
-                // 32 bytes per store: a thread writes whole sectors of its row.
+            if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging is free again
+            asm volatile("bar.sync 1, %0;" ::"n"(T2_THREADS) : "memory");
+            const int m0 = unit_m0(u), n0 = unit_n0(u);
+            const bool biased = !WGRAD && a.bias != nullptr && m0 + trow < a.bias_rows;
 #pragma unroll
-                for (int i = 0; i < NH; i += 8) {
-                    float v[8];
+            for (int j = 0; j < NH / 32; ++j) {
+                unsigned char* box = staging + (half * (NH / 32) + j) * (T2_BM * 128) + trow * 128;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = acc[i + j];
+                for (int c = 0; c < 8; ++c) {
+                    float4 v = make_float4(acc[j * 32 + 4 * c], acc[j * 32 + 4 * c + 1], acc[j * 32 + 4 * c + 2],
+                                           acc[j * 32 + 4 * c + 3]);
                     if (biased) {
-                        const float4 b0 = *reinterpret_cast<const float4*>(a.bias + col + i);
-                        const float4 b1 = *reinterpret_cast<const float4*>(a.bias + col + i + 4);
-                        v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                        v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                        const float4 bv = *reinterpret_cast<const float4*>(a.bias + n0 + half * NH + j * 32 + 4 * c);
+                        v.x += bv.x;
+                        v.y += bv.y;
+                        v.z += bv.z;
+                        v.w += bv.w;
                     }
-                    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out + i), "f"(v[0]),
-                                 "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
-                                 : "memory");
+                    *reinterpret_cast<float4*>(box + ((c ^ (trow & 7)) << 4)) = v;
                 }
             }
 #pragma unroll
             for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(T2_THREADS) : "memory");
+            if (tid == 0) {
+                const int y = WGRAD ? (int)blockIdx.z * a.M + m0 : m0;
+#pragma unroll
+                for (int j = 0; j < BN / 32; ++j)
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c),
+                                 "r"(n0 + 32 * j), "r"(y), "r"(smem_u32(staging + j * (T2_BM * 128)))
+                                 : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
         };
 
         for (int it = 0; it < items; ++it) {
             const int s = it % T2_STAGES, b = it & 1;
             const unsigned char* hi = smem + s * G::STAGE_BYTES;
-            unsigned char* lo = smem + G::LO_OFFSET + b * G::STAGE_BYTES;
+            unsigned char* lo = smem + G::LO_OFFSET + b * G::LO_BYTES;
             mbar_wait(full + s, (uint32_t)((it / T2_STAGES) & 1), a.error);
             // The lo buffer b was last read by item it-2, which this thread has drained.
+            if (A_TMEM) {
+                // Activation tile: this thread's row (its accumulator lane), 16 of the 32 k (by column
+                // half), read through the 128-byte swizzle (chunk c of row r sits at c ^ (r & 7)) and
+                // written, hi and lo, to the operand buffer b in tensor memory.
+                uint32_t xh[16], xl[16];
 #pragma unroll
-            for (int i = 0; i < G::VECTORS / T2_THREADS; ++i) {
-                const int v = tid + i * T2_THREADS;
-                const uint4 x = *reinterpret_cast<const uint4*>(hi + 16 * v);
-                *reinterpret_cast<uint4*>(lo + 16 * v) =
-                    make_uint4(t2_lo_bits(x.x), t2_lo_bits(x.y), t2_lo_bits(x.z), t2_lo_bits(x.w));
+                for (int c = 0; c < 4; ++c) {
+                    const int chunk = (half * 4 + c) ^ (trow & 7);
+                    const uint4 x = *reinterpret_cast<const uint4*>(hi + trow * 128 + chunk * 16);
+                    xh[4 * c + 0] = x.x; xh[4 * c + 1] = x.y; xh[4 * c + 2] = x.z; xh[4 * c + 3] = x.w;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) xl[i] = t2_lo_bits(xh[i]);
+                const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(A_COL0 + b * 64 + half * 16);
+                t2_store16(ta, xh);
+                t2_store16(ta + 32, xl);
+                // Weight tile: lo plane in shared memory, element by element.
+#pragma unroll
+                for (int i = 0; i < (G::B_BYTES / 16) / T2_THREADS; ++i) {
+                    const int v = tid + i * T2_THREADS;
+                    const uint4 x = *reinterpret_cast<const uint4*>(hi + T2_A_BYTES + 16 * v);
+                    *reinterpret_cast<uint4*>(lo + 16 * v) =
+                        make_uint4(t2_lo_bits(x.x), t2_lo_bits(x.y), t2_lo_bits(x.z), t2_lo_bits(x.w));
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int i = 0; i < G::VECTORS / T2_THREADS; ++i) {
+                    const int v = tid + i * T2_THREADS;
+                    const uint4 x = *reinterpret_cast<const uint4*>(hi + 16 * v);
+                    *reinterpret_cast<uint4*>(lo + 16 * v) =
+                        make_uint4(t2_lo_bits(x.x), t2_lo_bits(x.y), t2_lo_bits(x.z), t2_lo_bits(x.w));
+                }
             }
             // Generic-proxy writes must be visible to the tensor core (async proxy) before the
             // issuer is told; the tcgen05 fence orders the drain of item it-2 before that too.
@@ -329,6 +406,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             drain(items - 1);
             write_out(units - 1);
         }
+        if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // stores complete before exit
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
