@@ -114,6 +114,43 @@ __global__ void __launch_bounds__(256) gemm_kernel(GemmArgs<T> g) {
     }
 }
 
+// Forward product with a narrow contraction (the first layer: K = network inputs <= 4):
+// C[row][n] = sum_{j<K} A[row][j] * W[j][n] (+ bias[n] on rows < bias_rows).  A thread owns four
+// consecutive columns and keeps its 4 K weights in registers; a row's A values are a broadcast load.
+// HBM-bound on the write of C.
+template <typename T, int K>
+__global__ void __launch_bounds__(256) skinny_forward_kernel(const T* __restrict__ A, const T* __restrict__ W,
+                                                             const T* __restrict__ bias, T* __restrict__ C,
+                                                             long long rows, int N, int bias_rows) {
+    const int groups = N / 4;                       // column groups of four per row
+    const int group = threadIdx.x % groups;         // blockDim.x is a multiple of groups
+    const int rows_per_block = blockDim.x / groups;
+    T w[K][4], b[4];
+#pragma unroll
+    for (int j = 0; j < K; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[j][i] = W[(long long)j * N + 4 * group + i];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) b[i] = bias != nullptr ? bias[4 * group + i] : T(0);
+    for (long long row = (long long)blockIdx.x * rows_per_block + threadIdx.x / groups; row < rows;
+         row += (long long)gridDim.x * rows_per_block) {
+        T a[K], v[4];
+#pragma unroll
+        for (int j = 0; j < K; ++j) a[j] = A[row * K + j];
+        const bool biased = row < bias_rows;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            T sum = T(0);
+#pragma unroll
+            for (int j = 0; j < K; ++j) sum += a[j] * w[j][i];
+            v[i] = biased ? sum + b[i] : sum;
+        }
+        T* out = C + row * N + 4 * group;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[i] = v[i];
+    }
+}
+
 // Weight gradient with one narrow side (the first layer's d_in <= 8 coordinates, the head's single
 // output): P[z][m][n] = sum over the rows r of slice z of A[r][m] * B[r][n].  One thread per element
 // of the wide side streams its column (coalesced across the CTA) and keeps NARROW accumulators; the

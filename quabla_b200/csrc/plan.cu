@@ -782,6 +782,17 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         qb200_status tc_status = QB200_OK;
         if (tc_forward(l - 1, H_[l - 1], Z_[l], rows, C, &tc_status)) {
             QB_TRY(tc_status);
+        } else if (g.K <= 4 && g.N % 4 == 0 && g.N >= 32 && 256 % (g.N / 4) == 0) {
+            // Narrow contraction (the first layer): stream the output once.
+            const int rows_per_block = 256 / (g.N / 4);
+            const int grid = (int)std::min<long long>((rows + rows_per_block - 1) / rows_per_block, 148 * 16);
+            switch (g.K) {
+                case 1: skinny_forward_kernel<T, 1><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+                case 2: skinny_forward_kernel<T, 2><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+                case 3: skinny_forward_kernel<T, 3><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+                default: skinny_forward_kernel<T, 4><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+            }
+            QB_TRY(launched("skinny_forward_kernel"));
         } else {
             const cudaError_t e = gemm_launch<T, true, true>(g, 1, stream_);
             (void)e;  // launched() reads the launch status
@@ -822,7 +833,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         if ((d_in <= 4 && d_out >= 32) || (d_out == 1 && d_in >= 32)) {
             // One narrow side: stream the wide matrix once (HBM-bound) instead of a 64 x 64 tile GEMM.
             const int count = d_in * d_out;
-            long long chunk = (rows + 2 * SM_COUNT - 1) / (2 * SM_COUNT);
+            long long chunk = (rows + 8 * SM_COUNT - 1) / (8 * SM_COUNT);
             chunk = std::min<long long>(K_CHUNK_ROWS, std::max<long long>(64, (chunk + 7) / 8 * 8));
             const long long room = (long long)(wpartial_elems_ / (size_t)count);
             if ((rows + chunk - 1) / chunk > room) chunk = ((rows + room - 1) / room + 7) / 8 * 8;
@@ -872,10 +883,10 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     };
     auto bgrad = [&](const T* Gz, int d_out, int leaf) -> qb200_status {
         if (leaf < 0) return QB200_OK;
-        // About two CTAs per SM over (column blocks x row slices); a slice never drops below
+        // About eight CTAs per SM over (column blocks x row slices); a slice never drops below
         // 256 rows, so the slice count depends on the sizes only and the sum order is fixed.
         const int col_blocks = (d_out + 31) / 32;
-        const int want = std::min(BIAS_SLICES, std::max(1, (2 * 148 + col_blocks - 1) / col_blocks));
+        const int want = std::min(BIAS_SLICES, std::max(1, (8 * 148 + col_blocks - 1) / col_blocks));
         const int row_chunk = std::max(256, ((C + want - 1) / want + 7) / 8 * 8);
         const int slices = (C + row_chunk - 1) / row_chunk;
         dim3 grid(col_blocks, slices);
