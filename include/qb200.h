@@ -193,6 +193,16 @@ qb200_status qb200_plan_loss(qb200_plan* plan, void* host_scalar);
 /* retained_input_to_host (cuda.rs:1451-1489). */
 qb200_status qb200_plan_read_input(qb200_plan* plan, const char* name, void* host, size_t nbytes);
 
+/* Resamples column `column` of the data input `name` on the device, without a host copy:
+ * element i becomes the i-th value of random_uniform([rows], key, minval, maxval, plan dtype)
+ * (crates/quabla-python/src/tensor.rs:1482-1534 on the SplitMix64 stream of tensor.rs:327-333;
+ * python/quabla/random.py:119-129), bit for bit.  Stands where a training loop re-draws its
+ * collocation batch on the host and uploads it (batch_argnums of optim.Trainer,
+ * python/quabla/optim.py:458-487).  Counts as binding the input; other columns keep their
+ * values (zero if the input was never bound). */
+qb200_status qb200_plan_sample_uniform(qb200_plan* plan, const char* name, int32_t column, uint64_t key,
+                                       double minval, double maxval);
+
 /* Optimizer moments, which the reference keeps private to the device trainer:
  * which = 0 first moment, 1 second moment; all leaves flat in parameter order. */
 qb200_status qb200_plan_read_moments(qb200_plan* plan, int32_t which, void* host, size_t nbytes);

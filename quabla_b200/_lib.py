@@ -80,6 +80,7 @@ SIGNATURES = {
     "qb200_plan_optimizer_step": (_I32, [_P, C.POINTER(OptConfig)]),
     "qb200_plan_loss": (_I32, [_P, _P]),
     "qb200_plan_read_input": (_I32, [_P, C.c_char_p, _P, C.c_size_t]),
+    "qb200_plan_sample_uniform": (_I32, [_P, C.c_char_p, _I32, C.c_uint64, C.c_double, C.c_double]),
     "qb200_plan_read_moments": (_I32, [_P, _I32, _P, C.c_size_t]),
     "qb200_plan_write_moments": (_I32, [_P, _I32, _P, C.c_size_t, _I64]),
     "qb200_plan_query": (_I32, [_P, _I32, C.POINTER(_I64)]),

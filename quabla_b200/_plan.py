@@ -175,6 +175,13 @@ class Plan:
         _lib.check(self._lib.qb200_plan_read_input(self._handle, name.encode(), out.ctypes.data, out.nbytes))
         return out
 
+    def sample_uniform(self, name: str, column: int, key, minval: float = 0.0, maxval: float = 1.0) -> None:
+        """Resample one column of a data input on the device: the values of
+        random.uniform(key, (rows,), dtype, minval, maxval), bit for bit, with no host copy."""
+        value = getattr(key, "value", key)
+        _lib.check(self._lib.qb200_plan_sample_uniform(self._handle, name.encode(), int(column),
+                                                       int(value) & 0xFFFFFFFFFFFFFFFF, float(minval), float(maxval)))
+
     def read_parameter(self, index: int) -> np.ndarray:
         return self.read_input(self.spec.parameters[index][0], self.spec.parameter_shape(index))
 

@@ -341,6 +341,12 @@ qb200_status qb200_plan_read_input(qb200_plan* plan, const char* name, void* hos
     return plan->read_input(name, host, nbytes);
 }
 
+qb200_status qb200_plan_sample_uniform(qb200_plan* plan, const char* name, int32_t column, uint64_t key, double minval,
+                                       double maxval) {
+    QB_PLAN(plan);
+    return plan->sample_uniform(name, column, key, minval, maxval);
+}
+
 qb200_status qb200_plan_read_moments(qb200_plan* plan, int32_t which, void* host, size_t nbytes) {
     QB_PLAN(plan);
     if (host == nullptr) return fail(QB200_INVALID, "read_moments needs a host buffer");

@@ -145,9 +145,13 @@ __global__ void __launch_bounds__(256) skinny_forward_kernel(const T* __restrict
             for (int j = 0; j < K; ++j) sum += a[j] * w[j][i];
             v[i] = biased ? sum + b[i] : sum;
         }
-        T* out = C + row * N + 4 * group;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) out[i] = v[i];
+        T* out = C + row * N + 4 * group;  // 16-byte aligned: N % 4 == 0 and C comes from cudaMalloc
+        if (sizeof(T) == 4) {
+            *reinterpret_cast<float4*>(out) = make_float4((float)v[0], (float)v[1], (float)v[2], (float)v[3]);
+        } else {
+            reinterpret_cast<double2*>(out)[0] = make_double2((double)v[0], (double)v[1]);
+            reinterpret_cast<double2*>(out)[1] = make_double2((double)v[2], (double)v[3]);
+        }
     }
 }
 
@@ -207,18 +211,29 @@ __global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ G, T*
     }
 }
 
-// acc[i] += sum_z partial[z][i], z ascending, in double: the fixed-order
-// second pass that keeps gradients bit-reproducible (the reference sums long
-// axes in double as well, cuda.rs:8202-8247).
+// acc[i] += sum_z partial[z][i] in double, in a fixed order: the second pass that keeps gradients
+// bit-reproducible (the reference sums long axes in double as well, cuda.rs:8202-8247).  A block
+// owns 32 consecutive elements; thread (x, y) sums the slices z = y, y + 8, ... of element x
+// (coalesced along x), then the eight partial sums are added in y order.
 template <typename T>
-__global__ void accumulate_partials_kernel(const T* __restrict__ partial, double* __restrict__ acc, int count,
-                                           int slices) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= count) return;
+__global__ void __launch_bounds__(256) accumulate_partials_kernel(const T* __restrict__ partial, double* __restrict__ acc,
+                                                                  int count, int slices) {
+    __shared__ double part[8][33];
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + x;
     double s = 0.0;
-#pragma unroll 8
-    for (int z = 0; z < slices; ++z) s += (double)partial[(long long)z * count + i];
-    acc[i] += s;
+    if (i < count) {
+#pragma unroll 4
+        for (int z = y; z < slices; z += 8) s += (double)partial[(long long)z * count + i];
+    }
+    part[y][x] = s;
+    __syncthreads();
+    if (y == 0 && i < count) {
+        double total = part[0][x];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) total += part[k][x];
+        acc[i] += total;
+    }
 }
 
 // out[i] = sum_z partial[z][i], z ascending, summed in double and rounded once.

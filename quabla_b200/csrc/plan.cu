@@ -147,6 +147,7 @@ class Plan final : public qb200_plan {
     qb200_status optimizer_step(const qb200_opt_config* config) override;
     qb200_status loss(void* host_scalar) override;
     qb200_status read_input(const char* name, void* host, size_t nbytes) override;
+    qb200_status sample_uniform(const char* name, int column, uint64_t key, double minval, double maxval) override;
     qb200_status read_moments(int which, void* host, size_t nbytes) override;
     qb200_status write_moments(int which, const void* host, size_t nbytes, int64_t step_count) override;
     qb200_status query(int key, int64_t* out) override;
@@ -540,6 +541,49 @@ qb200_status Plan<T>::bind(const char* name, const void* host, size_t nbytes) {
 }
 
 template <typename T>
+qb200_status Plan<T>::sample_uniform(const char* name, int column, uint64_t key, double minval, double maxval) {
+    if (name == nullptr) return fail(QB200_INVALID, "sample_uniform needs an input name");
+    const double width = maxval - minval;
+    if (!(minval < maxval) || !std::isfinite(width))
+        return fail(QB200_INVALID, "random_uniform requires finite minval < maxval, got [%g, %g)", minval, maxval);
+    // Clip bounds in the plan dtype: the smallest representable value >= minval and the largest < maxval.
+    double low, high;
+    if (sizeof(T) == 8) {
+        low = minval;
+        high = std::nextafter(maxval, -std::numeric_limits<double>::infinity());
+    } else {
+        float low32 = (float)minval, high32 = (float)maxval;
+        if ((double)low32 < minval) low32 = std::nextafter(low32, std::numeric_limits<float>::infinity());
+        if ((double)high32 >= maxval) high32 = std::nextafter(high32, -std::numeric_limits<float>::infinity());
+        if (low32 > high32) return fail(QB200_INVALID, "no float32 value lies in [%g, %g)", minval, maxval);
+        low = low32;
+        high = high32;
+    }
+    QB_TRY(use_device());
+    const std::string wanted(name);
+    for (size_t i = 0; i < desc_.inputs.size(); ++i) {
+        if (desc_.inputs[i].name != wanted) continue;
+        const long long rows = desc_.inputs[i].rows;
+        const int cols = (int)desc_.inputs[i].cols;
+        if (column < 0 || column >= cols) return fail(QB200_INVALID, "input '%s' has %d columns, got column %d", name, cols, column);
+        if (!inputs_[i].bound && cols > 1) {
+            // The other columns must come from somewhere: zero the array on first use.
+            QB_CUDA(cudaMemsetAsync(inputs_[i].dev, 0, (size_t)rows * cols * sizeof(T), stream_));
+        }
+        const int grid = (int)std::min<long long>((rows + 255) / 256, 148 * 8);
+        sample_uniform_kernel<T><<<std::max(grid, 1), 256, 0, stream_>>>(inputs_[i].dev + column, rows, cols,
+                                                                        (unsigned long long)key, minval, width, low, high);
+        QB_TRY(launched("sample_uniform_kernel"));
+        inputs_[i].bound = true;
+        for (size_t si = 0; si < desc_.sets.size(); ++si)
+            for (const auto& c : desc_.sets[si].cols)
+                if (c.first == (int)i) sets_[si].table_dirty = true;
+        return QB200_OK;
+    }
+    return fail(QB200_INVALID, "the plan has no data input named '%s'", name);
+}
+
+template <typename T>
 qb200_status Plan<T>::check_bound() const {
     for (size_t i = 0; i < desc_.params.size(); ++i)
         if (!leaves_[i].bound) return fail(QB200_NOT_BOUND, "parameter '%s' was never bound", desc_.params[i].name.c_str());
@@ -825,7 +869,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                 QB_TRY(tc_status);
                 const int count = d_in * d_out;
                 const int slices = (int)((rows + tc_chunk - 1) / tc_chunk);
-                accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(
+                accumulate_partials_kernel<T><<<(count + 31) / 32, 256, 0, stream_>>>(
                     wpartial_, d_acc_ + leaves_[leaf].offset, count, slices);
                 return launched("accumulate_partials_kernel");
             }
@@ -851,7 +895,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                 else
                     skinny_wgrad_kernel<T, 4, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
                 QB_TRY(launched("skinny_wgrad_kernel"));
-                accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(
+                accumulate_partials_kernel<T><<<(count + 31) / 32, 256, 0, stream_>>>(
                     wpartial_, d_acc_ + leaves_[leaf].offset, count, slices);
                 return launched("accumulate_partials_kernel");
             }
@@ -877,7 +921,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         (void)e;
         QB_TRY(launched("gemm_kernel(wgrad)"));
         const int count = d_in * d_out;
-        accumulate_partials_kernel<T><<<(count + 255) / 256, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
+        accumulate_partials_kernel<T><<<(count + 31) / 32, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
                                                                                 count, slices);
         return launched("accumulate_partials_kernel");
     };
@@ -892,7 +936,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         dim3 grid(col_blocks, slices);
         colsum_kernel<T><<<grid, 256, 0, stream_>>>(Gz, wpartial_, C, d_out, row_chunk);
         QB_TRY(launched("colsum_kernel"));
-        accumulate_partials_kernel<T><<<(d_out + 255) / 256, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
+        accumulate_partials_kernel<T><<<(d_out + 31) / 32, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
                                                                                 d_out, slices);
         return launched("accumulate_partials_kernel");
     };

@@ -18,6 +18,7 @@ struct qb200_plan {
     virtual qb200_status optimizer_step(const qb200_opt_config* config) = 0;
     virtual qb200_status loss(void* host_scalar) = 0;
     virtual qb200_status read_input(const char* name, void* host, size_t nbytes) = 0;
+    virtual qb200_status sample_uniform(const char* name, int column, uint64_t key, double minval, double maxval) = 0;
     virtual qb200_status read_moments(int which, void* host, size_t nbytes) = 0;
     virtual qb200_status write_moments(int which, const void* host, size_t nbytes, int64_t step_count) = 0;
     virtual qb200_status query(int key, int64_t* out) = 0;

@@ -299,4 +299,29 @@ __global__ void __launch_bounds__(1024) global_norm_kernel(const T* __restrict__
     }
 }
 
+// ---------------------------------------------------------------------------
+// Device-side resampling of a collocation column with the reference's generator, so that a
+// training loop can draw a fresh batch without a host copy.  Element i of the column is
+//   clip(round_to_dtype(minval + width * ((splitmix64_output(key, i) >> 11) / 2^53)), low, high),
+// the arithmetic of random_uniform (crates/quabla-python/src/tensor.rs:1482-1534) on the i-th
+// output of the SplitMix64 stream seeded by key (tensor.rs:327-333): state = key + (i + 1) * gamma,
+// then the two multiply-xorshift rounds.  The stream is counter-based, so every element is
+// independent; multiply and add are kept separate (no FMA) as on the host.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void sample_uniform_kernel(T* __restrict__ column, long long rows, int stride, unsigned long long key,
+                                      double minval, double width, double low, double high) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < rows; i += (long long)gridDim.x * blockDim.x) {
+        unsigned long long z = key + (unsigned long long)(i + 1) * 0x9e3779b97f4a7c15ull;
+        z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+        z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+        z = z ^ (z >> 31);
+        const double unit = (double)(z >> 11) * (1.0 / 9007199254740992.0);  // exact: 53 bits, power-of-two scale
+        double value = __dadd_rn(minval, __dmul_rn(width, unit));
+        if (sizeof(T) == 4) value = (double)(float)value;  // one rounding to float32, as astype does
+        value = fmin(fmax(value, low), high);
+        column[i * stride] = (T)value;
+    }
+}
+
 }  // namespace qb

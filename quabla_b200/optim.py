@@ -334,6 +334,31 @@ class Trainer:
         self._data = tuple(data)
         return result
 
+    def resample(self, index: int, key, bounds: Sequence[tuple[float, float]]) -> None:
+        """Redraw batch argument `index` (one array of shape [rows, d]) on the device.
+
+        Column j becomes `random.uniform(random.fold_in(key, j), (rows,), dtype, *bounds[j])`, bit for
+        bit, generated by a kernel: no host array is built and nothing is copied to the device.
+        The next `step()` without arguments trains on the new batch.  Not part of the reference's
+        Trainer, which redraws on the host and passes the batch to `step`
+        (python/quabla/optim.py:490-550).
+        """
+        from . import random as qrandom
+
+        index = operator.index(index)
+        if index not in self._batch_argnums:
+            raise ValueError("resample takes one of batch_argnums")
+        names = self._batch_names[index]
+        specs = self._batch_specs[self._batch_argnums.index(index)]
+        if len(names) != 1 or len(specs) != 1 or len(specs[0][0]) != 2:
+            raise ValueError("resample needs a batch argument that is one array of shape [rows, columns]")
+        columns = specs[0][0][1]
+        if len(bounds) != columns:
+            raise ValueError(f"bounds must have one (minval, maxval) pair per column, {columns} here")
+        plan = self._executor.plan
+        for j, (low, high) in enumerate(bounds):
+            plan.sample_uniform(names[0], j, qrandom.fold_in(key, j), low, high)
+
     def loss(self):
         return self._executor.loss()
 

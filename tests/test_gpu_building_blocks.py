@@ -151,3 +151,52 @@ def test_matmul_3xtf32_over_many_tiles(cuda_device, M, N, K):
     expected = a.double() @ w.double()
     error = (c.double() - expected).abs().max().item() / expected.abs().max().item()
     assert error <= 2e-6
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_device_resampling_equals_the_host_generator_bit_for_bit(cuda_device, dtype):
+    import quabla_b200 as qb
+    from quabla_b200 import workloads
+    from quabla_b200._plan import Plan
+
+    from _util import traced
+
+    name = "poisson2d" if dtype == np.float32 else "burgers"
+    w, compiled, inputs = traced(name, 5000)
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    data_name, rows, cols, _ = compiled.spec.inputs[0]
+    bounds = [(-1.0, 1.0), (0.0, 0.3)][:cols] if cols <= 2 else [(0.0, 1.0)] * cols
+    key = qb.random.key(20240607)
+    for j, (low, high) in enumerate(bounds):
+        plan.sample_uniform(data_name, j, qb.random.fold_in(key, j), low, high)
+    got = plan.read_input(data_name, (rows, cols))
+    for j, (low, high) in enumerate(bounds):
+        expected = qb.random.uniform(qb.random.fold_in(key, j), (rows,), dtype, low, high)
+        assert got[:, j].tobytes() == expected.tobytes()
+    with pytest.raises(_lib.BackendError):
+        plan.sample_uniform(data_name, cols, key, 0.0, 1.0)
+    with pytest.raises(_lib.BackendError):
+        plan.sample_uniform(data_name, 0, key, 1.0, 1.0)
+    plan.close()
+
+
+def test_trainer_resample_trains_on_the_same_batch_as_a_host_draw(cuda_device):
+    import quabla_b200 as qb
+    from quabla_b200 import workloads
+
+    w = workloads.make("poisson2d", 1024)
+    key = qb.random.key(7)
+    bounds = [(0.0, 1.0), (0.0, 1.0)]
+    rows = w.data[0].shape[0]
+    host_batch = np.stack([qb.random.uniform(qb.random.fold_in(key, j), (rows,), np.float32, *bounds[j])
+                           for j in range(2)], axis=1)
+    a = qb.optim.Trainer(w.loss, w.params, qb.optim.Adam(1e-3), *w.data, device="cuda:0", batch_argnums=(0,))
+    b = qb.optim.Trainer(w.loss, w.params, qb.optim.Adam(1e-3), *w.data, device="cuda:0", batch_argnums=(0,))
+    a.step(host_batch)
+    b.resample(0, key, bounds)
+    b.step()
+    assert np.asarray(a.value).tobytes() == np.asarray(b.value).tobytes()
+    for pa, pb in zip(a.params, b.params):
+        assert pa["w"].tobytes() == pb["w"].tobytes() and pa["b"].tobytes() == pb["b"].tobytes()
