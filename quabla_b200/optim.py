@@ -20,10 +20,11 @@ import numpy as np
 from . import _trace as tr
 from ._devices import require_device
 from ._errors import UnsupportedOperationError
+from ._lbfgs import LBFGS
 from ._plan import COTANGENT_NAME, opt_config
 from ._transforms import CompiledLoss, _is_array
 
-__all__ = ["Adam", "AdamW", "SGD", "Trainer", "clip_by_global_norm"]
+__all__ = ["Adam", "AdamW", "SGD", "LBFGS", "Trainer", "clip_by_global_norm"]
 
 
 def _positive(value, name: str) -> float:
