@@ -133,6 +133,12 @@ void qb200_desc_destroy(qb200_desc* desc);
  * (a1/a2: tensor_ir.rs:4968-4972, elementwise.rs:400-407), the last is Linear. */
 qb200_status qb200_desc_set_network(qb200_desc* desc, const int32_t* sizes, int32_t n_sizes);
 
+/* Activation of the hidden layers: tanh (the default) or sin
+ * (UnaryMath kinds and their derivative chains, elementwise.rs:400-407, 416-468).
+ * Networks with a sin activation run on the layer-wise engine. */
+typedef enum { QB200_ACT_TANH = 0, QB200_ACT_SIN = 1 } qb200_activation;
+qb200_status qb200_desc_set_activation(qb200_desc* desc, int32_t activation);
+
 /* A parameter leaf, named as the reference names inputs (pytree path,
  * _transforms.py:363-377).  Gradient outputs follow the order of these calls
  * (tensor_trace.rs:4562-4573).  layer counts from 0; a weight is

@@ -51,6 +51,7 @@ typedef struct {
     const int* sizes;        /* n_layers + 1 */
     const double* const* W;  /* W[l]: [sizes[l]][sizes[l+1]] row-major */
     const double* const* b;  /* b[l]: [sizes[l+1]] or NULL */
+    int activation;          /* of the hidden layers: 0 tanh, 1 sin (elementwise.rs:400-407) */
 } qbo_net;
 
 typedef struct {
@@ -115,6 +116,25 @@ static void tanh_derivs(double t, double* d /* [6]: d[k] = k-th derivative */) {
     d[3] = -2.0 * (d[1] * d[1] + t * d[2]);
     d[4] = -2.0 * (3.0 * d[1] * d[2] + t * d[3]);
     d[5] = -2.0 * (3.0 * d[2] * d[2] + 4.0 * d[1] * d[3] + t * d[4]);
+}
+
+/* sin and its derivatives: cos, -sin, -cos, sin, cos (chain rules of elementwise.rs:416-468). */
+static void sin_derivs(double z, double* d) {
+    const double sn = sin(z), cs = cos(z);
+    d[0] = sn;
+    d[1] = cs;
+    d[2] = -sn;
+    d[3] = -cs;
+    d[4] = sn;
+    d[5] = cs;
+}
+
+/* Activation value and derivatives at the pre-activation z. */
+static void activation_derivs(int activation, double z, double* d) {
+    if (activation == 1)
+        sin_derivs(z, d);
+    else
+        tanh_derivs(tanh(z), d);
 }
 
 /* Faa di Bruno: h_m = d^m tanh(z(s))/ds^m, m = 1..K, from z[m-1] = d^m z/ds^m. */
@@ -229,7 +249,7 @@ static double point_eval(const qbo_net* net, const qbo_set* s, const qbo_layout*
         }
         for (int n = 0; n < dout; ++n) {
             double d[6];
-            tanh_derivs(tanh(z[n]), d);
+            activation_derivs(net->activation, z[n], d);
             hout[n] = d[0];
             for (int j = 0; j < s->ndirs; ++j) {
                 double zz[QBO_MAX_ORDER], hh[QBO_MAX_ORDER];
@@ -252,12 +272,11 @@ static double point_eval(const qbo_net* net, const qbo_set* s, const qbo_layout*
         const int din = net->sizes[l], dout = net->sizes[l + 1];
         const double* hin = work + L->act_off[l];
         const double* z = work + L->pre_off[l + 1];
-        const double* hout = work + L->act_off[l + 1];
-        /* ga holds cotangents of hout [S][dout]; turn them into cotangents of z. */
+        /* ga holds cotangents of the layer's output jets [S][dout]; turn them into cotangents of z. */
         if (l != nl - 1) {
             for (int n = 0; n < dout; ++n) {
                 double d[6];
-                tanh_derivs(hout[n], d);
+                activation_derivs(net->activation, z[n], d);  /* z[n]: the primal pre-activation */
                 double z0bar = d[1] * ga[n];
                 for (int j = 0; j < s->ndirs; ++j) {
                     double zz[QBO_MAX_ORDER], gg[QBO_MAX_ORDER], gz[QBO_MAX_ORDER];

@@ -22,7 +22,8 @@ WEIGHT, BIAS = 0, 1
 
 class _Net(C.Structure):
     _fields_ = [("n_layers", C.c_int), ("sizes", C.POINTER(C.c_int)),
-                ("W", C.POINTER(C.POINTER(C.c_double))), ("b", C.POINTER(C.POINTER(C.c_double)))]
+                ("W", C.POINTER(C.POINTER(C.c_double))), ("b", C.POINTER(C.POINTER(C.c_double))),
+                ("activation", C.c_int)]
 
 
 class _Set(C.Structure):
@@ -84,7 +85,8 @@ class _Problem:
         self.Wp = (C.POINTER(C.c_double) * n_layers)(*[_dp(w) for w in self.W])
         self.bp = (C.POINTER(C.c_double) * n_layers)(
             *[_dp(b) if b is not None else C.POINTER(C.c_double)() for b in self.b])
-        self.net = _Net(n_layers, self.sizes, self.Wp, self.bp)
+        activation = {"tanh": 0, "sin": 1}[getattr(spec, "activation", "tanh")]
+        self.net = _Net(n_layers, self.sizes, self.Wp, self.bp, activation)
         self.sets = []
         self.keep = []
         for s in spec.sets:

@@ -15,6 +15,7 @@ from . import _build
 OK, INVALID, UNSUPPORTED, CUDA_ERROR, NCCL_ERROR, NOT_BOUND, TOO_LARGE = range(7)
 F32, F64 = 0, 1
 WEIGHT, BIAS = 0, 1
+ACT_TANH, ACT_SIN = 0, 1
 SGD, ADAM = 0, 1
 REDUCE_SUM, REDUCE_MEAN = 0, 1
 (Q_DEVICE_BUFFER_COUNT, Q_NONFINITE_CLIP_SEEN, Q_STREAM, Q_PARAMETER_COUNT, Q_OUTPUT_COUNT,
@@ -65,6 +66,7 @@ SIGNATURES = {
     "qb200_desc_create": (_I32, [_I32, C.POINTER(_P)]),
     "qb200_desc_destroy": (None, [_P]),
     "qb200_desc_set_network": (_I32, [_P, C.POINTER(_I32), _I32]),
+    "qb200_desc_set_activation": (_I32, [_P, _I32]),
     "qb200_desc_add_parameter": (_I32, [_P, C.c_char_p, _I32, _I32]),
     "qb200_desc_add_input": (_I32, [_P, C.c_char_p, _I64, _I64, _I32, C.POINTER(_I32)]),
     "qb200_desc_add_set": (_I32, [_P, _I64, C.c_double, C.POINTER(_I32)]),

@@ -42,6 +42,7 @@ class PlanSpec:
     parameters: list[tuple[str, int, int]] = field(default_factory=list)   # (name, layer, kind)
     inputs: list[tuple[str, int, int, bool]] = field(default_factory=list)  # (name, rows, cols, retained)
     sets: list[SetSpec] = field(default_factory=list)
+    activation: str = "tanh"   # of the hidden layers: "tanh" or "sin"
 
     def parameter_shape(self, index: int) -> tuple[int, ...]:
         _, layer, kind = self.parameters[index]
@@ -76,6 +77,8 @@ def build_desc(spec: PlanSpec) -> C.c_void_p:
     _lib.check(lib.qb200_desc_create(dtype_code(spec.dtype), C.byref(desc)))
     try:
         _lib.check(lib.qb200_desc_set_network(desc, _int32_array(spec.sizes), len(spec.sizes)))
+        if spec.activation != "tanh":
+            _lib.check(lib.qb200_desc_set_activation(desc, {"sin": _lib.ACT_SIN}[spec.activation]))
         for name, layer, kind in spec.parameters:
             _lib.check(lib.qb200_desc_add_parameter(desc, name.encode(), layer, kind))
         for name, rows, cols, retained in spec.inputs:

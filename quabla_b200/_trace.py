@@ -108,24 +108,26 @@ class Network:
     tanh between them, linear last layer; `inputs` are the per-point expressions
     feeding the first layer."""
 
-    __slots__ = ("layers", "inputs", "_hash")
+    __slots__ = ("layers", "inputs", "activation", "_hash")
 
-    def __init__(self, layers: tuple, inputs: tuple) -> None:
+    def __init__(self, layers: tuple, inputs: tuple, activation: str = "tanh") -> None:
         self.layers = tuple(layers)
         self.inputs = tuple(inputs)
-        self._hash = hash((self.layers, self.inputs))
+        self.activation = activation
+        self._hash = hash((self.layers, self.inputs, self.activation))
 
     def __hash__(self) -> int:
         return self._hash
 
     def __eq__(self, other) -> bool:
-        return isinstance(other, Network) and self.layers == other.layers and self.inputs == other.inputs
+        return (isinstance(other, Network) and self.layers == other.layers and self.inputs == other.inputs
+                and self.activation == other.activation)
 
     def __repr__(self) -> str:
         return f"Network({[l[2] for l in self.layers] + [self.layers[-1][3]]})"
 
     def substituted(self, mapping: dict) -> "Network":
-        return Network(self.layers, tuple(sx.substitute(e, mapping) for e in self.inputs))
+        return Network(self.layers, tuple(sx.substitute(e, mapping) for e in self.inputs), self.activation)
 
     def direction(self, variable: sx.Expr) -> tuple[float, ...]:
         """d(inputs)/d(variable), which must be constant (affine input maps)."""
@@ -151,11 +153,13 @@ def _cells(value):
 class _Pending:
     """A per-point MLP prefix that has not been reduced to a scalar yet."""
 
-    def __init__(self, layers: list, inputs: tuple, activated: bool, shape: tuple[int, ...]) -> None:
+    def __init__(self, layers: list, inputs: tuple, activated: bool, shape: tuple[int, ...],
+                 activation: str | None = None) -> None:
         self.layers = layers        # [[w_name, b_name, d_in, d_out], ...]
         self.inputs = inputs
-        self.activated = activated  # tanh already applied to the last layer
+        self.activated = activated  # the activation already applied to the last layer
         self.shape = shape
+        self.activation = activation  # "tanh" or "sin" once a hidden layer has been activated
 
     @property
     def width(self) -> int:
@@ -166,7 +170,7 @@ class _Pending:
             raise _unsupported(
                 "a hidden layer of the network is used outside x @ w + b / tanh; only the scalar output of the "
                 "last linear layer can enter the residual")
-        network = Network(tuple(tuple(l) for l in self.layers), self.inputs)
+        network = Network(tuple(tuple(l) for l in self.layers), self.inputs, self.activation or "tanh")
         out = np.empty(self.shape, dtype=object)
         out[...] = sx.net(network, ())
         return out
@@ -220,7 +224,7 @@ class TraceValue:
             point = _resolve_shape(shape, int(np.prod(self.point_shape, dtype=np.int64)))
         if isinstance(self.inner, _Pending):
             p = self.inner
-            return self._like(_Pending(p.layers, p.inputs, p.activated, point))
+            return self._like(_Pending(p.layers, p.inputs, p.activated, point, p.activation))
         return self._like(self.inner.reshape(point))
 
     def astype(self, dtype) -> "TraceValue":
@@ -330,7 +334,7 @@ class TraceValue:
             raise ValueError(f"bias '{bias.name}' of shape {bias.shape} does not match layer width {p.width}")
         layers = [list(l) for l in p.layers]
         layers[-1][1] = bias.name
-        return self._like(_Pending(layers, p.inputs, False, p.shape))
+        return self._like(_Pending(layers, p.inputs, False, p.shape, p.activation))
 
     def __matmul__(self, weight):
         if not isinstance(weight, ParamRef):
@@ -345,7 +349,7 @@ class TraceValue:
             if p.width != d_in or not p.shape or p.shape[-1] != d_in:
                 raise ValueError(f"matmul of a width-{p.width} activation with '{weight.name}' {weight.shape}")
             layers = [list(l) for l in p.layers] + [[weight.name, None, d_in, d_out]]
-            return self._like(_Pending(layers, p.inputs, False, p.shape[:-1] + (d_out,)))
+            return self._like(_Pending(layers, p.inputs, False, p.shape[:-1] + (d_out,), p.activation))
         a = self.array()
         # A rank-1 operand is a row vector (python/quabla/_ops.py:366-387).
         if a.ndim == 0 or a.shape[-1] != d_in or int(np.prod(a.shape[:-1], dtype=np.int64)) != 1:
@@ -355,9 +359,12 @@ class TraceValue:
         return self._like(_Pending([[weight.name, None, d_in, d_out]], inputs, False, a.shape[:-1] + (d_out,)))
 
     def _unary(self, kind: str) -> "TraceValue":
-        if kind == "tanh" and isinstance(self.inner, _Pending) and not self.inner.activated:
+        if kind in ("tanh", "sin") and isinstance(self.inner, _Pending) and not self.inner.activated:
             p = self.inner
-            return self._like(_Pending(p.layers, p.inputs, True, p.shape))
+            if p.activation not in (None, kind):
+                raise _unsupported(f"one network mixes {p.activation} and {kind} activations; hidden layers share one",
+                                   kind)
+            return self._like(_Pending(p.layers, p.inputs, True, p.shape, kind))
         a = self.array()
         out = np.empty(a.shape, dtype=object)
         flat_in, flat_out = a.reshape(-1), out.reshape(-1)
@@ -686,6 +693,7 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
     data_shapes = {name: shape for name, shape, _ in data}
 
     layers = None
+    activation = "tanh"
     groups: dict = {}
     order: list = []
     for weight, batch, expr in loss.terms:
@@ -698,7 +706,8 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
                 raise _unsupported("one loss term evaluates the network at two different inputs", "loss")
         if layers is None:
             layers = network.layers
-        elif network.layers != layers:
+            activation = network.activation
+        elif network.layers != layers or network.activation != activation:
             raise _unsupported("the loss uses more than one network", "loss")
         key = (batch, network.inputs)
         if key not in groups:
@@ -718,7 +727,7 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
         raise _unsupported("a parameter is shared between layers", "loss")
     if sizes[-1] != 1:
         raise _unsupported("the network output must be one scalar per point", "loss")
-    spec = PlanSpec(dtype=dtype, sizes=sizes)
+    spec = PlanSpec(dtype=dtype, sizes=sizes, activation=activation)
     layer_of = {}
     for index, (w_name, b_name, _, _) in enumerate(layers):
         layer_of[w_name] = (index, _lib.WEIGHT)

@@ -233,6 +233,14 @@ qb200_status qb200_desc_set_network(qb200_desc* desc, const int32_t* sizes, int3
     return QB200_OK;
 }
 
+qb200_status qb200_desc_set_activation(qb200_desc* desc, int32_t activation) {
+    if (desc == nullptr) return fail(QB200_INVALID, "set_activation needs a description");
+    if (activation != QB200_ACT_TANH && activation != QB200_ACT_SIN)
+        return fail(QB200_UNSUPPORTED, "activation %d is not supported: tanh (0) or sin (1)", activation);
+    desc->activation = activation;
+    return QB200_OK;
+}
+
 qb200_status qb200_desc_add_parameter(qb200_desc* desc, const char* name, int32_t layer, int32_t kind) {
     if (desc == nullptr || name == nullptr) return fail(QB200_INVALID, "add_parameter needs a description and a name");
     desc->params.push_back({name, layer, kind});

@@ -82,6 +82,7 @@ struct qb200_desc {
         }
     };
     int dtype = QB200_F32;
+    int activation = QB200_ACT_TANH;  // of the hidden layers
     std::vector<int> sizes;
     std::vector<Param> params;
     std::vector<Input> inputs;

@@ -35,10 +35,34 @@ struct JetVec<double> {
     static __device__ __forceinline__ double2 pack(const double (&v)[2]) { return make_double2(v[0], v[1]); }
 };
 
-// Transposed jet composition with the primal activation t = tanh(z_0) given (saved by the forward pass).
+// Forward jet composition on the S streams of one (point, unit) for activation `act`.
 template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply_transposed_saved(T t, const T (&z)[SG::S], T (&g)[SG::S]) {
-    const TanhD<T> d(t);
+__device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act) {
+    T value;
+    const TanhD<T> d(v[0], act, &value);
+    v[0] = value;
+#pragma unroll
+    for (int j = 0; j < SG::ndirs; ++j) {
+        T z[MAX_ORDER], h[MAX_ORDER];
+        const int K = SG::order(j);
+        const int b = SG::base(j);
+#pragma unroll
+        for (int m = 0; m < MAX_ORDER; ++m) z[m] = m < K ? v[b + m] : T(0);
+        switch (K) {
+            case 1: jet_compose<T, 1>(d, z, h); break;
+            case 2: jet_compose<T, 2>(d, z, h); break;
+            case 3: jet_compose<T, 3>(d, z, h); break;
+            default: jet_compose<T, 4>(d, z, h); break;
+        }
+#pragma unroll
+        for (int m = 0; m < MAX_ORDER; ++m)
+            if (m < K) v[b + m] = h[m];
+    }
+}
+
+// Transposed jet composition with the activation's derivatives d at z_0 given.
+template <typename T, typename SG>
+__device__ __forceinline__ void jet_apply_transposed_saved(const TanhD<T>& d, const T (&z)[SG::S], T (&g)[SG::S]) {
     T z0bar = d.t1 * g[0];
 #pragma unroll
     for (int j = 0; j < SG::ndirs; ++j) {
@@ -65,7 +89,8 @@ __device__ __forceinline__ void jet_apply_transposed_saved(T t, const T (&z)[SG:
 
 // H = tanh-jet(Z), all streams.
 template <typename T, int CODE>
-__global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane) {
+__global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane,
+                                                              int act) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
@@ -83,7 +108,7 @@ __global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restric
             T v[S];
 #pragma unroll
             for (int s = 0; s < S; ++s) v[s] = lanes[s][i];
-            jet_apply<T, SG>(v);
+            jet_apply_act<T, SG>(v, act);
 #pragma unroll
             for (int s = 0; s < S; ++s) lanes[s][i] = v[s];
         }
@@ -99,7 +124,7 @@ template <typename T, int CODE, bool HEAD>
 __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
                                                                T* __restrict__ G, long long plane,
                                                                const T* __restrict__ Uhat, const T* __restrict__ w_head,
-                                                               int d, long long C) {
+                                                               int d, long long C, int act) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
@@ -107,7 +132,8 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
     const long long nvec = plane / V;
     for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < nvec; e += (long long)gridDim.x * blockDim.x) {
         VT qz[S], qg[S];
-        const VT qt = reinterpret_cast<const VT*>(Hprimal)[e];
+        // tanh rebuilds its derivatives from the saved activation, other activations from z_0.
+        const VT qt = reinterpret_cast<const VT*>(act == ACT_TANH ? Hprimal : Z)[e];
 #pragma unroll
         for (int s = 0; s < S; ++s) {
             // The transposed composition never reads z_0 itself (t replaces it).
@@ -141,7 +167,9 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
                 if (s > 0) z[s] = zl[s][i];
                 g[s] = gl[s][i];
             }
-            jet_apply_transposed_saved<T, SG>(t[i], z, g);
+            T unused;
+            const TanhD<T> dv = act == ACT_TANH ? TanhD<T>(t[i]) : TanhD<T>(t[i], act, &unused);
+            jet_apply_transposed_saved<T, SG>(dv, z, g);
 #pragma unroll
             for (int s = 0; s < S; ++s) gl[s][i] = g[s];
         }
@@ -165,25 +193,25 @@ inline int jet_sig_grid(long long vectors) {
 }
 
 template <typename T>
-inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, cudaStream_t stream) {
+inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, int act, cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
     switch (code) {
-        case 0: jet_forward_sig_kernel<T, 0><<<grid, 256, 0, stream>>>(Z, H, plane); break;
-        case 1: jet_forward_sig_kernel<T, 1><<<grid, 256, 0, stream>>>(Z, H, plane); break;
-        case 2: jet_forward_sig_kernel<T, 2><<<grid, 256, 0, stream>>>(Z, H, plane); break;
-        case 4: jet_forward_sig_kernel<T, 4><<<grid, 256, 0, stream>>>(Z, H, plane); break;
-        case 7: jet_forward_sig_kernel<T, 7><<<grid, 256, 0, stream>>>(Z, H, plane); break;
-        case 12: jet_forward_sig_kernel<T, 12><<<grid, 256, 0, stream>>>(Z, H, plane); break;
-        default: jet_forward_sig_kernel<T, 187><<<grid, 256, 0, stream>>>(Z, H, plane); break;
+        case 0: jet_forward_sig_kernel<T, 0><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
+        case 1: jet_forward_sig_kernel<T, 1><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
+        case 2: jet_forward_sig_kernel<T, 2><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
+        case 4: jet_forward_sig_kernel<T, 4><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
+        case 7: jet_forward_sig_kernel<T, 7><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
+        case 12: jet_forward_sig_kernel<T, 12><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
+        default: jet_forward_sig_kernel<T, 187><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
     }
 }
 
 template <typename T, bool HEAD>
 inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
-                                         const T* w_head, int d, long long C, cudaStream_t stream) {
+                                         const T* w_head, int d, long long C, int act, cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
 #define QB_JET_BWD(CODE) \
-    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C)
+    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act)
     switch (code) {
         case 0: QB_JET_BWD(0); break;
         case 1: QB_JET_BWD(1); break;
@@ -197,16 +225,17 @@ inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal,
 }
 
 template <typename T>
-inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, cudaStream_t stream) {
-    jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, 1, 1, stream);
+inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, int act,
+                                    cudaStream_t stream) {
+    jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, 1, 1, act, stream);
 }
 
 // Last hidden layer: the cotangents of H are Uhat (x) w_head, formed inside the kernel; d % V == 0
 // and w_head 16-byte aligned are the caller's to check.
 template <typename T>
 inline void jet_backward_head_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
-                                     const T* w_head, int d, long long C, cudaStream_t stream) {
-    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, stream);
+                                     const T* w_head, int d, long long C, int act, cudaStream_t stream) {
+    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, act, stream);
 }
 
 }  // namespace qb

@@ -36,10 +36,36 @@ __device__ __forceinline__ double qb_tanh<double>(double x) {
     return tanh(x);
 }
 
-// t1..t5 = d^k tanh / dz^k expressed through t.
+__device__ __forceinline__ void qb_sincos(float x, float* s, float* c) { sincosf(x, s, c); }
+__device__ __forceinline__ void qb_sincos(double x, double* s, double* c) { sincos(x, s, c); }
+
+// Hidden-layer activations (qb200_activation in the C ABI).
+constexpr int ACT_TANH = 0;
+constexpr int ACT_SIN = 1;
+
+// t1..t5 = the first five derivatives of the activation at z.  For tanh they are polynomials in
+// t = tanh(z); for sin they cycle through cos, -sin, -cos, sin, cos.
 template <typename T>
 struct TanhD {
     T t1, t2, t3, t4, t5;
+    __device__ __forceinline__ TanhD() {}
+    // Activation `act` at z; *value receives the activation itself.
+    __device__ __forceinline__ TanhD(T z, int act, T* value) {
+        if (act == ACT_SIN) {
+            T sn, cs;
+            qb_sincos(z, &sn, &cs);
+            *value = sn;
+            t1 = cs;
+            t2 = -sn;
+            t3 = -cs;
+            t4 = sn;
+            t5 = cs;
+        } else {
+            const T t = qb_tanh<T>(z);
+            *value = t;
+            *this = TanhD(t);
+        }
+    }
     __device__ __forceinline__ explicit TanhD(T t) {
         t1 = T(1) - t * t;
         t2 = T(-2) * t * t1;

@@ -275,12 +275,12 @@ __global__ void seed_input_kernel(const T* __restrict__ table, int table_cols, l
 
 // H = tanh-jet(Z), all streams, one thread per (point, unit).
 template <typename T>
-__global__ void jet_forward_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane, JetSpec spec) {
+__global__ void jet_forward_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane, JetSpec spec, int act) {
     for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < plane;
          e += (long long)gridDim.x * blockDim.x) {
-        const T t = qb_tanh<T>(Z[e]);
+        T t;
+        const TanhD<T> d(Z[e], act, &t);
         H[e] = t;
-        const TanhD<T> d(t);
         for (int j = 0; j < spec.ndirs; ++j) {
             const long long off = (long long)spec.base[j] * plane + e;
             T z[MAX_ORDER], h[MAX_ORDER];
@@ -303,11 +303,12 @@ __global__ void jet_forward_kernel(const T* __restrict__ Z, T* __restrict__ H, l
 // In place: G (cotangents of H) becomes the cotangents of Z.
 template <typename T>
 __global__ void jet_backward_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal, T* __restrict__ G,
-                                    long long plane, JetSpec spec) {
+                                    long long plane, JetSpec spec, int act) {
     for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < plane;
          e += (long long)gridDim.x * blockDim.x) {
-        const T t = Hprimal[e];
-        const TanhD<T> d(t);
+        // tanh: derivatives from the saved activation; otherwise from the saved pre-activation.
+        T unused;
+        const TanhD<T> d = act == ACT_TANH ? TanhD<T>(Hprimal[e]) : TanhD<T>(Z[e], act, &unused);
         T z0bar = d.t1 * G[e];
         for (int j = 0; j < spec.ndirs; ++j) {
             const long long off = (long long)spec.base[j] * plane + e;

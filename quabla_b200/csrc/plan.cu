@@ -617,6 +617,7 @@ template <typename T>
 bool Plan<T>::choose_fused() {
     if (const char* env = getenv("QB200_ENGINE"))
         if (std::string(env) == "layerwise") return false;
+    if (desc_.activation != QB200_ACT_TANH) return false;  // the fused kernels are written for tanh
     const int hidden = L_ - 1;
     if (hidden < 1 || hidden > FUSED_MAX_LAYERS || desc_.sizes[0] > 4) return false;
     const int W = desc_.sizes[1];
@@ -844,9 +845,9 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         }
         const long long plane = (long long)C * sz[l];
         if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], nullptr))
-            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, stream_);
+            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, desc_.activation, stream_);
         else
-            jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec);
+            jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec, desc_.activation);
         QB_TRY(launched("jet_forward_kernel"));
     }
     head_forward_kernel<T><<<grid_for(rows * 32, 256), 256, 0, stream_>>>(H_[head], weight(head), bias(head), U_, rows,
@@ -959,11 +960,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         const long long plane = (long long)C * sz[l];
         if (l == head && head_fused)
             jet_backward_head_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, Uhat_, weight(head), sz[head], C,
-                                        stream_);
+                                        desc_.activation, stream_);
         else if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], G_[cur]))
-            jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, stream_);
+            jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, desc_.activation, stream_);
         else
-            jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec);
+            jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec, desc_.activation);
         QB_TRY(launched("jet_backward_kernel"));
         QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1], l - 1));
         QB_TRY(bgrad(G_[cur], sz[l], b_leaf_[l - 1]));

@@ -63,14 +63,16 @@ def init_mlp(key, sizes, dtype=np.float64):
             for k, m, n in zip(keys, sizes[:-1], sizes[1:])]
 
 
-def make_u(api):
+def make_u(api, activation: str = "tanh"):
     """The network as a scalar function of one point (scalar or vector), written
-    against `api` (this package, or any module with the same surface)."""
+    against `api` (this package, or any module with the same surface); hidden
+    layers use `api.tanh` or `api.sin`."""
+    act = getattr(api, activation)
 
     def mlp(params, x):
         h = x
         for layer in params[:-1]:
-            h = api.tanh(h @ layer["w"] + layer["b"])
+            h = act(h @ layer["w"] + layer["b"])
         last = params[-1]
         return h @ last["w"] + last["b"]
 
@@ -95,9 +97,9 @@ def _scaled(n: int, points: int | None, full: int) -> int:
 
 
 # -- 1: 1-D Poisson, float64 ---------------------------------------------------
-def poisson1d(points: int | None = None, api=None) -> Workload:
+def poisson1d(points: int | None = None, api=None, activation: str = "tanh") -> Workload:
     api = qb if api is None else api
-    u = make_u(api)
+    u = make_u(api, activation)
     sizes, dtype, seed = [1, 16, 16, 1], np.float64, 0
     n = _scaled(128, points, 128)
 
@@ -114,9 +116,9 @@ def poisson1d(points: int | None = None, api=None) -> Workload:
 
 
 # -- 2: 2-D Poisson on the unit square, float32 -----------------------------------
-def poisson2d(points: int | None = None, api=None) -> Workload:
+def poisson2d(points: int | None = None, api=None, activation: str = "tanh") -> Workload:
     api = qb if api is None else api
-    u = make_u(api)
+    u = make_u(api, activation)
     sizes, dtype, seed = [2, 64, 64, 64, 64, 1], np.float32, 1
     n = _scaled(65536, points, 65536)
     nb = _scaled(4096, points, 65536)
@@ -139,9 +141,9 @@ def poisson2d(points: int | None = None, api=None) -> Workload:
 
 
 # -- 3: viscous Burgers (x, t), float64 --------------------------------------------
-def burgers(points: int | None = None, api=None) -> Workload:
+def burgers(points: int | None = None, api=None, activation: str = "tanh") -> Workload:
     api = qb if api is None else api
-    u = make_u(api)
+    u = make_u(api, activation)
     sizes, dtype, seed = [2] + [128] * 8 + [1], np.float64, 2
     n = _scaled(262144, points, 262144)
     n_ic = _scaled(8192, points, 262144)
@@ -171,9 +173,9 @@ def burgers(points: int | None = None, api=None) -> Workload:
 
 
 # -- 4: 3-D heat equation (x, y, z, t), float32 -------------------------------------
-def heat3d(points: int | None = None, api=None) -> Workload:
+def heat3d(points: int | None = None, api=None, activation: str = "tanh") -> Workload:
     api = qb if api is None else api
-    u = make_u(api)
+    u = make_u(api, activation)
     sizes, dtype, seed = [4] + [256] * 6 + [1], np.float32, 3
     n = _scaled(1048576, points, 1048576)
     alpha, decay = 0.1, 0.3 * math.pi**2
@@ -195,9 +197,9 @@ def heat3d(points: int | None = None, api=None) -> Workload:
 
 
 # -- 5: Euler-Bernoulli beam, 4th order, float32 --------------------------------------
-def beam(points: int | None = None, api=None) -> Workload:
+def beam(points: int | None = None, api=None, activation: str = "tanh") -> Workload:
     api = qb if api is None else api
-    u = make_u(api)
+    u = make_u(api, activation)
     sizes, dtype, seed = [1] + [64] * 4 + [1], np.float32, 4
     n = _scaled(1048576, points, 1048576)
 
@@ -219,6 +221,7 @@ WORKLOADS = {"poisson1d": poisson1d, "poisson2d": poisson2d, "burgers": burgers,
 ORDER = ["poisson1d", "poisson2d", "burgers", "heat3d", "beam"]
 
 
-def make(name: str, points: int | None = None, api=None) -> Workload:
-    """`api` selects the module the loss is written against (default: this package)."""
-    return WORKLOADS[name](points, api)
+def make(name: str, points: int | None = None, api=None, activation: str = "tanh") -> Workload:
+    """`api` selects the module the loss is written against (default: this package);
+    `activation` ("tanh" or "sin") the hidden layers' activation."""
+    return WORKLOADS[name](points, api, activation)

@@ -20,9 +20,9 @@ def relative_error(actual, expected) -> float:
     return float(np.max(np.abs(actual - expected))) / scale
 
 
-def traced(name: str, points: int | None):
+def traced(name: str, points: int | None, activation: str = "tanh"):
     """(workload, traced loss without a device plan, named inputs)."""
-    w = workloads.make(name, points)
+    w = workloads.make(name, points, activation=activation)
     args = (w.params, *w.data)
     compiled = CompiledLoss(w.loss, args, (0,), 0, build_plan=False)
     return w, compiled, compiled.named_inputs(args)

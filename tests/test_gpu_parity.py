@@ -140,3 +140,21 @@ def test_trainer_reduces_the_loss(cuda_device):
     params = trainer.params
     assert params[0]["w"].shape == (1, 16) and params[2]["b"].shape == (1,)
     assert trainer._executor.device_buffer_count > 0
+
+
+@pytest.mark.parametrize("name", ["poisson1d", "poisson2d", "burgers", "heat3d", "beam"])
+def test_sin_activation_matches_the_oracle(cuda_device, name):
+    # Networks with a sin activation run on the layer-wise engine, whatever their width.
+    w, compiled, inputs = traced(name, SMALL[name], "sin")
+    expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    plan.execute()
+    assert plan.query(_lib.Q_ENGINE) in (0, 3)
+    outputs = plan.outputs()
+    tol = TOLERANCE[np.dtype(w.dtype)]
+    assert relative_error(outputs[0], expected_loss) <= tol
+    for got, expected, (pname, _, _) in zip(outputs[1:], expected_grads, compiled.spec.parameters):
+        assert relative_error(got.reshape(expected.shape), expected) <= tol, pname
+    plan.close()

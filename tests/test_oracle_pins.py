@@ -139,14 +139,16 @@ def test_vectorised_random_streams_equal_the_scalar_restatement():
         rng.glorot_normal((7, 5), key).astype(np.float32).tobytes()
 
 
-@pytest.mark.parametrize("name,points", [("poisson1d", 16), ("poisson2d", 16), ("burgers", 8), ("heat3d", 4),
-                                         ("beam", 8)])
-def test_contracted_oracle_equals_the_literal_oracle(name, points):
+@pytest.mark.parametrize("name,points,activation", [
+    ("poisson1d", 16, "tanh"), ("poisson2d", 16, "tanh"), ("burgers", 8, "tanh"), ("heat3d", 4, "tanh"),
+    ("beam", 8, "tanh"), ("poisson1d", 16, "sin"), ("burgers", 8, "sin"), ("beam", 8, "sin")])
+def test_contracted_oracle_equals_the_literal_oracle(name, points, activation):
     # Literal: the reference's graph transforms and per-node rounding.  Contracted:
     # jets forward, one reverse sweep, float64.  Equal up to rounding.
-    w, compiled, inputs = traced(name, points)
+    w, compiled, inputs = traced(name, points, activation)
+    assert compiled.spec.activation == activation
     expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
-    wl = workloads.make(name, points, api=literal)
+    wl = workloads.make(name, points, api=literal, activation=activation)
     value, grads = literal.value_and_grad(wl.loss)(wl.params, *wl.data)
     tolerance = 1e-13 if np.dtype(w.dtype) == np.float64 else 2e-6
     assert value.dtype == np.dtype(w.dtype)
@@ -176,3 +178,20 @@ def test_threads_do_not_change_the_contracted_oracle_beyond_rounding():
     assert abs(l1 - l4) <= 1e-13 * abs(l1)
     for a, b in zip(g1, g4):
         assert relative_error(a, b) <= 1e-12
+
+
+def test_a_network_cannot_mix_activations():
+    import quabla_b200 as qb
+    from quabla_b200._errors import UnsupportedOperationError
+    from quabla_b200._transforms import CompiledLoss
+
+    def loss(params, x):
+        def u(t):
+            h = qb.tanh(t.reshape(1, -1) @ params[0]["w"] + params[0]["b"])
+            h = qb.sin(h @ params[1]["w"] + params[1]["b"])
+            return (h @ params[2]["w"] + params[2]["b"]).reshape(())
+        return qb.mean(qb.vmap(u)(x) ** 2)
+
+    params = workloads.init_mlp(qb.random.key(0), [1, 8, 8, 1])
+    with pytest.raises(UnsupportedOperationError):
+        CompiledLoss(loss, (params, np.linspace(0.0, 1.0, 8)), (0,), 0, build_plan=False)
