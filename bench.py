@@ -60,18 +60,65 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of one GPU while the timed region runs:
+    NVML from a thread every 10 ms (plus one reading at the start and one at the end, so that
+    even a region of a few milliseconds is covered); nvidia-smi when NVML cannot be loaded.
+    Read-only: no setting of the GPU is touched."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, index: int) -> None:
+    def __init__(self, index: int, uuid: str | None = None) -> None:
         self.index = index
         self.process = None
         self.lines: list[str] = []
+        self.sm: list[float] = []
+        self.reasons: set[str] = set()
+        self.sm_max = None
+        self.nvml = None
+        self.handle = None
+        self.stop_flag = threading.Event()
+        self.thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            handle = None
+            if uuid:
+                try:
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+                except Exception:
+                    handle = None
+            self.handle = handle if handle is not None else pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+        except Exception:
+            self.nvml = None
+
+    def _read_nvml(self) -> None:
+        nv = self.nvml
+        try:
+            self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+            getter = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            mask = int(getter(self.handle))
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _loop(self) -> None:
+        while not self.stop_flag.wait(0.01):
+            self._read_nvml()
 
     def start(self) -> None:
+        if self.nvml is not None:
+            self._read_nvml()
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+            return
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
@@ -85,8 +132,15 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self) -> dict:
+        if self.nvml is not None:
+            self._read_nvml()
+            self.stop_flag.set()
+            if self.thread is not None:
+                self.thread.join(timeout=1.0)
+            return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_max_mhz": self.sm_max,
+                    "samples": len(self.sm), "reasons": sorted(self.reasons), "source": "nvml, 10 ms"}
         if self.process is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
         self.process.terminate()
         sm, sm_max, reasons = [], [], set()
@@ -104,7 +158,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(sm_max) if sm_max else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi, 100 ms"}
 
 
 def cpu_sample(workload_name: str, seconds: float, threads: int):
@@ -220,8 +274,10 @@ def main() -> None:
         plan.attach_comm(ids[0], rank, world, "mean")
     stream = torch.cuda.ExternalStream(plan.query(_lib.Q_STREAM), device=device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # larger than the 126 MB L2
+    align_token = torch.zeros(1, device=device)
 
     kernel_ns: list = []  # device time of the interior point set's kernels, one entry per timed step
+    allreduce_ns: list = []  # device time of the gradient all-reduce (waits for the other ranks included)
 
     def barrier():
         if world > 1:
@@ -236,11 +292,17 @@ def main() -> None:
         for i in range(count):
             flush.fill_(i & 0xFF)
             barrier()  # ranks enter the step together: the bracket times the step, not the ranks' skew
+            if world > 1:
+                # ... and their streams too: a one-element all-reduce on the plan's stream releases every
+                # rank's stream at the same moment, so host jitter after the barrier stays outside the bracket.
+                with torch.cuda.stream(stream):
+                    torch.distributed.all_reduce(align_token)
             starts[i].record(stream)
             step_fn()
             stops[i].record(stream)
             stops[i].synchronize()
             kernel_ns.append(plan.query(_lib.Q_SET0_NANOSECONDS))
+            allreduce_ns.append(plan.query(_lib.Q_ALLREDUCE_NANOSECONDS))
         return sum(a.elapsed_time(b) for a, b in zip(starts, stops))
 
     def device_step():
@@ -257,7 +319,11 @@ def main() -> None:
         device_step()
     plan.synchronize()
     barrier()
-    sampler = ClockSampler(local_rank)
+    try:
+        gpu_uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+    except Exception:
+        gpu_uuid = None
+    sampler = ClockSampler(local_rank, gpu_uuid)
     sampler.start()
     launches0 = plan.query(_lib.Q_KERNEL_LAUNCHES)
     device_ms = timed_steps(device_step, args.steps)
@@ -329,7 +395,8 @@ def main() -> None:
         "config": {"workload": w.name, "description": w.description, "interior_points_per_gpu": per_gpu,
                    "other_sets": w.extra, "optimizer": "adam lr=1e-3", "parameters": w.parameter_count,
                    "engine": engine_name,
-                   "l2": "256 MB written between timed steps, outside the per-step event brackets"},
+                   "l2": "256 MB written between timed steps, outside the per-step event brackets",
+                   "allreduce_us_rank0": float(np.mean(allreduce_ns)) * 1e-3 if world > 1 else 0.0},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches),
         "clocks": clocks,

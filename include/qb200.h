@@ -86,7 +86,8 @@ typedef enum qb200_query {
     QB200_Q_SCRATCH_BYTES = 7,       /* bytes of saved-jet scratch the plan holds */
     QB200_Q_STEP_COUNT = 8,          /* optimizer updates applied so far */
     QB200_Q_ENGINE = 9,              /* 0: layer-wise (FP pipe), 1: fused (FP32 pipe), 2: fused (mma 3xTF32), 3: layer-wise with tcgen05 GEMMs */
-    QB200_Q_SET0_NANOSECONDS = 10    /* device time of the last execute's kernels for point set 0 (events) */
+    QB200_Q_SET0_NANOSECONDS = 10,   /* device time of the last execute's kernels for point set 0 (events) */
+    QB200_Q_ALLREDUCE_NANOSECONDS = 11 /* device time of the last execute's gradient all-reduce, waits for peers included */
 } qb200_query;
 
 /* Opcodes of the per-point residual program (see qb200_desc_set_program). */

@@ -19,7 +19,8 @@ ACT_TANH, ACT_SIN = 0, 1
 SGD, ADAM = 0, 1
 REDUCE_SUM, REDUCE_MEAN = 0, 1
 (Q_DEVICE_BUFFER_COUNT, Q_NONFINITE_CLIP_SEEN, Q_STREAM, Q_PARAMETER_COUNT, Q_OUTPUT_COUNT,
- Q_KERNEL_LAUNCHES, Q_FLAT_DEVICE_PTR, Q_SCRATCH_BYTES, Q_STEP_COUNT, Q_ENGINE, Q_SET0_NANOSECONDS) = range(11)
+ Q_KERNEL_LAUNCHES, Q_FLAT_DEVICE_PTR, Q_SCRATCH_BYTES, Q_STEP_COUNT, Q_ENGINE, Q_SET0_NANOSECONDS,
+ Q_ALLREDUCE_NANOSECONDS) = range(12)
 
 
 class OptConfig(C.Structure):

@@ -265,7 +265,8 @@ class Plan final : public qb200_plan {
     std::vector<char> tc_fwd_, tc_bwd_, tc_wgrad_;
     bool tc_any_ = false;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;  // around the kernels of point set 0
-    bool ev_valid_ = false;
+    cudaEvent_t ev_ar0_ = nullptr, ev_ar1_ = nullptr;    // around the gradient all-reduce
+    bool ev_valid_ = false, ev_ar_valid_ = false;
     int64_t launches_ = 0;
     int64_t steps_ = 0;
     bool executed_ = false;
@@ -304,7 +305,9 @@ void Plan<T>::release() {
     buffers_.clear();
     if (ev_begin_ != nullptr) cudaEventDestroy(ev_begin_);
     if (ev_end_ != nullptr) cudaEventDestroy(ev_end_);
-    ev_begin_ = ev_end_ = nullptr;
+    if (ev_ar0_ != nullptr) cudaEventDestroy(ev_ar0_);
+    if (ev_ar1_ != nullptr) cudaEventDestroy(ev_ar1_);
+    ev_begin_ = ev_end_ = ev_ar0_ = ev_ar1_ = nullptr;
     if (stream_ != nullptr) cudaStreamDestroy(stream_);
     stream_ = nullptr;
 }
@@ -319,6 +322,8 @@ qb200_status Plan<T>::init() {
     QB_CUDA(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     QB_CUDA(cudaEventCreate(&ev_begin_));
     QB_CUDA(cudaEventCreate(&ev_end_));
+    QB_CUDA(cudaEventCreate(&ev_ar0_));
+    QB_CUDA(cudaEventCreate(&ev_ar1_));
 
     L_ = (int)desc_.sizes.size() - 1;
     w_leaf_.assign(L_, -1);
@@ -1058,7 +1063,10 @@ qb200_status Plan<T>::all_reduce() {
     if (comm_ == nullptr) return QB200_OK;
     const NcclApi* api = nccl_api();
     if (api == nullptr) return QB200_NCCL_ERROR;
+    cudaEventRecord(ev_ar0_, stream_);
     ncclResult_t r = api->AllReduce(d_flat_, d_flat_, 1 + n_params_, DTypeOf<T>::nccl, ncclSum, comm_, stream_);
+    cudaEventRecord(ev_ar1_, stream_);
+    ev_ar_valid_ = r == ncclSuccess;
     if (r != ncclSuccess) {
         // Failure contract: drop the communicator, the caller re-attaches
         // (crates/quabla-core/src/tensor_ir/cuda.rs:132-145, 699-716).
@@ -1217,6 +1225,17 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
         case QB200_Q_SCRATCH_BYTES: *out = (int64_t)scratch_bytes_; return QB200_OK;
         case QB200_Q_STEP_COUNT: *out = steps_; return QB200_OK;
         case QB200_Q_ENGINE: *out = fused_ ? (fused_tensor_core_ ? 2 : 1) : (tc_any_ ? 3 : 0); return QB200_OK;
+        case QB200_Q_ALLREDUCE_NANOSECONDS: {
+            if (!ev_ar_valid_) {
+                *out = 0;  // no communicator attached, or no execute yet
+                return QB200_OK;
+            }
+            float ms = 0.0f;
+            QB_CUDA(cudaEventSynchronize(ev_ar1_));
+            QB_CUDA(cudaEventElapsedTime(&ms, ev_ar0_, ev_ar1_));
+            *out = (int64_t)((double)ms * 1e6);
+            return QB200_OK;
+        }
         case QB200_Q_SET0_NANOSECONDS: {
             if (!ev_valid_) return fail(QB200_INVALID, "no execute has run yet");
             QB_TRY(use_device());
