@@ -105,7 +105,7 @@ cudaError_t fused_prep_launch(const float* params, const int* w_off, int hidden_
 
 template <typename T>
 cudaError_t fused_reduce_launch(const T* grad_cta, double* acc, int P, int ctas, cudaStream_t stream) {
-    fused_reduce_kernel<T><<<(P + 255) / 256, 256, 0, stream>>>(grad_cta, acc, P, ctas);
+    fused_reduce_kernel<T><<<(P + 31) / 32, 256, 0, stream>>>(grad_cta, acc, P, ctas);
     return cudaGetLastError();
 }
 
