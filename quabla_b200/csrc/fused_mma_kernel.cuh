@@ -152,7 +152,8 @@ struct MmaGeom {
     static constexpr int OFF_BAR = OFF_UH + ROWS;           // 2 mbarriers (4 words)
     static constexpr int TOTAL = OFF_BAR + 4;
     static constexpr size_t SMEM_BASE_BYTES = ((size_t)TOTAL * sizeof(float) + 15) / 16 * 16;
-    static constexpr size_t SCRATCH_PER_CTA = (size_t)S * TP * W;
+    // Saved jets keep the row stride of the shared-memory operand (LDA), so that one bulk copy saves a layer.
+    static constexpr size_t SCRATCH_PER_CTA = (size_t)S * TP * LDA;
 };
 
 // acc[s][j] += A[rows of stream s][64] * B[64][16 columns of this warp], 3xTF32.
@@ -343,8 +344,19 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                 const uint32_t* whi = wbuf + (use & 1) * 2 * WIMG_PLANE;
                 mbar_wait(bars + (use & 1), (uint32_t)((use >> 1) & 1), a.error);
                 __syncthreads();  // the previous epilogue's activations are in place
+                if (backward && tid == 0) {
+                    // Save layer l-1's jets for the reverse sweep: the operand tile as it sits in shared memory,
+                    // one bulk copy (TMA engine) instead of 8-byte stores from every thread.
+                    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                                     sh + (size_t)(l - 1) * G::SCRATCH_PER_CTA),
+                                 "r"(smem_u32(act)), "r"((uint32_t)(ROWS * LDA * sizeof(float)))
+                                 : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
                 QB_PHASE(0);      // wait for the weight image
                 warp_gemm_3xtf32<S, TP, LDA>(act, whi, whi + WIMG_PLANE, row0, col0, lane, acc);
+                // The epilogue overwrites the operand: the bulk copy must have read it.
+                if (backward && tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncthreads();
                 issue(use + 2);
                 ++use;
@@ -358,7 +370,6 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     for (int c = 0; c < 4; ++c) acc[0][j][c] += bl[unit_of(j, c)];
             }
             float* zl = sz + (size_t)l * G::SCRATCH_PER_CTA;
-            float* hl = sh + (size_t)l * G::SCRATCH_PER_CTA;
             if (backward) {
 #pragma unroll
                 for (int s = 0; s < S; ++s)
@@ -380,16 +391,6 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
 #pragma unroll
                     for (int s = 0; s < S; ++s) acc[s][j][c] = v[s];
                 }
-            if (backward && l + 1 < L) {
-#pragma unroll
-                for (int s = 0; s < S; ++s)
-#pragma unroll
-                    for (int j = 0; j < 2; ++j)
-#pragma unroll
-                        for (int i = 0; i < 2; ++i)
-                            st2(hl + ((size_t)s * TP + row0 + g + 8 * i) * W + col0 + j * 8 + 2 * t, acc[s][j][2 * i],
-                                acc[s][j][2 * i + 1]);
-            }
             if (l + 1 < L) {
 #pragma unroll
                 for (int s = 0; s < S; ++s)
@@ -399,6 +400,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                         for (int i = 0; i < 2; ++i)
                             st2(act + (s * TP + row0 + g + 8 * i) * LDA + col0 + j * 8 + 2 * t, acc[s][j][2 * i],
                                 acc[s][j][2 * i + 1]);
+                // The next iteration saves this tile with a bulk copy: make the writes visible to that proxy.
+                if (backward) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
         }
 
@@ -446,6 +449,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
         __syncthreads();
         QB_PHASE(3);  // head and residual program
         if (!backward) continue;
+        // The saved jets are read back below (cp.async): the bulk stores must have completed.  The
+        // barriers of the head phase separate this wait from the first prefetch.
+        if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 
         // ------------------------------ backward ------------------------------
         {
@@ -483,7 +489,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                 // transposed jets are computed.
                 const float* hp = sh + (size_t)(l - 1) * G::SCRATCH_PER_CTA;
                 for (int e = tid; e < ROWS * 16; e += FUSED_THREADS)
-                    cp_async16(ht + (e >> 4) * LDH + 4 * (e & 15), hp + (size_t)(e >> 4) * W + 4 * (e & 15));
+                    cp_async16(ht + (e >> 4) * LDH + 4 * (e & 15), hp + (size_t)(e >> 4) * LDA + 4 * (e & 15));
                 cp_async_commit();
             }
 #pragma unroll
