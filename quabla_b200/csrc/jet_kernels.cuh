@@ -124,12 +124,17 @@ template <typename T, int CODE, bool HEAD>
 __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
                                                                T* __restrict__ G, long long plane,
                                                                const T* __restrict__ Uhat, const T* __restrict__ w_head,
-                                                               int d, long long C, int act) {
+                                                               int d, long long C, int act, T* __restrict__ bias_partial) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
     constexpr int S = SG::S, V = JV::V;
     const long long nvec = plane / V;
+    // Bias gradient (column sums of the primal pre-activation cotangents), when asked for: the
+    // grid stride is a multiple of the layer width, so a thread always owns the same V units.
+    T bsum[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) bsum[i] = T(0);
     for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < nvec; e += (long long)gridDim.x * blockDim.x) {
         VT qz[S], qg[S];
         // tanh rebuilds its derivatives from the saved activation, other activations from z_0.
@@ -175,6 +180,24 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
         }
 #pragma unroll
         for (int s = 0; s < S; ++s) reinterpret_cast<VT*>(G + (long long)s * plane)[e] = JV::pack(gl[s]);
+#pragma unroll
+        for (int i = 0; i < V; ++i) bsum[i] += gl[0][i];
+    }
+    if (bias_partial != nullptr) {
+        // The block covers 256 V / d rows of the plane: add them in row order, one partial per block.
+        __shared__ T red[256][V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) red[threadIdx.x][i] = bsum[i];
+        __syncthreads();
+        const int groups = d / V;  // threads per row
+        if ((int)threadIdx.x < groups) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                T total = red[threadIdx.x][i];
+                for (int r = groups; r < 256; r += groups) total += red[threadIdx.x + r][i];
+                bias_partial[(long long)blockIdx.x * d + threadIdx.x * V + i] = total;
+            }
+        }
     }
 }
 
@@ -185,6 +208,13 @@ inline bool jet_sig_eligible(int code, long long plane, const void* a, const voi
     const bool known = code == 0 || code == 1 || code == 2 || code == 4 || code == 7 || code == 12 || code == 187;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
     return known && plane % JetVec<T>::V == 0 && (bits & 15) == 0;
+}
+
+// Whether the backward kernel can also form the bias-gradient partials of a layer of width d:
+// its grid stride (256 V elements per block) must cover whole rows.
+template <typename T>
+inline bool jet_bias_fusable(int d) {
+    return d >= JetVec<T>::V && d % JetVec<T>::V == 0 && (256 * JetVec<T>::V) % d == 0;
 }
 
 inline int jet_sig_grid(long long vectors) {
@@ -208,10 +238,10 @@ inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, 
 
 template <typename T, bool HEAD>
 inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
-                                         const T* w_head, int d, long long C, int act, cudaStream_t stream) {
+                                         const T* w_head, int d, long long C, int act, T* bias_partial, cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
 #define QB_JET_BWD(CODE) \
-    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act)
+    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, bias_partial)
     switch (code) {
         case 0: QB_JET_BWD(0); break;
         case 1: QB_JET_BWD(1); break;
@@ -225,17 +255,17 @@ inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal,
 }
 
 template <typename T>
-inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, int act,
-                                    cudaStream_t stream) {
-    jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, 1, 1, act, stream);
+inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, int d, int act,
+                                    T* bias_partial, cudaStream_t stream) {
+    jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, stream);
 }
 
 // Last hidden layer: the cotangents of H are Uhat (x) w_head, formed inside the kernel; d % V == 0
 // and w_head 16-byte aligned are the caller's to check.
 template <typename T>
 inline void jet_backward_head_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
-                                     const T* w_head, int d, long long C, int act, cudaStream_t stream) {
-    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, act, stream);
+                                     const T* w_head, int d, long long C, int act, T* bias_partial, cudaStream_t stream) {
+    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, act, bias_partial, stream);
 }
 
 }  // namespace qb

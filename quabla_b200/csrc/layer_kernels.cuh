@@ -213,27 +213,37 @@ __global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ G, T*
 
 // acc[i] += sum_z partial[z][i] in double, in a fixed order: the second pass that keeps gradients
 // bit-reproducible (the reference sums long axes in double as well, cuda.rs:8202-8247).  A block
-// owns 32 consecutive elements; thread (x, y) sums the slices z = y, y + 8, ... of element x
-// (coalesced along x), then the eight partial sums are added in y order.
-template <typename T>
+// owns EX consecutive elements; thread (x, y) sums the slices z = y, y + G, ... of element x
+// (G = 256 / EX groups, coalesced along x), then the G partial sums are added in y order.
+// EX = 32 suits many elements and few slices, EX = 8 few elements and thousands of slices.
+template <typename T, int EX>
 __global__ void __launch_bounds__(256) accumulate_partials_kernel(const T* __restrict__ partial, double* __restrict__ acc,
                                                                   int count, int slices) {
-    __shared__ double part[8][33];
-    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
-    const int i = blockIdx.x * 32 + x;
+    constexpr int GROUPS = 256 / EX;
+    __shared__ double part[GROUPS][EX + 1];
+    const int x = threadIdx.x % EX, y = threadIdx.x / EX;
+    const int i = blockIdx.x * EX + x;
     double s = 0.0;
     if (i < count) {
 #pragma unroll 4
-        for (int z = y; z < slices; z += 8) s += (double)partial[(long long)z * count + i];
+        for (int z = y; z < slices; z += GROUPS) s += (double)partial[(long long)z * count + i];
     }
     part[y][x] = s;
     __syncthreads();
     if (y == 0 && i < count) {
         double total = part[0][x];
 #pragma unroll
-        for (int k = 1; k < 8; ++k) total += part[k][x];
+        for (int k = 1; k < GROUPS; ++k) total += part[k][x];
         acc[i] += total;
     }
+}
+
+template <typename T>
+inline void accumulate_partials_launch(const T* partial, double* acc, int count, int slices, cudaStream_t stream) {
+    if (slices > 256 && count <= 4096)
+        accumulate_partials_kernel<T, 8><<<(count + 7) / 8, 256, 0, stream>>>(partial, acc, count, slices);
+    else
+        accumulate_partials_kernel<T, 32><<<(count + 31) / 32, 256, 0, stream>>>(partial, acc, count, slices);
 }
 
 // out[i] = sum_z partial[z][i], z ascending, summed in double and rounded once.

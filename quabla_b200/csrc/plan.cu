@@ -875,8 +875,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                 QB_TRY(tc_status);
                 const int count = d_in * d_out;
                 const int slices = (int)((rows + tc_chunk - 1) / tc_chunk);
-                accumulate_partials_kernel<T><<<(count + 31) / 32, 256, 0, stream_>>>(
-                    wpartial_, d_acc_ + leaves_[leaf].offset, count, slices);
+                accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset, count, slices, stream_);
                 return launched("accumulate_partials_kernel");
             }
         }
@@ -901,8 +900,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                 else
                     skinny_wgrad_kernel<T, 4, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
                 QB_TRY(launched("skinny_wgrad_kernel"));
-                accumulate_partials_kernel<T><<<(count + 31) / 32, 256, 0, stream_>>>(
-                    wpartial_, d_acc_ + leaves_[leaf].offset, count, slices);
+                accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset, count, slices, stream_);
                 return launched("accumulate_partials_kernel");
             }
         }
@@ -927,8 +925,8 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         (void)e;
         QB_TRY(launched("gemm_kernel(wgrad)"));
         const int count = d_in * d_out;
-        accumulate_partials_kernel<T><<<(count + 31) / 32, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
-                                                                                count, slices);
+        accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset,
+                                                                                count, slices, stream_);
         return launched("accumulate_partials_kernel");
     };
     auto bgrad = [&](const T* Gz, int d_out, int leaf) -> qb200_status {
@@ -942,8 +940,8 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         dim3 grid(col_blocks, slices);
         colsum_kernel<T><<<grid, 256, 0, stream_>>>(Gz, wpartial_, C, d_out, row_chunk);
         QB_TRY(launched("colsum_kernel"));
-        accumulate_partials_kernel<T><<<(d_out + 31) / 32, 256, 0, stream_>>>(wpartial_, d_acc_ + leaves_[leaf].offset,
-                                                                                d_out, slices);
+        accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset,
+                                                                                d_out, slices, stream_);
         return launched("accumulate_partials_kernel");
     };
 
@@ -963,16 +961,27 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     }
     for (int l = head; l >= 1; --l) {
         const long long plane = (long long)C * sz[l];
+        // The vectorised kernel can form the bias-gradient partials (one row of sz[l] per block) on its way.
+        const bool sig = (l == head && head_fused) || jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], G_[cur]);
+        const int jet_grid = jet_sig_grid(plane / JetVec<T>::V);
+        const bool bias_fused = sig && b_leaf_[l - 1] >= 0 && jet_bias_fusable<T>(sz[l]) &&
+                                (size_t)jet_grid * sz[l] <= wpartial_elems_;
+        T* bias_partial = bias_fused ? wpartial_ : nullptr;
         if (l == head && head_fused)
             jet_backward_head_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, Uhat_, weight(head), sz[head], C,
-                                        desc_.activation, stream_);
-        else if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], G_[cur]))
-            jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, desc_.activation, stream_);
+                                        desc_.activation, bias_partial, stream_);
+        else if (sig)
+            jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, sz[l], desc_.activation, bias_partial,
+                                       stream_);
         else
             jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec, desc_.activation);
         QB_TRY(launched("jet_backward_kernel"));
+        if (bias_fused) {
+            accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[b_leaf_[l - 1]].offset, sz[l], jet_grid, stream_);
+            QB_TRY(launched("accumulate_partials_kernel"));
+        }
         QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1], l - 1));
-        QB_TRY(bgrad(G_[cur], sz[l], b_leaf_[l - 1]));
+        if (!bias_fused) QB_TRY(bgrad(G_[cur], sz[l], b_leaf_[l - 1]));
         if (l > 1) {
             GemmArgs<T> g;
             g.A = G_[cur];
