@@ -22,19 +22,23 @@ FusedEntry<T> make_entry() {
     e.smem_bytes = G::SMEM_BASE_BYTES;
     e.scratch_per_layer = G::SCRATCH_PER_CTA;
     e.tensor_core = false;
+    e.threads = FUSED_THREADS;
+    e.ctas_per_sm = 1;
     return e;
 }
 
-template <int CODE>
+template <int CODE, int PG>
 FusedEntry<float> make_mma_entry() {
-    typedef MmaGeom<CODE> G;
+    typedef MmaGeom<CODE, PG> G;
     FusedEntry<float> e;
-    e.kernel = fused_mma_kernel<CODE>;
+    e.kernel = fused_mma_kernel<CODE, PG>;
     e.streams = G::S;
     e.tile_points = G::TP;
     e.smem_bytes = G::SMEM_BASE_BYTES;
     e.scratch_per_layer = G::SCRATCH_PER_CTA;
     e.tensor_core = true;
+    e.threads = G::THREADS;
+    e.ctas_per_sm = 3 - PG;
     return e;
 }
 
@@ -45,12 +49,19 @@ bool want_simt() {
     return env != nullptr && strcmp(env, "simt") == 0;
 }
 
+// QB200_FUSED_TILE=32 selects the one-CTA-per-SM variant (32 points per tile, 256 threads); the
+// default is two CTAs per SM with 16 points per tile each.
+bool want_wide_tile() {
+    const char* env = getenv("QB200_FUSED_TILE");
+    return env != nullptr && strcmp(env, "32") == 0;
+}
+
 }  // namespace
 
-#define QB_MMA_CASE(CODE)                             \
-    if (width == 64 && code == CODE && !want_simt()) { \
-        *out = make_mma_entry<CODE>();                \
-        return true;                                  \
+#define QB_MMA_CASE(CODE)                                                                  \
+    if (width == 64 && code == CODE && !want_simt()) {                                      \
+        *out = want_wide_tile() ? make_mma_entry<CODE, 2>() : make_mma_entry<CODE, 1>();   \
+        return true;                                                                        \
     }
 
 // Signature codes: 0 = value only; 1 = {1}; 2 = {2}; 3 = {3}; 4 = {4}; 6 = {1,1};
@@ -85,7 +96,13 @@ cudaError_t fused_launch(const FusedEntry<T>& entry, int grid, cudaStream_t stre
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(entry.kernel),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    entry.kernel<<<grid, FUSED_THREADS, smem, stream>>>(args);
+    if (entry.ctas_per_sm > 1) {
+        // Co-residency needs the whole shared-memory carve-out.
+        e = cudaFuncSetAttribute(reinterpret_cast<const void*>(entry.kernel),
+                                 cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+    }
+    entry.kernel<<<grid, entry.threads, smem, stream>>>(args);
     return cudaGetLastError();
 }
 

@@ -16,6 +16,8 @@ struct FusedEntry {
     size_t smem_bytes;            // dynamic shared memory per CTA, without the residual program
     size_t scratch_per_layer;     // saved-jet elements per CTA per hidden layer (each of Z and H)
     bool tensor_core;             // 3xTF32 variant: needs the pre-split weight images
+    int threads;                  // threads per CTA
+    int ctas_per_sm;              // CTAs the kernel is sized to co-reside on one SM
 };
 
 constexpr size_t FUSED_MAX_SMEM = 227 * 1024;

@@ -129,12 +129,17 @@ static __global__ void prep_weights_kernel(const float* __restrict__ params, Pre
     }
 }
 
-template <int CODE>
+// PG = point groups of 16 per tile.  PG = 2: 256 threads, 32 points, two weight buffers, one CTA per
+// SM.  PG = 1: 128 threads, 16 points, one weight buffer; half the shared memory, so two CTAs share
+// an SM and one's GEMM phases overlap the other's epilogues and residual program.
+template <int CODE, int PG>
 struct MmaGeom {
     typedef Sig<CODE> sig;
     static constexpr int W = 64;
     static constexpr int S = sig::S;
-    static constexpr int TP = 32;
+    static constexpr int THREADS = 128 * PG;
+    static constexpr int NBUF = PG;  // weight-image buffers
+    static constexpr int TP = 16 * PG;
     static constexpr int ROWS = S * TP;
     // Every operand row is 16-byte aligned and its stride is 4 (mod 32) words, so the eight
     // row addresses of an ldmatrix tile fall into distinct bank groups.
@@ -144,12 +149,12 @@ struct MmaGeom {
     static constexpr int LDH = 72;        // previous layer's jets [row][unit], read k-major: stride 8 (mod 32)
     static constexpr int OFF_HT = OFF_ACT + ROWS * LDA;     // [ROWS][LDH] previous layer's jets
     static constexpr int OFF_ZT = OFF_HT + ROWS * LDH;      // [64][LDT] pre-activation cotangents, transposed
-    static constexpr int OFF_WB = OFF_ZT + W * LDT;         // 2 buffers x {hi, lo} x [64][WIMG_LDH]
-    static constexpr int OFF_RED = OFF_WB + 4 * WIMG_PLANE; // [5][2][64] column reductions / [4][S][TP] head partials
-    static constexpr int RED = (5 * 2 * W > 4 * ROWS) ? 5 * 2 * W : 4 * ROWS;
+    static constexpr int OFF_WB = OFF_ZT + W * LDT;         // NBUF buffers x {hi, lo} x [64][WIMG_LDH]
+    static constexpr int OFF_RED = OFF_WB + NBUF * 2 * WIMG_PLANE;  // [5][PG][64] column reductions / [4][S][TP] head partials
+    static constexpr int RED = (5 * PG * W > 4 * ROWS) ? 5 * PG * W : 4 * ROWS;
     static constexpr int OFF_U = OFF_RED + RED;             // [S][TP]
     static constexpr int OFF_UH = OFF_U + ROWS;             // [S][TP]
-    static constexpr int OFF_BAR = OFF_UH + ROWS;           // 2 mbarriers (4 words)
+    static constexpr int OFF_BAR = OFF_UH + ROWS;           // NBUF mbarriers (4 words reserved)
     static constexpr int TOTAL = OFF_BAR + 4;
     static constexpr size_t SMEM_BASE_BYTES = ((size_t)TOTAL * sizeof(float) + 15) / 16 * 16;
     // Saved jets keep the row stride of the shared-memory operand (LDA), so that one bulk copy saves a layer.
@@ -233,9 +238,10 @@ __device__ __forceinline__ void reduce_units_over_points(float (&v)[4], float* d
 #define QB_PHASE(i)
 #endif
 
-template <int CODE>
-__global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<float> a) {
-    typedef MmaGeom<CODE> G;
+template <int CODE, int PG>
+__global__ void __launch_bounds__(128 * PG, 3 - PG) fused_mma_kernel(FusedArgs<float> a) {
+    typedef MmaGeom<CODE, PG> G;
+    constexpr int THREADS = G::THREADS, NBUF = G::NBUF;
     typedef Sig<CODE> SG;
     constexpr int S = G::S, TP = G::TP, W = G::W, LDA = G::LDA, LDT = G::LDT, LDH = G::LDH, ROWS = G::ROWS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
     long long last_ = clock64();
 #endif
     const int g = lane >> 2, t = lane & 3;
-    const int pg = warp & 1, cg = warp >> 1;
+    const int pg = PG == 2 ? (warp & 1) : 0, cg = PG == 2 ? (warp >> 1) : warp;
     const int row0 = pg * 16;   // first point of the warp inside the tile
     const int col0 = cg * 16;   // first unit of the warp
     const int L = a.L, d0 = a.d0;
@@ -265,14 +271,14 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
     float* sz = a.scratch_z + (size_t)blockIdx.x * L * G::SCRATCH_PER_CTA;
     float* sh = a.scratch_h + (size_t)blockIdx.x * L * G::SCRATCH_PER_CTA;
 
-    for (int i = tid; i < a.prog.n_instr; i += FUSED_THREADS) code[i] = a.prog.code[i];
+    for (int i = tid; i < a.prog.n_instr; i += THREADS) code[i] = a.prog.code[i];
     if (backward)
-        for (int i = tid; i < a.P; i += FUSED_THREADS) my_grad[i] = 0.0f;
+        for (int i = tid; i < a.P; i += THREADS) my_grad[i] = 0.0f;
     double loss_sum = 0.0;
     const float seed = a.cotangent[0] * a.weight * a.extra;
     if (tid == 0) {
-        mbar_init(bars, 1);
-        mbar_init(bars + 1, 1);
+#pragma unroll
+        for (int b = 0; b < NBUF; ++b) mbar_init(bars + b, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -282,9 +288,9 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
     auto unit_of = [&](int j, int c) { return col0 + j * 8 + 2 * t + (c & 1); };
 
     const long long n_tiles = (a.n_points + TP - 1) / TP;
-    // Weight pipeline: the split weight images are bulk-copied into two shared buffers in
+    // Weight pipeline: the split weight images are bulk-copied into NBUF shared buffers in
     // the fixed order a tile uses them (forward layers 1..L-1, then the transposed images
-    // of layers L-1..1), two uses ahead of the GEMM that consumes them.
+    // of layers L-1..1), NBUF uses ahead of the GEMM that consumes them.
     const int HL = L - 1;
     const int uses_per_tile = backward ? 2 * HL : HL;
     const long long my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -296,15 +302,15 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
             const int idx = (int)(q % uses_per_tile);
             const int layer = idx < HL ? idx : 2 * HL - 1 - idx;
             const int plane = idx < HL ? 0 : 2;
-            uint64_t* bar = bars + (q & 1);
+            uint64_t* bar = bars + (q % NBUF);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect_tx(bar, WIMG_PAIR_BYTES);
-            bulk_load(wbuf + (q & 1) * 2 * WIMG_PLANE, images + ((size_t)layer * 4 + plane) * WIMG_PLANE,
+            bulk_load(wbuf + (q % NBUF) * 2 * WIMG_PLANE, images + ((size_t)layer * 4 + plane) * WIMG_PLANE,
                       WIMG_PAIR_BYTES, bar);
         }
     };
-    issue(0);
-    issue(1);
+#pragma unroll
+    for (int q = 0; q < NBUF; ++q) issue(q);
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const long long p0 = tile * TP;
         float acc[S][2][4];
@@ -341,8 +347,8 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     }
                 }
             } else {
-                const uint32_t* whi = wbuf + (use & 1) * 2 * WIMG_PLANE;
-                mbar_wait(bars + (use & 1), (uint32_t)((use >> 1) & 1), a.error);
+                const uint32_t* whi = wbuf + (use % NBUF) * 2 * WIMG_PLANE;
+                mbar_wait(bars + (use % NBUF), (uint32_t)((use / NBUF) & 1), a.error);
                 __syncthreads();  // the previous epilogue's activations are in place
                 if (backward && tid == 0) {
                     // Save layer l-1's jets for the reverse sweep: the operand tile as it sits in shared memory,
@@ -358,7 +364,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                 // The epilogue overwrites the operand: the bulk copy must have read it.
                 if (backward && tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 __syncthreads();
-                issue(use + 2);
+                issue(use + NBUF);
                 ++use;
                 QB_PHASE(1);  // forward GEMM
             }
@@ -474,7 +480,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     }
             reduce_units_over_points(pw, red + pg * W, lane, col0, t);
             __syncthreads();
-            if (tid < W) my_grad[a.w_off[L] + tid] += red[tid] + red[W + tid];
+            if (tid < W) my_grad[a.w_off[L] + tid] += PG == 2 ? red[tid] + red[W + tid] : red[tid];
             if (tid == 0 && a.b_off[L] >= 0) {
                 float total = 0.0f;
                 for (int p = 0; p < TP; ++p) total += uh[p];
@@ -488,7 +494,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                 // Prefetch the previous layer's saved jets (weight-gradient operand) while the
                 // transposed jets are computed.
                 const float* hp = sh + (size_t)(l - 1) * G::SCRATCH_PER_CTA;
-                for (int e = tid; e < ROWS * 16; e += FUSED_THREADS)
+                for (int e = tid; e < ROWS * 16; e += THREADS)
                     cp_async16(ht + (e >> 4) * LDH + 4 * (e & 15), hp + (size_t)(e >> 4) * LDA + 4 * (e & 15));
                 cp_async_commit();
             }
@@ -537,13 +543,13 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                                 for (int dj = 0; dj < SG::ndirs; ++dj) v += a.dirs[dj * d0 + k] * acc[SG::base(dj)][j][c];
                                 pw[2 * j + (c & 1)] += v;
                             }
-                        reduce_units_over_points(pw, red + ((1 + k) * 2 + pg) * W, lane, col0, t);
+                        reduce_units_over_points(pw, red + ((1 + k) * PG + pg) * W, lane, col0, t);
                     }
                 }
                 __syncthreads();
-                for (int e = tid; e < (1 + d0) * W; e += FUSED_THREADS) {
+                for (int e = tid; e < (1 + d0) * W; e += THREADS) {
                     const int which = e / W, n = e % W;
-                    const float total = red[(which * 2) * W + n] + red[(which * 2 + 1) * W + n];
+                    const float total = PG == 2 ? red[(which * 2) * W + n] + red[(which * 2 + 1) * W + n] : red[which * W + n];
                     if (which == 0) {
                         if (a.b_off[0] >= 0) my_grad[a.b_off[0] + n] += total;
                     } else {
@@ -573,17 +579,18 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
             cp_async_wait_all();
             __syncthreads();
             QB_PHASE(5);  // backward staging
-            if (tid < W && a.b_off[l] >= 0) my_grad[a.b_off[l] + tid] += red[tid] + red[W + tid];
-            // Weight gradient: dW[k][n] += sum_rows H[row][k] * Zhat[row][n]; warp: 16 k x 32 n,
+            if (tid < W && a.b_off[l] >= 0) my_grad[a.b_off[l] + tid] += PG == 2 ? red[tid] + red[W + tid] : red[tid];
+            // Weight gradient: dW[k][n] += sum_rows H[row][k] * Zhat[row][n]; warp: 16 k x 64/PG n,
             // the cotangents read from their transposed copy.
             {
-                const int k0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
+                constexpr int NJJ = 4 / PG;  // 16-column groups of this warp's (64 / PG) columns
+                const int k0 = (warp / PG) * 16, n0 = (warp % PG) * (W / PG);
                 float* gw = my_grad + a.w_off[l];
                 // Starts from the running per-CTA sums, loaded before the loop so that the latency of
                 // the read-modify-write hides behind the contraction.
-                float dw[4][4];
+                float dw[2 * NJJ][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 2 * NJJ; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
                         ld2(gw + (k0 + g + 8 * i) * W + n0 + j * 8 + 2 * t, dw[j][2 * i], dw[j][2 * i + 1]);
@@ -599,7 +606,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     split_tf32(ha[4 * LDH], ahi[2], alo[2]);
                     split_tf32(ha[4 * LDH + 8], ahi[3], alo[3]);
 #pragma unroll
-                    for (int jj = 0; jj < 2; ++jj) {
+                    for (int jj = 0; jj < NJJ; ++jj) {
                         uint32_t braw[4], bhi[4], blo[4];
                         ldmatrix_x4(braw, b_lane + jj * 16 * LDT + kb * 8);
 #pragma unroll
@@ -616,7 +623,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 2 * NJJ; ++j)
 #pragma unroll
                     for (int i = 0; i < 2; ++i)
                         st2(gw + (k0 + g + 8 * i) * W + n0 + j * 8 + 2 * t, dw[j][2 * i], dw[j][2 * i + 1]);
@@ -624,12 +631,12 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_mma_kernel(FusedArgs<f
             QB_PHASE(6);  // weight gradient
             // Cotangents of layer l-1's jets: G = Zhat W^T.
             {
-                const uint32_t* whi = wbuf + (use & 1) * 2 * WIMG_PLANE;
-                mbar_wait(bars + (use & 1), (uint32_t)((use >> 1) & 1), a.error);
+                const uint32_t* whi = wbuf + (use % NBUF) * 2 * WIMG_PLANE;
+                mbar_wait(bars + (use % NBUF), (uint32_t)((use / NBUF) & 1), a.error);
                 warp_gemm_3xtf32<S, TP, LDA>(act, whi, whi + WIMG_PLANE, row0, col0, lane, acc);
             }
             __syncthreads();
-            issue(use + 2);
+            issue(use + NBUF);
             ++use;
             QB_PHASE(7);  // dgrad
         }

@@ -642,7 +642,7 @@ bool Plan<T>::choose_fused() {
         if (!fused_lookup<T>(W, code, &fused_entries_[si])) return false;
         if (fused_smem_bytes(fused_entries_[si], (int)s.code.size() / 4) > FUSED_MAX_SMEM) return false;
         const long long tiles = (s.n + fused_entries_[si].tile_points - 1) / fused_entries_[si].tile_points;
-        fused_grid_[si] = (int)std::min<long long>(tiles, sms);
+        fused_grid_[si] = (int)std::min<long long>(tiles, (long long)sms * fused_entries_[si].ctas_per_sm);
     }
     fused_width_ = W;
     return true;

@@ -46,3 +46,13 @@ def test_narrow_network_forced_onto_the_layerwise_engine(cuda_device):
     result = _run("poisson2d", 3000, QB200_ENGINE="layerwise")
     assert result["engine"] == 3
     assert result["max_error"] <= TOLERANCE[np.dtype(np.float32)]
+
+
+@pytest.mark.parametrize("name,points", [("poisson2d", 3000), ("beam", 2500)])
+@pytest.mark.parametrize("switches", [{}, {"QB200_FUSED_TILE": "32"}, {"QB200_FUSED": "simt"}],
+                         ids=["two CTAs per SM", "one CTA per SM", "simt"])
+def test_fused_engine_variants(cuda_device, name, points, switches):
+    # Ragged point counts: the last tile of both tile sizes is partial.
+    result = _run(name, points, **switches)
+    assert result["engine"] == (1 if switches.get("QB200_FUSED") == "simt" else 2)
+    assert result["max_error"] <= TOLERANCE[np.dtype(np.float32)]
