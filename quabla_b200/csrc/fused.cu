@@ -120,15 +120,7 @@ cudaError_t fused_prep_launch(const float* params, const int* w_off, int hidden_
     return cudaGetLastError();
 }
 
-template <typename T>
-cudaError_t fused_reduce_launch(const T* grad_cta, double* acc, int P, int ctas, cudaStream_t stream) {
-    fused_reduce_kernel<T><<<(P + 31) / 32, 256, 0, stream>>>(grad_cta, acc, P, ctas);
-    return cudaGetLastError();
-}
-
 template cudaError_t fused_launch<float>(const FusedEntry<float>&, int, cudaStream_t, const FusedArgs<float>&);
 template cudaError_t fused_launch<double>(const FusedEntry<double>&, int, cudaStream_t, const FusedArgs<double>&);
-template cudaError_t fused_reduce_launch<float>(const float*, double*, int, int, cudaStream_t);
-template cudaError_t fused_reduce_launch<double>(const double*, double*, int, int, cudaStream_t);
 
 }  // namespace qb

@@ -43,7 +43,4 @@ size_t fused_weight_image_bytes(int hidden_to_hidden);
 cudaError_t fused_prep_launch(const float* params, const int* w_off, int hidden_to_hidden, void* images,
                               cudaStream_t stream);
 
-template <typename T>
-cudaError_t fused_reduce_launch(const T* grad_cta, double* acc, int P, int ctas, cudaStream_t stream);
-
 }  // namespace qb

@@ -541,28 +541,4 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_step_kernel(FusedArgs<
     }
 }
 
-// acc[i] += sum over CTAs of grad_cta[cta][i] in double, in a fixed order.  A block owns 32
-// consecutive elements; thread (x, y) sums the rows y, y + 8, ... of element x (coalesced along x),
-// then the eight partial sums are added in y order.
-template <typename T>
-__global__ void __launch_bounds__(256) fused_reduce_kernel(const T* __restrict__ grad_cta, double* __restrict__ acc,
-                                                           int P, int ctas) {
-    __shared__ double part[8][33];
-    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
-    const int i = blockIdx.x * 32 + x;
-    double s = 0.0;
-    if (i < P) {
-#pragma unroll 4
-        for (int c = y; c < ctas; c += 8) s += (double)grad_cta[(size_t)c * P + i];
-    }
-    part[y][x] = s;
-    __syncthreads();
-    if (y == 0 && i < P) {
-        double total = part[0][x];
-#pragma unroll
-        for (int k = 1; k < 8; ++k) total += part[k][x];
-        acc[i] += total;
-    }
-}
-
 }  // namespace qb

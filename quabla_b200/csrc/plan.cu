@@ -254,6 +254,12 @@ class Plan final : public qb200_plan {
     int fused_width_ = 0;
     std::vector<FusedEntry<T>> fused_entries_;  // per set
     std::vector<int> fused_grid_;               // per set
+    // Every set has its own saved-jet scratch and gradient rows, so that the small sets run beside
+    // the first one on a second stream; rows of all sets are consecutive for the final reduction.
+    std::vector<size_t> fused_jet0_, fused_row0_;  // per set: first scratch element, first gradient row
+    size_t fused_rows_ = 0;
+    cudaStream_t side_stream_ = nullptr;        // lower priority: fills the tail of the first set's kernel
+    cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
     T* fused_z_ = nullptr;
     T* fused_h_ = nullptr;
     T* fused_grad_ = nullptr;
@@ -308,6 +314,14 @@ void Plan<T>::release() {
     if (ev_ar0_ != nullptr) cudaEventDestroy(ev_ar0_);
     if (ev_ar1_ != nullptr) cudaEventDestroy(ev_ar1_);
     ev_begin_ = ev_end_ = ev_ar0_ = ev_ar1_ = nullptr;
+    if (ev_fork_ != nullptr) cudaEventDestroy(ev_fork_);
+    if (ev_join_ != nullptr) cudaEventDestroy(ev_join_);
+    ev_fork_ = ev_join_ = nullptr;
+    if (side_stream_ != nullptr) {
+        cudaStreamSynchronize(side_stream_);
+        cudaStreamDestroy(side_stream_);
+    }
+    side_stream_ = nullptr;
     if (stream_ != nullptr) cudaStreamDestroy(stream_);
     stream_ = nullptr;
 }
@@ -458,9 +472,21 @@ qb200_status Plan<T>::init() {
         // gradient rows; the layer-wise scratch is not needed.
         size_t jets = 0, rows = 0;
         const int hidden = L_ - 1;
+        fused_jet0_.assign(sets_.size(), 0);
+        fused_row0_.assign(sets_.size(), 0);
         for (size_t si = 0; si < sets_.size(); ++si) {
-            jets = std::max(jets, (size_t)fused_grid_[si] * hidden * fused_entries_[si].scratch_per_layer);
-            rows = std::max(rows, (size_t)fused_grid_[si]);
+            fused_jet0_[si] = jets;
+            fused_row0_[si] = rows;
+            jets += (size_t)fused_grid_[si] * hidden * fused_entries_[si].scratch_per_layer;
+            rows += (size_t)fused_grid_[si];
+        }
+        fused_rows_ = rows;
+        if (sets_.size() > 1) {
+            int least = 0, greatest = 0;
+            QB_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+            QB_CUDA(cudaStreamCreateWithPriority(&side_stream_, cudaStreamNonBlocking, least));
+            QB_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
+            QB_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
         }
         QB_TRY(dev_alloc(&fused_z_, jets));
         QB_TRY(dev_alloc(&fused_h_, jets));
@@ -703,21 +729,18 @@ qb200_status Plan<T>::run_fused(int si, bool forward_only) {
     a.cotangent = d_ct_;
     a.weight = (T)s.weight;
     a.extra = (T)dp_scale_;
-    a.scratch_z = fused_z_;
-    a.scratch_h = fused_h_;
-    a.grad_cta = fused_grad_;
+    a.scratch_z = fused_z_ + fused_jet0_[si];
+    a.scratch_h = fused_h_ + fused_jet0_[si];
+    a.grad_cta = fused_grad_ + fused_row0_[si] * n_params_;
     a.loss_cta = d_partials_ + st.partial_offset;
     a.forward_only = forward_only ? 1 : 0;
     a.weight_images = fused_images_;
     a.error = d_error_;
-    cudaError_t e = fused_launch<T>(fused_entries_[si], fused_grid_[si], stream_, a);
+    // Sets after the first run on the side stream, between the fork and join events of run().
+    cudaStream_t stream = (si > 0 && side_stream_ != nullptr) ? side_stream_ : stream_;
+    cudaError_t e = fused_launch<T>(fused_entries_[si], fused_grid_[si], stream, a);
     ++launches_;
     if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of fused_step_kernel failed: %s", cudaGetErrorString(e));
-    if (!forward_only) {
-        e = fused_reduce_launch<T>(fused_grad_, d_acc_, (int)n_params_, fused_grid_[si], stream_);
-        ++launches_;
-        if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of fused_reduce_kernel failed: %s", cudaGetErrorString(e));
-    }
     return QB200_OK;
 }
 
@@ -1017,8 +1040,14 @@ qb200_status Plan<T>::run(bool forward_only) {
     QB_TRY(use_device());
     QB_TRY(check_bound());
     QB_TRY(refresh_tables());
-    if (!forward_only) QB_CUDA(cudaMemsetAsync(d_acc_, 0, n_params_ * sizeof(double), stream_));
+    if (!forward_only && !fused_) QB_CUDA(cudaMemsetAsync(d_acc_, 0, n_params_ * sizeof(double), stream_));
     if (fused_ && fused_tensor_core_) QB_TRY(prepare_weight_images());
+    const bool side = fused_ && side_stream_ != nullptr;
+    if (side) {
+        // Tables and weight images are ready on the main stream before the side stream starts.
+        QB_CUDA(cudaEventRecord(ev_fork_, stream_));
+        QB_CUDA(cudaStreamWaitEvent(side_stream_, ev_fork_, 0));
+    }
     if (!fused_ && tc_any_) QB_TRY(tc_prepare());
     LossArgs la;
     la.n_sets = (int)sets_.size();
@@ -1051,7 +1080,19 @@ qb200_status Plan<T>::run(bool forward_only) {
         la.count[si] = slot - st.partial_offset;
         la.weight[si] = desc_.sets[si].weight;
     }
+    if (side) {
+        QB_CUDA(cudaEventRecord(ev_join_, side_stream_));
+        QB_CUDA(cudaStreamWaitEvent(stream_, ev_join_, 0));
+    }
     T* loss_out = forward_only ? d_loss_only_ : d_flat_;
+    if (fused_ && !forward_only) {
+        const int P = (int)n_params_;
+        fused_finalize_kernel<T><<<(P + 31) / 32 + 1, 256, 0, stream_>>>(fused_grad_, P, (int)fused_rows_, d_flat_ + 1,
+                                                                       d_partials_, la, (T)dp_scale_, loss_out);
+        QB_TRY(launched("fused_finalize_kernel"));
+        executed_ = true;
+        return QB200_OK;
+    }
     loss_finalize_kernel<T><<<1, 256, 0, stream_>>>(d_partials_, la, forward_only ? T(1) : (T)dp_scale_, loss_out);
     QB_TRY(launched("loss_finalize_kernel"));
     if (!forward_only) {

@@ -159,10 +159,10 @@ struct LossArgs {
     int count[MAX_SETS];
     double weight[MAX_SETS];
 };
+// Weighted sum of the per-block loss partials of every point set, in a fixed order; whole block.
 template <typename T>
-__global__ void __launch_bounds__(256) loss_finalize_kernel(const double* __restrict__ partials, LossArgs a, T extra,
-                                                            T* __restrict__ out) {
-    __shared__ double red[8];
+__device__ __forceinline__ void loss_finalize_block(const double* __restrict__ partials, const LossArgs& a, T extra,
+                                                    T* __restrict__ out, double* red) {
     T loss = T(0);
     for (int s = 0; s < a.n_sets; ++s) {
         double v = 0.0;
@@ -172,6 +172,45 @@ __global__ void __launch_bounds__(256) loss_finalize_kernel(const double* __rest
         __syncthreads();
     }
     if (threadIdx.x == 0) out[0] = loss * extra;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) loss_finalize_kernel(const double* __restrict__ partials, LossArgs a, T extra,
+                                                            T* __restrict__ out) {
+    __shared__ double red[8];
+    loss_finalize_block<T>(partials, a, extra, out, red);
+}
+
+// End of a step of the fused engines, one launch: grads[i] = sum over the per-CTA gradient rows of
+// every point set (rows are consecutive, set after set) in double, in a fixed order, and the loss
+// from the per-CTA partials.  Blocks 0 .. gridDim.x - 2 own 32 consecutive elements each; thread
+// (x, y) sums the rows y, y + 8, ... of element x (coalesced along x), then the eight partial sums
+// are added in y order.  The last block forms the loss.
+template <typename T>
+__global__ void __launch_bounds__(256) fused_finalize_kernel(const T* __restrict__ grad_rows, int P, int rows,
+                                                             T* __restrict__ grads,
+                                                             const double* __restrict__ partials, LossArgs a, T extra,
+                                                             T* __restrict__ loss_out) {
+    __shared__ double part[8][33];
+    if (blockIdx.x == gridDim.x - 1) {
+        loss_finalize_block<T>(partials, a, extra, loss_out, &part[0][0]);
+        return;
+    }
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + x;
+    double s = 0.0;
+    if (i < P) {
+#pragma unroll 4
+        for (int c = y; c < rows; c += 8) s += (double)grad_rows[(size_t)c * P + i];
+    }
+    part[y][x] = s;
+    __syncthreads();
+    if (y == 0 && i < P) {
+        double total = part[0][x];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) total += part[k][x];
+        grads[i] = (T)total;
+    }
 }
 
 template <typename T>
