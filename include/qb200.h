@@ -79,7 +79,7 @@ typedef enum qb200_query {
     QB200_Q_DEVICE_BUFFER_COUNT = 0, /* CudaExecutionPlan::device_buffer_count, cuda.rs:1146-1173 */
     QB200_Q_NONFINITE_CLIP_SEEN = 1, /* nonfinite_clip_seen, cuda_optimizer.rs:405-420 */
     QB200_Q_STREAM = 2,              /* the plan's cudaStream_t, for event timing by the caller */
-    QB200_Q_PARAMETER_COUNT = 3,     /* scalars over all parameter leaves */
+    QB200_Q_PARAMETER_COUNT = 3,     /* elements of the flat parameter buffer (leaves padded to 4 elements) */
     QB200_Q_OUTPUT_COUNT = 4,        /* 1 (loss) + number of parameter leaves */
     QB200_Q_KERNEL_LAUNCHES = 5,     /* kernels of this library launched by the plan so far */
     QB200_Q_FLAT_DEVICE_PTR = 6,     /* device address of the flat [loss, gradients...] buffer */
@@ -211,7 +211,8 @@ qb200_status qb200_plan_sample_uniform(qb200_plan* plan, const char* name, int32
                                        double minval, double maxval);
 
 /* Optimizer moments, which the reference keeps private to the device trainer:
- * which = 0 first moment, 1 second moment; all leaves flat in parameter order. */
+ * which = 0 first moment, 1 second moment; all leaves flat in parameter order, every leaf starting on
+ * a 4-element boundary (QB200_Q_PARAMETER_COUNT elements in all; the padding is zero). */
 qb200_status qb200_plan_read_moments(qb200_plan* plan, int32_t which, void* host, size_t nbytes);
 qb200_status qb200_plan_write_moments(qb200_plan* plan, int32_t which, const void* host, size_t nbytes,
                                       int64_t step_count);

@@ -13,6 +13,7 @@ import numpy as _np
 
 from . import optim, random  # noqa: F401
 from ._errors import QuablaError, TracerError, UnsupportedOperationError  # noqa: F401
+from ._io import load, save  # noqa: F401
 from ._transforms import (cos, exp, grad, hessian, jit, jvp, log, mean, reshape, sin, sqrt, stack, sum,  # noqa: F401,A004
                           tanh, trace, value_and_grad, vmap)
 

@@ -22,9 +22,11 @@ from ._devices import require_device
 from ._errors import UnsupportedOperationError
 from ._lbfgs import LBFGS
 from ._plan import COTANGENT_NAME, opt_config
+from ._schedules import constant, cosine_decay, exponential_decay, piecewise_constant, warmup_cosine_decay
 from ._transforms import CompiledLoss, _is_array
 
-__all__ = ["Adam", "AdamW", "SGD", "LBFGS", "Trainer", "clip_by_global_norm"]
+__all__ = ["Adam", "AdamW", "SGD", "LBFGS", "Trainer", "clip_by_global_norm", "constant", "cosine_decay",
+           "exponential_decay", "piecewise_constant", "warmup_cosine_decay"]
 
 
 def _positive(value, name: str) -> float:
@@ -235,6 +237,84 @@ class CudaTrainerExecutor:
                 out[name] = self._frozen[name].astype(self._dtype)
         return out
 
+    def _moment_layout(self):
+        """(name, shape, first element, element count) of every active parameter, in the plan's flat order."""
+        layout, offset = [], 0
+        for name, _, _ in self._compiled.spec.parameters:
+            shape = tuple(self._shapes[name])
+            count = int(np.prod(shape, dtype=np.int64)) if shape else 1
+            layout.append((name, shape, offset, count))
+            offset += (count + 3) // 4 * 4  # leaves start on 4-element boundaries; the padding stays zero
+        return layout
+
+    def export_state(self) -> dict:
+        """Optimizer state as host arrays: `{"step": n}` plus, for Adam, `"m"` and `"v"` (name -> array in the
+        plan dtype).  One device-to-host read per moment buffer (qb200_plan_read_moments)."""
+        from . import _lib
+
+        state: dict = {"step": int(self._plan.query(_lib.Q_STEP_COUNT))}
+        if self._rule["rule"] == "adam":
+            for key, which in (("m", 0), ("v", 1)):
+                flat = self._plan.read_moments(which)
+                state[key] = {name: flat[first:first + count].reshape(shape).copy()
+                              for name, shape, first, count in self._moment_layout()}
+        return state
+
+    def _checked_moments(self, state: dict):
+        """The flat moment vectors (or None for SGD) and the step count of a state; raises on any mismatch."""
+        step = operator.index(state["step"])
+        if step < 0:
+            raise ValueError("optimizer step count must be nonnegative")
+        if self._rule["rule"] != "adam":
+            if "m" in state or "v" in state:
+                raise ValueError("this optimizer has no moments")
+            return None, step
+        from . import _lib
+
+        layout = self._moment_layout()
+        total = int(self._plan.query(_lib.Q_PARAMETER_COUNT))
+        flats = []
+        for key in ("m", "v"):
+            moments = state[key]
+            if set(moments) != {name for name, _, _, _ in layout}:
+                raise ValueError(f'optimizer state "{key}" must hold exactly the trained parameters')
+            flat = np.zeros((total,), dtype=self._dtype)
+            for name, shape, first, count in layout:
+                value = np.asarray(moments[name])
+                if value.shape != shape or value.dtype != self._dtype:
+                    raise ValueError(f'optimizer state "{key}"["{name}"] must be {self._dtype} of shape {shape}, '
+                                     f"got {value.dtype} of shape {value.shape}")
+                flat[first:first + count] = value.reshape(-1)
+            flats.append(flat)
+        return flats, step
+
+    def _checked_parameters(self, values: dict) -> dict:
+        checked = {}
+        for name, value in values.items():
+            value = np.asarray(value)
+            if name in self._active:
+                if value.shape != tuple(self._shapes[name]) or value.dtype != self._dtype:
+                    raise ValueError(f'parameter "{name}" must be {self._dtype} of shape {tuple(self._shapes[name])}, '
+                                     f"got {value.dtype} of shape {value.shape}")
+            elif name not in self._frozen:
+                raise ValueError(f'no parameter named "{name}"')
+            checked[name] = value
+        return checked
+
+    def import_state(self, state: dict, parameters: dict | None = None) -> None:
+        """Inverse of `export_state`, optionally with new parameter values by name.  Names, shapes and dtypes of
+        everything are validated first; then the parameters are bound and both moment buffers and the step
+        counter uploaded (qb200_plan_write_moments)."""
+        flats, step = self._checked_moments(state)
+        values = self._checked_parameters(parameters or {})
+        for name, value in values.items():
+            if name in self._active:
+                self._plan.bind(name, value)
+            else:
+                self._frozen[name] = np.array(value, dtype=np.float64)
+        for which, flat in enumerate(flats or ()):
+            self._plan.write_moments(which, flat, step)
+
     @property
     def device_buffer_count(self) -> int:
         return self._plan.device_buffer_count
@@ -334,6 +414,27 @@ class Trainer:
         result = self._device_step(inputs)
         self._data = tuple(data)
         return result
+
+    def export_state(self) -> dict:
+        """Everything a run needs to resume: `{"step", "params", "optimizer"}` as host arrays and Python
+        scalars, a tree that `quabla_b200.save` writes as it is.  `params` is the parameter pytree,
+        `optimizer` holds the device step counter and, for Adam, both moment buffers by parameter name.
+        The reference's Trainer keeps this state inside its native executor and exposes only
+        `params` (python/quabla/optim.py:351-550); checkpointing a device run needs the moments too.
+        """
+        return {"step": self._device_steps, "params": self.params, "optimizer": self._executor.export_state()}
+
+    def import_state(self, state: dict) -> None:
+        """Resume from `export_state()` (of a trainer built with the same loss, parameter shapes and
+        optimizer rule): the next `step()` continues bit for bit where the exporting run stood."""
+        step = operator.index(state["step"])
+        if step < 0:
+            raise ValueError("step must be nonnegative")
+        leaves, _ = tr.flatten(state["params"])
+        if len(leaves) != len(self._parameter_names):
+            raise ValueError(f"state holds {len(leaves)} parameter arrays, the trainer has {len(self._parameter_names)}")
+        self._executor.import_state(state["optimizer"], dict(zip(self._parameter_names, leaves)))
+        self._device_steps = step
 
     def resample(self, index: int, key, bounds: Sequence[tuple[float, float]]) -> None:
         """Redraw batch argument `index` (one array of shape [rows, d]) on the device.

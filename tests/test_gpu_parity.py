@@ -6,6 +6,7 @@ import pytest
 import quabla_b200 as qb
 from oracle import contracted
 from quabla_b200 import _lib, workloads
+from quabla_b200 import _trace as tr
 from quabla_b200._plan import Plan, opt_config
 
 from _util import TOLERANCE, relative_error, traced
@@ -158,3 +159,85 @@ def test_sin_activation_matches_the_oracle(cuda_device, name):
     for got, expected, (pname, _, _) in zip(outputs[1:], expected_grads, compiled.spec.parameters):
         assert relative_error(got.reshape(expected.shape), expected) <= tol, pname
     plan.close()
+
+
+def test_trainer_applies_the_schedule_at_the_completed_step(cuda_device):
+    # Rates 0, r, r, 0, 0: the first update runs at schedule(0), and three scheduled steps equal two
+    # steps at the constant rate r bit for bit.
+    w = workloads.make("poisson1d")
+    rate = 0.01
+    schedule = qb.optim.piecewise_constant([1, 3], [0.0, rate, 0.0])
+    scheduled = qb.optim.Trainer(w.loss, w.params, qb.optim.SGD(schedule), *w.data, device="cuda:0")
+    fixed = qb.optim.Trainer(w.loss, w.params, qb.optim.SGD(rate), *w.data, device="cuda:0")
+
+    def leaves(trainer):
+        return [np.asarray(leaf) for leaf in tr.flatten(trainer.params)[0]]
+
+    start = leaves(scheduled)
+    scheduled.step()
+    assert all(a.tobytes() == b.tobytes() for a, b in zip(leaves(scheduled), start))
+    scheduled.step()
+    scheduled.step()
+    fixed.step()
+    fixed.step()
+    after = leaves(scheduled)
+    assert all(a.tobytes() == b.tobytes() for a, b in zip(after, leaves(fixed)))
+    assert any(a.tobytes() != b.tobytes() for a, b in zip(after, start))
+    scheduled.step()
+    scheduled.step()
+    assert all(a.tobytes() == b.tobytes() for a, b in zip(leaves(scheduled), after))
+    assert scheduled._executor.learning_rate == 0.0
+
+
+@pytest.mark.parametrize("rule", ["adam", "sgd"])
+def test_trainer_resumes_bit_for_bit_from_a_saved_state(cuda_device, tmp_path, rule):
+    # Five steps in one run == two steps, save, load into a fresh trainer, three more steps.
+    w = workloads.make("poisson1d")
+    schedule = qb.optim.warmup_cosine_decay(0.0, 0.02, 2, 8, end_value=0.002)
+
+    def build():
+        optimizer = qb.optim.AdamW(schedule, weight_decay=0.01) if rule == "adam" else qb.optim.SGD(schedule)
+        return qb.optim.Trainer(w.loss, w.params, optimizer, *w.data, device="cuda:0")
+
+    def leaves(tree):
+        return [np.asarray(leaf) for leaf in tr.flatten(tree)[0]]
+
+    straight = build()
+    for _ in range(5):
+        straight.step()
+
+    first = build()
+    first.step()
+    first.step()
+    path = tmp_path / f"{rule}.qb"
+    qb.save(path, first.export_state())
+    state = qb.load(path)
+    assert state["step"] == 2 and state["optimizer"]["step"] == 2
+    assert ("m" in state["optimizer"]) == (rule == "adam")
+
+    resumed = build()
+    resumed.import_state(state)
+    for _ in range(3):
+        resumed.step()
+    for a, b in zip(leaves(resumed.params), leaves(straight.params)):
+        assert a.tobytes() == b.tobytes()
+    assert float(resumed.value) == float(straight.value)
+    final = resumed.export_state()
+    reference = straight.export_state()
+    assert final["step"] == reference["step"] == 5
+    if rule == "adam":
+        for key in ("m", "v"):
+            for name, value in final["optimizer"][key].items():
+                assert value.tobytes() == reference["optimizer"][key][name].tobytes(), (key, name)
+
+    # Validation happens before anything is written.
+    bad = qb.load(path)
+    if rule == "adam":
+        name = next(iter(bad["optimizer"]["m"]))
+        bad["optimizer"]["m"][name] = bad["optimizer"]["m"][name].astype(np.float32)
+        with pytest.raises(ValueError):
+            resumed.import_state(bad)
+    bad = qb.load(path)
+    bad["params"] = leaves(bad["params"])[:-1]
+    with pytest.raises(ValueError):
+        resumed.import_state(bad)
