@@ -360,7 +360,12 @@ def main() -> None:
     # Roofline of the dominant kernel: the kernels of the interior point set (one fused launch on
     # narrow networks), timed live with CUDA events on the plan's stream inside the timed steps.
     kernel_s = float(np.mean(kernel_ns)) * 1e-9
-    flops = w.flops_per_point(w.streams) * per_gpu  # algorithmic matmul FLOPs of one launch
+    # Matmul FLOPs one launch EXECUTES: the streams the plan carries (a Laplacian carried as one merged
+    # second-order stream is fewer streams than the reference formulation's one per direction).
+    interior = plan.spec.sets[0]
+    streams = interior.streams
+    flops = w.flops_per_point(streams) * per_gpu
+    step_flops = flops + sum(w.flops_per_point(s) * n for n, s in w.extra)
     achieved_tflops = flops / kernel_s / 1e12
     if dtype_name == "f32":
         # 3xTF32 on the tensor pipe: TF32 runs at half the bf16 rate, three passes per product.
@@ -384,7 +389,7 @@ def main() -> None:
     # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under profiles/
     # (dram__bytes read + write); known for the default workload's fused kernel only.
     traffic = None
-    if w.name == "poisson2d" and engine == 2 and per_gpu == 65536:
+    if w.name == "poisson2d" and engine == 2 and per_gpu == 65536 and streams == 4:
         traffic = 215.8e6
     extra_peaks = {}
     if dtype_name == "f32":
@@ -397,7 +402,8 @@ def main() -> None:
         "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
         "config": {"workload": w.name, "description": w.description, "interior_points_per_gpu": per_gpu,
                    "other_sets": w.extra, "optimizer": "adam lr=1e-3", "parameters": w.parameter_count,
-                   "engine": engine_name,
+                   "engine": engine_name, "streams": streams, "reference_streams": w.streams,
+                   "merged_second_order": interior.merge_weights is not None,
                    "l2": "256 MB written between timed steps, outside the per-step event brackets",
                    "allreduce_us_rank0": float(np.mean(allreduce_ns)) * 1e-3 if world > 1 else 0.0},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -406,7 +412,7 @@ def main() -> None:
         "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s",
                      "frac": achieved_tflops / peak_tflops, "traffic": traffic, **extra_peaks,
                      "kernel": kernel_name, "kernel_us": kernel_s * 1e6, "flops_per_launch": flops,
-                     "step_flops": w.flops_per_step, "peak_source": peak_note},
+                     "step_flops": step_flops, "peak_source": peak_note},
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:

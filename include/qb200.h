@@ -161,6 +161,16 @@ qb200_status qb200_desc_set_add_column(qb200_desc* desc, int32_t set, int32_t in
 /* A derivative direction v (length sizes[0]) carried to `order` (1..4): adds
  * `order` streams d^m u / dv^m after the streams declared so far. */
 qb200_status qb200_desc_set_add_direction(qb200_desc* desc, int32_t set, const double* vec, int32_t order);
+/* Declares one more stream after all directions' streams: M = sum_j weights[j] * d^2 u / dv_j^2 over
+ * the set's directions (n_weights = number of directions declared; 0 leaves a direction out).  The
+ * directions themselves then need first order only: the kernels carry M through every layer as
+ *   M_out = f'(z) M_in + f''(z) sum_j weights[j] (dz/dv_j)^2,
+ * the forward-Laplacian recurrence, instead of one second-order stream per direction.  For a residual
+ * that uses the second derivatives only through that sum (u_xx + u_yy, a heat or wave operator) this
+ * is the reference's value and gradient (hessian + trace, python/quabla/_transforms.py:1780-1995)
+ * with fewer streams.  Call after the last add_direction and before set_program; the program
+ * addresses M as the last stream. */
+qb200_status qb200_desc_set_merge_second_order(qb200_desc* desc, int32_t set, const double* weights, int32_t n_weights);
 /* Register program evaluated once per point: code is n_instr x {op, dst, a, b}.
  * value_reg holds e; grad_regs[s] holds de/d(stream s) or is -1 when zero. */
 qb200_status qb200_desc_set_program(qb200_desc* desc, int32_t set, const int32_t* code, int32_t n_instr,

@@ -120,7 +120,14 @@ def value_and_grad(spec, inputs: dict, cotangent: float = 1.0, threads: int = 1,
     """(loss, [gradient per spec parameter]) in float64.
 
     point_slices, when given, restricts set k to points [lo, hi) (for bounded
-    timing samples); weights are unchanged."""
+    timing samples); weights are unchanged.
+
+    A spec whose sets carry a merged second-order stream (the forward-Laplacian recurrence of the
+    device kernels) is evaluated in its `reference` form, one second-order stream per direction:
+    the oracle always computes the formulation pinned against the reference's known answers."""
+    spec = getattr(spec, "reference", None) or spec
+    if any(getattr(s, "merge_weights", None) is not None for s in spec.sets):
+        raise ValueError("the oracle evaluates unmerged specs only")
     lib = _load()
     problem = _Problem(spec, inputs)
     n_layers = len(spec.sizes) - 1

@@ -73,6 +73,7 @@ SIGNATURES = {
     "qb200_desc_add_set": (_I32, [_P, _I64, C.c_double, C.POINTER(_I32)]),
     "qb200_desc_set_add_column": (_I32, [_P, _I32, _I32, _I32]),
     "qb200_desc_set_add_direction": (_I32, [_P, _I32, C.POINTER(C.c_double), _I32]),
+    "qb200_desc_set_merge_second_order": (_I32, [_P, _I32, C.POINTER(C.c_double), _I32]),
     "qb200_desc_set_program": (_I32, [_P, _I32, C.POINTER(_I32), _I32, C.POINTER(C.c_double), _I32, _I32, _I32,
                                       C.POINTER(_I32), _I32]),
     "qb200_plan_create": (_I32, [_P, _I32, C.POINTER(_P)]),

@@ -29,10 +29,13 @@ class SetSpec:
     columns: list[tuple[int, int]]            # (input index, column); network inputs first
     directions: list[tuple[tuple[float, ...], int]]  # (vector, order)
     program: Program
+    # One weight per direction when the set carries the merged second-order stream
+    # sum_j w_j d^2u/dv_j^2 as its last stream (qb200_desc_set_merge_second_order); else None.
+    merge_weights: list[float] | None = None
 
     @property
     def streams(self) -> int:
-        return 1 + sum(order for _, order in self.directions)
+        return 1 + sum(order for _, order in self.directions) + (0 if self.merge_weights is None else 1)
 
 
 @dataclass
@@ -43,6 +46,10 @@ class PlanSpec:
     inputs: list[tuple[str, int, int, bool]] = field(default_factory=list)  # (name, rows, cols, retained)
     sets: list[SetSpec] = field(default_factory=list)
     activation: str = "tanh"   # of the hidden layers: "tanh" or "sin"
+    # The same loss with one second-order stream per direction (the formulation the reference's
+    # hessian-and-trace code computes), when some set of this spec uses the merged stream; the CPU
+    # oracle evaluates that one.
+    reference: "PlanSpec | None" = None
 
     def parameter_shape(self, index: int) -> tuple[int, ...]:
         _, layer, kind = self.parameters[index]
@@ -91,6 +98,9 @@ def build_desc(spec: PlanSpec) -> C.c_void_p:
                 _lib.check(lib.qb200_desc_set_add_column(desc, index.value, input_index, column))
             for vector, order in s.directions:
                 _lib.check(lib.qb200_desc_set_add_direction(desc, index.value, _double_array(vector), order))
+            if s.merge_weights is not None:
+                _lib.check(lib.qb200_desc_set_merge_second_order(desc, index.value, _double_array(s.merge_weights),
+                                                                 len(s.merge_weights)))
             p = s.program
             _lib.check(lib.qb200_desc_set_program(
                 desc, index.value, _int32_array(p.code), p.n_instr, _double_array(p.consts), len(p.consts),

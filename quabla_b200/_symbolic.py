@@ -327,6 +327,99 @@ def substitute(root: Expr, mapping: dict) -> Expr:
     return out[root]
 
 
+MERGED_WORD = ("merged",)  # word of the net leaf that stands for a weighted sum of second derivatives
+
+
+def merge_weighted_sum(root: Expr, targets: list[Expr], merged_leaf: Expr):
+    """Rewrite `root` so that the leaves `targets` appear only through `merged_leaf`.
+
+    Succeeds when `root` depends on the targets only through sums  sum_t c_t * t  with constant
+    coefficients that are all proportional to one weight vector w (u_xx + u_yy;
+    0.1 * (u_xx + u_yy + u_zz) - u_t; ...).  Returns (new_root, {target: w_t}) with
+    merged_leaf = sum_t w_t * t, or None when some target is used in another way (multiplied by a
+    non-constant, alone inside a nonlinear function with different weights, ...).
+    """
+    target_set = set(targets)
+    weights: dict[Expr, float] = {}
+
+    def close(coeffs: dict, rest: Expr):
+        """The node  rest + sum coeffs[t] * t  as  rest + k * merged_leaf, fixing or checking w."""
+        if not coeffs:
+            return rest
+        if not weights:
+            if set(coeffs) != target_set or any(c == 0.0 for c in coeffs.values()):
+                return None
+            weights.update(coeffs)
+            return add(rest, merged_leaf)
+        if set(coeffs) != set(weights):
+            return None
+        first = next(iter(weights))
+        k = coeffs[first] / weights[first]
+        for t, c in coeffs.items():
+            if abs(c - k * weights[t]) > 1e-12 * max(abs(c), abs(k * weights[t])):
+                return None
+        return add(rest, mul(const(k), merged_leaf))
+
+    # value[e] = (coeffs, rest): e == rest + sum coeffs[t] * t with `rest` free of targets (rebuilt).
+    value: dict[Expr, tuple[dict, Expr]] = {}
+    for e in topological([root]):
+        k = e.kind
+        if e in target_set:
+            value[e] = ({e: 1.0}, ZERO)
+            continue
+        if k in ("const", "sym", "net"):
+            value[e] = ({}, e)
+            continue
+        parts = [value[c] for c in children(e)]
+        if k in ("add", "sub"):
+            (ca, ra), (cb, rb) = parts
+            sign = 1.0 if k == "add" else -1.0
+            coeffs = dict(ca)
+            for t, c in cb.items():
+                coeffs[t] = coeffs.get(t, 0.0) + sign * c
+            value[e] = ({t: c for t, c in coeffs.items() if c != 0.0} if any(coeffs.values()) else {},
+                        add(ra, rb) if k == "add" else sub(ra, rb))
+            if len(value[e][0]) != len(coeffs):  # a target cancelled: give up rather than reason about it
+                return None
+            continue
+        if k == "neg":
+            (ca, ra), = parts
+            value[e] = ({t: -c for t, c in ca.items()}, neg(ra))
+            continue
+        if k == "mul":
+            (ca, ra), (cb, rb) = parts
+            if ca and not cb and is_const(rb):
+                ca, ra, cb, rb = cb, rb, ca, ra
+            if cb and not ca and is_const(ra):
+                factor = ra.args[0]
+                value[e] = ({t: factor * c for t, c in cb.items()}, mul(ra, rb))
+                continue
+        if k == "div":
+            (ca, ra), (cb, rb) = parts
+            if ca and not cb and is_const(rb):
+                factor = 1.0 / rb.args[0]
+                value[e] = ({t: factor * c for t, c in ca.items()}, div(ra, rb))
+                continue
+        # Any other use is nonlinear in the children: each child that carries targets is closed here.
+        closed = []
+        for coeffs, rest in parts:
+            node = close(coeffs, rest)
+            if node is None:
+                return None
+            closed.append(node)
+        if k == "powi":
+            rebuilt = powi(closed[0], e.args[1])
+        elif k in _BINARY_OPS:
+            rebuilt = {"add": add, "sub": sub, "mul": mul, "div": div}[k](closed[0], closed[1])
+        else:
+            rebuilt = unary(k, closed[0])
+        value[e] = ({}, rebuilt)
+    new_root = close(*value[root])
+    if new_root is None or not weights:
+        return None
+    return new_root, weights
+
+
 def leaves(roots: Iterable[Expr], kind: str) -> list[Expr]:
     return [e for e in topological(roots) if e.kind == kind]
 

@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import itertools
 import math
+import os
 from typing import Any, Callable
 
 import numpy as np
@@ -678,9 +679,21 @@ def _single_direction(word: tuple) -> tuple[tuple[float, ...], int]:
     return first, len(word)
 
 
+def _merge_enabled() -> bool:
+    """QB200_MERGE=0 keeps one second-order stream per direction (for comparisons)."""
+    return os.environ.get("QB200_MERGE", "1") != "0"
+
+
 def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]]],
-                    data: list[tuple[str, tuple[int, ...], bool]], dtype) -> PlanSpec:
-    """parameters: (name, shape) in gradient-output order; data: (name, shape, retained)."""
+                    data: list[tuple[str, tuple[int, ...], bool]], dtype, merge: bool | None = None) -> PlanSpec:
+    """parameters: (name, shape) in gradient-output order; data: (name, shape, retained).
+
+    With `merge` (default: on unless QB200_MERGE=0) a set whose residual uses the second derivatives
+    along two or more directions only through one weighted sum (a Laplacian, a heat operator) carries
+    that sum as a single stream; `spec.reference` then holds the unmerged spec of the same loss.
+    """
+    if merge is None:
+        merge = _merge_enabled()
     if not isinstance(loss, LossValue):
         raise _unsupported("the loss must be a mean or sum over collocation points (or a sum of those)", "loss")
     if loss.constant != 0.0:
@@ -741,6 +754,7 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
         cols = int(np.prod(shape[1:], dtype=np.int64))
         spec.inputs.append((name, rows, cols, bool(retained)))
 
+    merged_any = False
     for key in order:
         batch, inputs = key
         members = groups[key]
@@ -784,6 +798,20 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
             if word:
                 direction, m = _single_direction(word)
                 orders[direction] = max(orders.get(direction, 0), m)
+        # Second derivatives along directions of order exactly two are candidates for the merged stream.
+        merge_weights = None
+        targets = [leaf for leaf in sx.leaves([total], "net")
+                   if len(leaf.args[1]) == 2 and orders[_single_direction(leaf.args[1])[0]] == 2]
+        rewritten = None
+        if merge and len(targets) >= 2:
+            rewritten = sx.merge_weighted_sum(total, targets, sx.Expr("net", (network, sx.MERGED_WORD)))
+        weight_of: dict = {}
+        if rewritten is not None:
+            total, by_target = rewritten
+            weight_of = {_single_direction(t.args[1])[0]: w for t, w in by_target.items()}
+            for direction in weight_of:
+                orders[direction] = 1  # the merged stream needs their first-order streams only
+            merged_any = True
         directions = sorted(orders.items(), key=lambda kv: kv[0], reverse=True)
         base = {}
         next_stream = 1
@@ -792,11 +820,18 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
                 raise _unsupported(f"derivative order {m} along one direction; orders 1..4 are supported", "grad")
             base[direction] = next_stream
             next_stream += m
+        merged_stream = -1
+        if rewritten is not None:
+            merge_weights = [weight_of.get(direction, 0.0) for direction, _ in directions]
+            merged_stream = next_stream  # the last stream
+            next_stream += 1
 
         def stream_of(leaf: sx.Expr) -> int:
             word = leaf.args[1]
             if not word:
                 return 0
+            if word == sx.MERGED_WORD:
+                return merged_stream
             direction, m = _single_direction(word)
             return base[direction] + m - 1
 
@@ -810,5 +845,8 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
                 grads.append(sx.derivative(total, lambda l, target=leaf: sx.ONE if l is target else sx.ZERO))
         program = sx.compile_program(total, grads, lambda leaf: column_of[leaf], stream_of)
         spec.sets.append(SetSpec(n_points=batch, weight=set_weight, columns=columns,
-                                 directions=[(d, m) for d, m in directions], program=program))
+                                 directions=[(d, m) for d, m in directions], program=program,
+                                 merge_weights=merge_weights))
+    if merged_any:
+        spec.reference = build_plan_spec(loss, parameters, data, dtype, merge=False)
     return spec

@@ -289,6 +289,19 @@ qb200_status qb200_desc_set_add_direction(qb200_desc* desc, int32_t set, const d
     return QB200_OK;
 }
 
+qb200_status qb200_desc_set_merge_second_order(qb200_desc* desc, int32_t set, const double* weights, int32_t n_weights) {
+    qb200_desc::Set* s;
+    QB_TRY(set_of(desc, set, &s));
+    if (weights == nullptr || n_weights < 1) return fail(QB200_INVALID, "merge weights are missing");
+    if (n_weights != (int32_t)s->dirs.size())
+        return fail(QB200_INVALID, "%d merge weights for %zu directions", n_weights, s->dirs.size());
+    if (s->has_program) return fail(QB200_INVALID, "declare the merged stream before the program");
+    for (int32_t j = 0; j < n_weights; ++j)
+        if (!std::isfinite(weights[j])) return fail(QB200_INVALID, "merge weight %d is not finite", j);
+    s->merge_w.assign(weights, weights + n_weights);
+    return QB200_OK;
+}
+
 qb200_status qb200_desc_set_program(qb200_desc* desc, int32_t set, const int32_t* code, int32_t n_instr,
                                     const double* consts, int32_t n_consts, int32_t n_regs, int32_t value_reg,
                                     const int32_t* grad_regs, int32_t n_grad_regs) {

@@ -69,6 +69,7 @@ struct qb200_desc {
         std::vector<std::pair<int, int>> cols;  // (input index, column)
         std::vector<std::vector<double>> dirs;
         std::vector<int> orders;
+        std::vector<double> merge_w;  // non-empty: one more stream, the weighted sum of second derivatives
         std::vector<int32_t> code;  // 4 per instruction
         std::vector<double> consts;
         int n_regs = 0;
@@ -78,7 +79,7 @@ struct qb200_desc {
         int streams() const {
             int s = 1;
             for (int k : orders) s += k;
-            return s;
+            return s + (merge_w.empty() ? 0 : 1);
         }
     };
     int dtype = QB200_F32;

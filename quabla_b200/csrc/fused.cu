@@ -65,7 +65,8 @@ bool want_wide_tile() {
     }
 
 // Signature codes: 0 = value only; 1 = {1}; 2 = {2}; 3 = {3}; 4 = {4}; 6 = {1,1};
-// 7 = {2,1}; 11 = {1,2}; 12 = {2,2}.
+// 7 = {2,1}; 11 = {1,2}; 12 = {2,2}; SIG_MERGED + 6 / 31 = {1,1} / {1,1,1} plus the merged
+// second-order stream (2-D / 3-D Laplacian).
 #define QB_CASE(T, W, CODE)                           \
     if (width == W && code == CODE) {                 \
         *out = make_entry<T, W, CODE>();              \
@@ -75,17 +76,20 @@ bool want_wide_tile() {
 template <>
 bool fused_lookup<float>(int width, int code, FusedEntry<float>* out) {
     QB_MMA_CASE(0) QB_MMA_CASE(1) QB_MMA_CASE(2) QB_MMA_CASE(4) QB_MMA_CASE(7) QB_MMA_CASE(12)
+    QB_MMA_CASE(SIG_MERGED + 6) QB_MMA_CASE(SIG_MERGED + 31)
     QB_CASE(float, 64, 0) QB_CASE(float, 64, 1) QB_CASE(float, 64, 2) QB_CASE(float, 64, 4)
-    QB_CASE(float, 64, 7) QB_CASE(float, 64, 12)
+    QB_CASE(float, 64, 7) QB_CASE(float, 64, 12) QB_CASE(float, 64, SIG_MERGED + 6)
     QB_CASE(float, 32, 0) QB_CASE(float, 32, 1) QB_CASE(float, 32, 2) QB_CASE(float, 32, 12)
+    QB_CASE(float, 32, SIG_MERGED + 6)
     QB_CASE(float, 16, 0) QB_CASE(float, 16, 1) QB_CASE(float, 16, 2) QB_CASE(float, 16, 12)
+    QB_CASE(float, 16, SIG_MERGED + 6)
     return false;
 }
 
 template <>
 bool fused_lookup<double>(int width, int code, FusedEntry<double>* out) {
     QB_CASE(double, 16, 0) QB_CASE(double, 16, 1) QB_CASE(double, 16, 2) QB_CASE(double, 16, 7)
-    QB_CASE(double, 16, 12)
+    QB_CASE(double, 16, 12) QB_CASE(double, 16, SIG_MERGED + 6)
     QB_CASE(double, 32, 0) QB_CASE(double, 32, 1) QB_CASE(double, 32, 2)
     return false;
 }

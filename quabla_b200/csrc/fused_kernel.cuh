@@ -27,13 +27,15 @@ constexpr int FUSED_THREADS = 256;
 // order_j * 5^j.  All loops over streams unroll completely.
 template <int CODE>
 struct Sig {
+    static constexpr bool merged = CODE >= SIG_MERGED;  // one extra stream: the merged second order
+    static constexpr int PLAIN = CODE % SIG_MERGED;
     static __host__ __device__ constexpr int order(int j) {
-        int c = CODE;
+        int c = PLAIN;
         for (int i = 0; i < j; ++i) c /= 5;
         return c % 5;
     }
     static __host__ __device__ constexpr int count_dirs() {
-        int c = CODE, n = 0;
+        int c = PLAIN, n = 0;
         while (c > 0) {
             ++n;
             c /= 5;
@@ -46,8 +48,18 @@ struct Sig {
         return b;
     }
     static constexpr int ndirs = count_dirs();
-    static constexpr int S = base(ndirs);
+    static constexpr int S = base(ndirs) + (merged ? 1 : 0);
+    static constexpr int MS = S - 1;  // the merged stream, when there is one
 };
+
+// q = sum_j c_j z1_j^2 over the first-order streams of a merged signature.
+template <typename T, typename SG>
+__device__ __forceinline__ T merged_square_sum(const T (&v)[SG::S], const T* mw) {
+    T q = T(0);
+#pragma unroll
+    for (int j = 0; j < SG::ndirs; ++j) q += mw[j] * v[SG::base(j)] * v[SG::base(j)];
+    return q;
+}
 
 template <typename T>
 struct FusedArgs {
@@ -61,6 +73,7 @@ struct FusedArgs {
     int ncols;
     long long n_points;
     T dirs[MAX_DIRS * 4];  // [ndirs][d0]
+    T merge_w[MAX_DIRS];   // weights of the merged second-order stream (merged signatures only)
     ProgramRef prog;
     const T* cotangent;
     T weight;
@@ -162,16 +175,16 @@ __device__ __forceinline__ void tile_gemm(const T* __restrict__ A, const T* __re
     }
 }
 
-// Forward jet composition on the S streams of one (point, unit).
+// Forward jet composition on the S streams of one (point, unit); mw: weights of the merged stream.
 template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply(T (&v)[SG::S]) {
+__device__ __forceinline__ void jet_apply(T (&v)[SG::S], const T* mw) {
     const T t = qb_tanh<T>(v[0]);
     const TanhD<T> d(t);
+    T hM = T(0);
+    if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG>(v, mw), v[SG::MS]);
     v[0] = t;
 #pragma unroll
     for (int j = 0; j < SG::ndirs; ++j) {
-        constexpr int dummy = 0;
-        (void)dummy;
         T z[MAX_ORDER], h[MAX_ORDER];
         const int K = SG::order(j);
         const int b = SG::base(j);
@@ -187,15 +200,23 @@ __device__ __forceinline__ void jet_apply(T (&v)[SG::S]) {
         for (int m = 0; m < MAX_ORDER; ++m)
             if (m < K) v[b + m] = h[m];
     }
+    if (SG::merged) v[SG::MS] = hM;
 }
 
-// Transposed jet composition: g (cotangents of the post-activation streams)
-// becomes the cotangents of the pre-activation streams z.
+// Transposed composition with the activation's derivatives d at z_0 given: g (cotangents of the
+// post-activation streams) becomes the cotangents of the pre-activation streams z.  z[0] is not read.
 template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply_transposed(const T (&z)[SG::S], T (&g)[SG::S]) {
-    const T t = qb_tanh<T>(z[0]);
-    const TanhD<T> d(t);
+__device__ __forceinline__ void jet_apply_transposed_with(const TanhD<T>& d, const T (&z)[SG::S], T (&g)[SG::S],
+                                                          const T* mw) {
     T z0bar = d.t1 * g[0];
+    T first_factor = T(0);
+    if (SG::merged) {
+        const T gM = g[SG::MS];
+        T gzM;
+        z0bar += merged_compose_transposed(d, merged_square_sum<T, SG>(z, mw), z[SG::MS], gM, &gzM);
+        first_factor = merged_first_order_factor(d, gM);
+        g[SG::MS] = gzM;
+    }
 #pragma unroll
     for (int j = 0; j < SG::ndirs; ++j) {
         T zz[MAX_ORDER], gg[MAX_ORDER], gz[MAX_ORDER];
@@ -215,8 +236,16 @@ __device__ __forceinline__ void jet_apply_transposed(const T (&z)[SG::S], T (&g)
 #pragma unroll
         for (int m = 0; m < MAX_ORDER; ++m)
             if (m < K) g[b + m] = gz[m];
+        if (SG::merged) g[b] += first_factor * mw[j] * z[b];
     }
     g[0] = z0bar;
+}
+
+// The same for tanh, rebuilding the derivatives from z_0.
+template <typename T, typename SG>
+__device__ __forceinline__ void jet_apply_transposed(const T (&z)[SG::S], T (&g)[SG::S], const T* mw) {
+    const TanhD<T> d(qb_tanh<T>(z[0]));
+    jet_apply_transposed_with<T, SG>(d, z, g, mw);
 }
 
 template <typename T, int W, int CODE>
@@ -326,7 +355,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_step_kernel(FusedArgs<
                     T v[S];
 #pragma unroll
                     for (int s = 0; s < S; ++s) v[s] = acc[s][i][j];
-                    jet_apply<T, SG>(v);
+                    jet_apply<T, SG>(v, a.merge_w);
 #pragma unroll
                     for (int s = 0; s < S; ++s) acc[s][i][j] = v[s];
                 }
@@ -427,7 +456,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_step_kernel(FusedArgs<
                         z[s] = zs[s][j];
                         g[s] = acc[s][i][j];
                     }
-                    jet_apply_transposed<T, SG>(z, g);
+                    jet_apply_transposed<T, SG>(z, g, a.merge_w);
 #pragma unroll
                     for (int s = 0; s < S; ++s) acc[s][i][j] = g[s];
                 }

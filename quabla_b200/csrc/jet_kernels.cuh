@@ -37,9 +37,11 @@ struct JetVec<double> {
 
 // Forward jet composition on the S streams of one (point, unit) for activation `act`.
 template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act) {
+__device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act, const T* mw) {
     T value;
     const TanhD<T> d(v[0], act, &value);
+    T hM = T(0);
+    if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG>(v, mw), v[SG::MS]);
     v[0] = value;
 #pragma unroll
     for (int j = 0; j < SG::ndirs; ++j) {
@@ -58,39 +60,13 @@ __device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act) {
         for (int m = 0; m < MAX_ORDER; ++m)
             if (m < K) v[b + m] = h[m];
     }
-}
-
-// Transposed jet composition with the activation's derivatives d at z_0 given.
-template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply_transposed_saved(const TanhD<T>& d, const T (&z)[SG::S], T (&g)[SG::S]) {
-    T z0bar = d.t1 * g[0];
-#pragma unroll
-    for (int j = 0; j < SG::ndirs; ++j) {
-        T zz[MAX_ORDER], gg[MAX_ORDER], gz[MAX_ORDER];
-        const int K = SG::order(j);
-        const int b = SG::base(j);
-#pragma unroll
-        for (int m = 0; m < MAX_ORDER; ++m) {
-            zz[m] = m < K ? z[b + m] : T(0);
-            gg[m] = m < K ? g[b + m] : T(0);
-        }
-        switch (K) {
-            case 1: z0bar += jet_compose_transposed<T, 1>(d, zz, gg, gz); break;
-            case 2: z0bar += jet_compose_transposed<T, 2>(d, zz, gg, gz); break;
-            case 3: z0bar += jet_compose_transposed<T, 3>(d, zz, gg, gz); break;
-            default: z0bar += jet_compose_transposed<T, 4>(d, zz, gg, gz); break;
-        }
-#pragma unroll
-        for (int m = 0; m < MAX_ORDER; ++m)
-            if (m < K) g[b + m] = gz[m];
-    }
-    g[0] = z0bar;
+    if (SG::merged) v[SG::MS] = hM;
 }
 
 // H = tanh-jet(Z), all streams.
 template <typename T, int CODE>
 __global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane,
-                                                              int act) {
+                                                              int act, MergeW<T> mw) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
@@ -108,7 +84,7 @@ __global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restric
             T v[S];
 #pragma unroll
             for (int s = 0; s < S; ++s) v[s] = lanes[s][i];
-            jet_apply_act<T, SG>(v, act);
+            jet_apply_act<T, SG>(v, act, mw.w);
 #pragma unroll
             for (int s = 0; s < S; ++s) lanes[s][i] = v[s];
         }
@@ -124,7 +100,8 @@ template <typename T, int CODE, bool HEAD>
 __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
                                                                T* __restrict__ G, long long plane,
                                                                const T* __restrict__ Uhat, const T* __restrict__ w_head,
-                                                               int d, long long C, int act, T* __restrict__ bias_partial) {
+                                                               int d, long long C, int act, T* __restrict__ bias_partial,
+                                                               MergeW<T> mw) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
@@ -174,7 +151,7 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
             }
             T unused;
             const TanhD<T> dv = act == ACT_TANH ? TanhD<T>(t[i]) : TanhD<T>(t[i], act, &unused);
-            jet_apply_transposed_saved<T, SG>(dv, z, g);
+            jet_apply_transposed_with<T, SG>(dv, z, g, mw.w);
 #pragma unroll
             for (int s = 0; s < S; ++s) gl[s][i] = g[s];
         }
@@ -205,7 +182,8 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
 // 16 bytes at a time.
 template <typename T>
 inline bool jet_sig_eligible(int code, long long plane, const void* a, const void* b, const void* c) {
-    const bool known = code == 0 || code == 1 || code == 2 || code == 4 || code == 7 || code == 12 || code == 187;
+    const bool known = code == 0 || code == 1 || code == 2 || code == 4 || code == 7 || code == 12 || code == 187 ||
+                       code == SIG_MERGED + 6 || code == SIG_MERGED + 31 || code == SIG_MERGED + 156;
     const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c);
     return known && plane % JetVec<T>::V == 0 && (bits & 15) == 0;
 }
@@ -222,26 +200,36 @@ inline int jet_sig_grid(long long vectors) {
     return (int)(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16);
 }
 
+// Merged codes: SIG_MERGED + 6 / 31 / 156 = two / three / four first-order directions plus the merged
+// second-order stream (Laplacians in 2 and 3 dimensions; 3-D heat equation with its time direction).
 template <typename T>
-inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, int act, cudaStream_t stream) {
+inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, int act, const MergeW<T>& mw,
+                                   cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
+#define QB_JET_FWD(CODE) jet_forward_sig_kernel<T, CODE><<<grid, 256, 0, stream>>>(Z, H, plane, act, mw)
     switch (code) {
-        case 0: jet_forward_sig_kernel<T, 0><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
-        case 1: jet_forward_sig_kernel<T, 1><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
-        case 2: jet_forward_sig_kernel<T, 2><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
-        case 4: jet_forward_sig_kernel<T, 4><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
-        case 7: jet_forward_sig_kernel<T, 7><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
-        case 12: jet_forward_sig_kernel<T, 12><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
-        default: jet_forward_sig_kernel<T, 187><<<grid, 256, 0, stream>>>(Z, H, plane, act); break;
+        case 0: QB_JET_FWD(0); break;
+        case 1: QB_JET_FWD(1); break;
+        case 2: QB_JET_FWD(2); break;
+        case 4: QB_JET_FWD(4); break;
+        case 7: QB_JET_FWD(7); break;
+        case 12: QB_JET_FWD(12); break;
+        case SIG_MERGED + 6: QB_JET_FWD(SIG_MERGED + 6); break;
+        case SIG_MERGED + 31: QB_JET_FWD(SIG_MERGED + 31); break;
+        case SIG_MERGED + 156: QB_JET_FWD(SIG_MERGED + 156); break;
+        default: QB_JET_FWD(187); break;
     }
+#undef QB_JET_FWD
 }
 
 template <typename T, bool HEAD>
 inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
-                                         const T* w_head, int d, long long C, int act, T* bias_partial, cudaStream_t stream) {
+                                         const T* w_head, int d, long long C, int act, T* bias_partial,
+                                         const MergeW<T>& mw, cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
-#define QB_JET_BWD(CODE) \
-    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, bias_partial)
+#define QB_JET_BWD(CODE)                                                                                             \
+    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, \
+                                                                     bias_partial, mw)
     switch (code) {
         case 0: QB_JET_BWD(0); break;
         case 1: QB_JET_BWD(1); break;
@@ -249,6 +237,9 @@ inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal,
         case 4: QB_JET_BWD(4); break;
         case 7: QB_JET_BWD(7); break;
         case 12: QB_JET_BWD(12); break;
+        case SIG_MERGED + 6: QB_JET_BWD(SIG_MERGED + 6); break;
+        case SIG_MERGED + 31: QB_JET_BWD(SIG_MERGED + 31); break;
+        case SIG_MERGED + 156: QB_JET_BWD(SIG_MERGED + 156); break;
         default: QB_JET_BWD(187); break;
     }
 #undef QB_JET_BWD
@@ -256,16 +247,18 @@ inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal,
 
 template <typename T>
 inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, int d, int act,
-                                    T* bias_partial, cudaStream_t stream) {
-    jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, stream);
+                                    T* bias_partial, const MergeW<T>& mw, cudaStream_t stream) {
+    jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, mw,
+                                           stream);
 }
 
 // Last hidden layer: the cotangents of H are Uhat (x) w_head, formed inside the kernel; d % V == 0
 // and w_head 16-byte aligned are the caller's to check.
 template <typename T>
 inline void jet_backward_head_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
-                                     const T* w_head, int d, long long C, int act, T* bias_partial, cudaStream_t stream) {
-    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, act, bias_partial, stream);
+                                     const T* w_head, int d, long long C, int act, T* bias_partial,
+                                     const MergeW<T>& mw, cudaStream_t stream) {
+    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, act, bias_partial, mw, stream);
 }
 
 }  // namespace qb

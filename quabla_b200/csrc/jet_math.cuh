@@ -18,11 +18,27 @@ constexpr int MAX_STREAMS = 17;  // 1 + sum of orders, bounded for kernel argume
 
 // Streams of one point set: stream 0 is the primal; direction j of order k_j owns
 // streams base[j] .. base[j] + k_j - 1 (first .. k_j-th derivative along it).
+//
+// Merged second-order stream (merged != 0): when the residual needs second derivatives only as one
+// weighted sum M = sum_j c_j d^2u/ds_j^2 (a Laplacian), the directions j carry first order only and
+// one extra stream, the last, carries M: through an affine layer it maps like every other stream,
+// and through the activation f as  h_M = f'(z_0) z_M + f''(z_0) sum_j c_j z1_j^2.
 struct JetSpec {
     int S;
     int ndirs;
     int order[MAX_DIRS];
     int base[MAX_DIRS];
+    int merged;
+    double merge_w[MAX_DIRS];  // c_j (0 for directions outside the sum)
+};
+
+// Signature codes at or above SIG_MERGED denote (code - SIG_MERGED) plus the merged stream.
+constexpr int SIG_MERGED = 1000000;
+
+// The weights c_j in the arithmetic type of a kernel, passed by value.
+template <typename T>
+struct MergeW {
+    T w[MAX_DIRS];
 };
 
 template <typename T>
@@ -126,6 +142,25 @@ __device__ __forceinline__ T jet_compose_transposed(const TanhD<T>& d, const T* 
     if (K >= 2) gz[1] = a2;
     if (K >= 3) gz[2] = a3;
     return z0bar;
+}
+
+// Merged stream through the activation.  q = sum_j c_j z1_j^2 over the PRE-activation first-order
+// streams; zM the pre-activation merged stream.
+template <typename T>
+__device__ __forceinline__ T merged_compose(const TanhD<T>& d, T q, T zM) {
+    return d.t1 * zM + d.t2 * q;
+}
+// Transpose: gM is the cotangent of h_M.  Returns the contribution to the cotangent of z_0, writes
+// the cotangent of z_M to *gzM; the caller adds  2 f''(z_0) c_j z1_j gM  to the cotangent of z1_j
+// (merged_first_order_factor gives 2 f'' gM).
+template <typename T>
+__device__ __forceinline__ T merged_compose_transposed(const TanhD<T>& d, T q, T zM, T gM, T* gzM) {
+    *gzM = d.t1 * gM;
+    return (d.t2 * zM + d.t3 * q) * gM;
+}
+template <typename T>
+__device__ __forceinline__ T merged_first_order_factor(const TanhD<T>& d, T gM) {
+    return T(2) * d.t2 * gM;
 }
 
 }  // namespace qb

@@ -291,6 +291,16 @@ __global__ void jet_forward_kernel(const T* __restrict__ Z, T* __restrict__ H, l
         T t;
         const TanhD<T> d(Z[e], act, &t);
         H[e] = t;
+        if (spec.merged) {
+            // Reads the pre-activation first-order streams, so it goes before the loop that may run in place.
+            T q = T(0);
+            for (int j = 0; j < spec.ndirs; ++j) {
+                const T z1 = Z[(long long)spec.base[j] * plane + e];
+                q += (T)spec.merge_w[j] * z1 * z1;
+            }
+            const long long m = (long long)(spec.S - 1) * plane + e;
+            H[m] = merged_compose(d, q, Z[m]);
+        }
         for (int j = 0; j < spec.ndirs; ++j) {
             const long long off = (long long)spec.base[j] * plane + e;
             T z[MAX_ORDER], h[MAX_ORDER];
@@ -320,6 +330,20 @@ __global__ void jet_backward_kernel(const T* __restrict__ Z, const T* __restrict
         T unused;
         const TanhD<T> d = act == ACT_TANH ? TanhD<T>(Hprimal[e]) : TanhD<T>(Z[e], act, &unused);
         T z0bar = d.t1 * G[e];
+        T first_factor = T(0);
+        if (spec.merged) {
+            T q = T(0);
+            for (int j = 0; j < spec.ndirs; ++j) {
+                const T z1 = Z[(long long)spec.base[j] * plane + e];
+                q += (T)spec.merge_w[j] * z1 * z1;
+            }
+            const long long m = (long long)(spec.S - 1) * plane + e;
+            const T gM = G[m];
+            T gzM;
+            z0bar += merged_compose_transposed(d, q, Z[m], gM, &gzM);
+            first_factor = merged_first_order_factor(d, gM);
+            G[m] = gzM;
+        }
         for (int j = 0; j < spec.ndirs; ++j) {
             const long long off = (long long)spec.base[j] * plane + e;
             T z[MAX_ORDER], g[MAX_ORDER], gz[MAX_ORDER];
@@ -335,6 +359,7 @@ __global__ void jet_backward_kernel(const T* __restrict__ Z, const T* __restrict
                 case 3: z0bar += jet_compose_transposed<T, 3>(d, z, g, gz); break;
                 default: z0bar += jet_compose_transposed<T, 4>(d, z, g, gz); break;
             }
+            if (spec.merged) gz[0] += first_factor * (T)spec.merge_w[j] * z[0];
 #pragma unroll
             for (int m = 0; m < MAX_ORDER; ++m)
                 if (m < K) G[off + m * plane] = gz[m];

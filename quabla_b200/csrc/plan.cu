@@ -174,6 +174,7 @@ class Plan final : public qb200_plan {
     };
     struct SetState {
         JetSpec spec;
+        MergeW<T> merge_w;         // spec.merge_w in the plan dtype
         int sig_code = 0;          // sum of order_j * 5^j (-1: more than 8 digits would overflow)
         int ncols = 0;
         T* table = nullptr;
@@ -413,13 +414,17 @@ qb200_status Plan<T>::init() {
                 code += k * scale;
                 scale *= 5;
             }
-            st.sig_code = code < 1000000 ? (int)code : -1;
+            st.sig_code = code < SIG_MERGED ? (int)code : -1;
+            if (!s.merge_w.empty() && st.sig_code >= 0) st.sig_code += SIG_MERGED;
         }
         int base = 1;
+        st.spec.merged = s.merge_w.empty() ? 0 : 1;
         for (int j = 0; j < MAX_DIRS; ++j) {
             st.spec.order[j] = j < st.spec.ndirs ? s.orders[j] : 0;
             st.spec.base[j] = base;
             base += st.spec.order[j];
+            st.spec.merge_w[j] = j < (int)s.merge_w.size() ? s.merge_w[j] : 0.0;
+            st.merge_w.w[j] = (T)st.spec.merge_w[j];
         }
         st.ncols = (int)s.cols.size();
         const size_t S = st.spec.S;
@@ -665,6 +670,7 @@ bool Plan<T>::choose_fused() {
             code += k * scale;
             scale *= 5;
         }
+        if (!s.merge_w.empty()) code += SIG_MERGED;
         if (!fused_lookup<T>(W, code, &fused_entries_[si])) return false;
         if (fused_smem_bytes(fused_entries_[si], (int)s.code.size() / 4) > FUSED_MAX_SMEM) return false;
         const long long tiles = (s.n + fused_entries_[si].tile_points - 1) / fused_entries_[si].tile_points;
@@ -723,6 +729,7 @@ qb200_status Plan<T>::run_fused(int si, bool forward_only) {
     a.ncols = st.ncols;
     a.n_points = s.n;
     for (int i = 0; i < MAX_DIRS * 4; ++i) a.dirs[i] = T(0);
+    for (int j = 0; j < MAX_DIRS; ++j) a.merge_w[j] = sets_[si].merge_w.w[j];
     for (size_t j = 0; j < s.dirs.size(); ++j)
         for (int k = 0; k < a.d0; ++k) a.dirs[j * a.d0 + k] = (T)s.dirs[j][k];
     a.prog = st.prog;
@@ -873,7 +880,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         }
         const long long plane = (long long)C * sz[l];
         if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], nullptr))
-            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, desc_.activation, stream_);
+            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, desc_.activation, st.merge_w, stream_);
         else
             jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec, desc_.activation);
         QB_TRY(launched("jet_forward_kernel"));
@@ -992,10 +999,10 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         T* bias_partial = bias_fused ? wpartial_ : nullptr;
         if (l == head && head_fused)
             jet_backward_head_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, Uhat_, weight(head), sz[head], C,
-                                        desc_.activation, bias_partial, stream_);
+                                        desc_.activation, bias_partial, st.merge_w, stream_);
         else if (sig)
             jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, sz[l], desc_.activation, bias_partial,
-                                       stream_);
+                                       st.merge_w, stream_);
         else
             jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec, desc_.activation);
         QB_TRY(launched("jet_backward_kernel"));
