@@ -390,7 +390,7 @@ def main() -> None:
     # (dram__bytes read + write); known for the default workload's fused kernel only.
     traffic = None
     if w.name == "poisson2d" and engine == 2 and per_gpu == 65536 and streams == 4:
-        traffic = 215.8e6
+        traffic = 114.3e6
     extra_peaks = {}
     if dtype_name == "f32":
         # Also measured on this pool (torch.matmul 8192^3, best of 10): TF32 GEMM 756.5, SGEMM 63.9 TFLOP/s.
