@@ -43,8 +43,13 @@ struct Sig {
         return n;
     }
     static __host__ __device__ constexpr int base(int j) {
-        int b = 1;
-        for (int i = 0; i < j; ++i) b += order(i);
+        // One pass over the digits (a nested loop here was not folded to a constant for the fourth
+        // direction, which put the streams of a thread into local memory).
+        int c = PLAIN, b = 1;
+        for (int i = 0; i < j; ++i) {
+            b += c % 5;
+            c /= 5;
+        }
         return b;
     }
     static constexpr int ndirs = count_dirs();
@@ -53,8 +58,10 @@ struct Sig {
 };
 
 // q = sum_j c_j z1_j^2 over the first-order streams of a merged signature.
-template <typename T, typename SG>
-__device__ __forceinline__ T merged_square_sum(const T (&v)[SG::S], const T* mw) {
+// MW is anything indexable by direction (a pointer, or the array inside a by-value kernel parameter,
+// which is then read straight from parameter space).
+template <typename T, typename SG, typename MW>
+__device__ __forceinline__ T merged_square_sum(const T (&v)[SG::S], const MW& mw) {
     T q = T(0);
 #pragma unroll
     for (int j = 0; j < SG::ndirs; ++j) q += mw[j] * v[SG::base(j)] * v[SG::base(j)];
@@ -176,12 +183,12 @@ __device__ __forceinline__ void tile_gemm(const T* __restrict__ A, const T* __re
 }
 
 // Forward jet composition on the S streams of one (point, unit); mw: weights of the merged stream.
-template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply(T (&v)[SG::S], const T* mw) {
+template <typename T, typename SG, typename MW>
+__device__ __forceinline__ void jet_apply(T (&v)[SG::S], const MW& mw) {
     const T t = qb_tanh<T>(v[0]);
     const TanhD<T> d(t);
     T hM = T(0);
-    if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG>(v, mw), v[SG::MS]);
+    if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG, MW>(v, mw), v[SG::MS]);
     v[0] = t;
 #pragma unroll
     for (int j = 0; j < SG::ndirs; ++j) {
@@ -205,15 +212,15 @@ __device__ __forceinline__ void jet_apply(T (&v)[SG::S], const T* mw) {
 
 // Transposed composition with the activation's derivatives d at z_0 given: g (cotangents of the
 // post-activation streams) becomes the cotangents of the pre-activation streams z.  z[0] is not read.
-template <typename T, typename SG>
+template <typename T, typename SG, typename MW>
 __device__ __forceinline__ void jet_apply_transposed_with(const TanhD<T>& d, const T (&z)[SG::S], T (&g)[SG::S],
-                                                          const T* mw) {
+                                                          const MW& mw) {
     T z0bar = d.t1 * g[0];
     T first_factor = T(0);
     if (SG::merged) {
         const T gM = g[SG::MS];
         T gzM;
-        z0bar += merged_compose_transposed(d, merged_square_sum<T, SG>(z, mw), z[SG::MS], gM, &gzM);
+        z0bar += merged_compose_transposed(d, merged_square_sum<T, SG, MW>(z, mw), z[SG::MS], gM, &gzM);
         first_factor = merged_first_order_factor(d, gM);
         g[SG::MS] = gzM;
     }
@@ -242,10 +249,10 @@ __device__ __forceinline__ void jet_apply_transposed_with(const TanhD<T>& d, con
 }
 
 // The same for tanh, rebuilding the derivatives from z_0.
-template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply_transposed(const T (&z)[SG::S], T (&g)[SG::S], const T* mw) {
+template <typename T, typename SG, typename MW>
+__device__ __forceinline__ void jet_apply_transposed(const T (&z)[SG::S], T (&g)[SG::S], const MW& mw) {
     const TanhD<T> d(qb_tanh<T>(z[0]));
-    jet_apply_transposed_with<T, SG>(d, z, g, mw);
+    jet_apply_transposed_with<T, SG, MW>(d, z, g, mw);
 }
 
 template <typename T, int W, int CODE>

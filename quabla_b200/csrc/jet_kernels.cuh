@@ -36,12 +36,12 @@ struct JetVec<double> {
 };
 
 // Forward jet composition on the S streams of one (point, unit) for activation `act`.
-template <typename T, typename SG>
-__device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act, const T* mw) {
+template <typename T, typename SG, typename MW>
+__device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act, const MW& mw) {
     T value;
     const TanhD<T> d(v[0], act, &value);
     T hM = T(0);
-    if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG>(v, mw), v[SG::MS]);
+    if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG, MW>(v, mw), v[SG::MS]);
     v[0] = value;
 #pragma unroll
     for (int j = 0; j < SG::ndirs; ++j) {
