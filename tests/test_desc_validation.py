@@ -123,3 +123,57 @@ def test_activation_is_checked():
     assert lib.qb200_desc_set_activation(desc, 7) == UNSUPPORTED
     assert "tanh (0) or sin (1)" in lib.qb200_last_error().decode()
     lib.qb200_desc_destroy(desc)
+
+
+def test_merged_stream_declaration_is_validated():
+    lib = _lib.load()
+
+    def declare(weights, *, directions=2, after_program=False):
+        desc = C.c_void_p()
+        assert lib.qb200_desc_create(_lib.F64, C.byref(desc)) == 0
+        try:
+            sizes = (C.c_int32 * 3)(2, 8, 1)
+            assert lib.qb200_desc_set_network(desc, sizes, 3) == 0
+            index = C.c_int32()
+            assert lib.qb200_desc_add_input(desc, b"x", 16, 2, 1, C.byref(index)) == 0
+            set_index = C.c_int32()
+            assert lib.qb200_desc_add_set(desc, 16, 1.0 / 16, C.byref(set_index)) == 0
+            for j in range(directions):
+                vec = (C.c_double * 2)(*[1.0 if k == j else 0.0 for k in range(2)])
+                assert lib.qb200_desc_set_add_direction(desc, set_index.value, vec, 1) == 0
+            if after_program:
+                p = _program(1 + directions)
+                assert lib.qb200_desc_set_program(desc, set_index.value, (C.c_int32 * len(p.code))(*p.code), p.n_instr,
+                                                  (C.c_double * 1)(), 0, p.n_regs, p.value_reg,
+                                                  (C.c_int32 * len(p.grad_regs))(*p.grad_regs), len(p.grad_regs)) == 0
+            array = (C.c_double * max(1, len(weights)))(*weights) if weights is not None else None
+            status = lib.qb200_desc_set_merge_second_order(desc, set_index.value, array, len(weights or ()))
+            return status, lib.qb200_last_error().decode()
+        finally:
+            lib.qb200_desc_destroy(desc)
+
+    assert declare([1.0, 1.0])[0] == 0
+    assert declare([1.0, 0.0])[0] == 0  # a direction may stay out of the sum
+    for weights, kwargs, fragment in (([1.0], {}, "1 merge weights for 2 directions"),
+                                      ([1.0, 1.0, 1.0], {}, "3 merge weights for 2 directions"),
+                                      (None, {}, "merge weights are missing"),
+                                      ([1.0, float("nan")], {}, "not finite"),
+                                      ([1.0, float("inf")], {}, "not finite"),
+                                      ([1.0, 1.0], {"after_program": True}, "before the program")):
+        status, message = declare(weights, **kwargs)
+        assert status == INVALID and fragment in message, (weights, message)
+
+
+def test_a_merged_set_counts_its_extra_stream():
+    # Two first-order directions plus the merged stream: the program addresses stream 3.
+    spec = _spec()
+    code = [sx.OP_JET, 0, 3, 0, sx.OP_MUL, 1, 0, 0, sx.OP_ADD, 2, 0, 0]
+    program = Program(code=code, consts=[], n_regs=3, value_reg=1, grad_regs=[-1, -1, -1, 2])
+    spec.sets = [SetSpec(n_points=16, weight=1.0 / 16, columns=[(0, 0), (0, 1)],
+                         directions=[((1.0, 0.0), 1), ((0.0, 1.0), 1)], program=program, merge_weights=[1.0, 1.0])]
+    assert spec.sets[0].streams == 4
+    status, message = _create(spec)
+    assert status in (0, 3), message
+    spec.sets[0].merge_weights = None  # without the declaration stream 3 does not exist
+    status, message = _create(spec)
+    assert status == INVALID, message
