@@ -780,10 +780,13 @@ template <>
 qb200_status Plan<float>::tc_prepare() {
     for (int l = 0; l < L_; ++l) {
         if (tc_image_[l] == nullptr) continue;
-        // TMA kernels take the weight unsplit: W itself for the data gradient, W^T for the forward product.
+        // TMA kernels take the weight unsplit plus its lo plane: W itself for the data gradient, W^T for the
+        // forward product.  Image: [W^T | lo(W^T) | lo(W)], K*N floats each.
+        const size_t kn = (size_t)desc_.sizes[l] * desc_.sizes[l + 1];
+        float* image = reinterpret_cast<float*>(tc_image_[l]);
         cudaError_t e = tc_generation() == 2
-                            ? tc2_transpose_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1],
-                                                   reinterpret_cast<float*>(tc_image_[l]), stream_)
+                            ? tc2_prepare_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], image, image + kn,
+                                                 image + 2 * kn, stream_)
                             : tc_prep_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], tc_image_[l], stream_);
         ++launches_;
         if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of tc_prep_weight_kernel failed: %s", cudaGetErrorString(e));
@@ -796,8 +799,9 @@ bool Plan<float>::tc_forward(int layer, const float* A, float* C, long long rows
     if (!tc_fwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
     cudaError_t e = tc_generation() == 2
-                        ? tc2_rows_launch(A, K, reinterpret_cast<const float*>(tc_image_[layer]), K, C, N, bias(layer),
-                                          bias_rows, (int)rows, N, K, d_error_, stream_)
+                        ? tc2_rows_launch(A, K, reinterpret_cast<const float*>(tc_image_[layer]),
+                                          reinterpret_cast<const float*>(tc_image_[layer]) + (size_t)K * N, K, C, N,
+                                          bias(layer), bias_rows, (int)rows, N, K, d_error_, stream_)
                         : tc_rows_launch(A, K, tc_image_[layer], false, K, N, C, N, bias(layer), bias_rows, (int)rows,
                                          d_error_, stream_);
     ++launches_;
@@ -810,7 +814,8 @@ bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long ro
     if (!tc_bwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
     cudaError_t e = tc_generation() == 2
-                        ? tc2_rows_launch(G, N, weight(layer), N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, stream_)
+                        ? tc2_rows_launch(G, N, weight(layer), reinterpret_cast<const float*>(tc_image_[layer]) + 2 * (size_t)K * N,
+                                          N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, stream_)
                         : tc_rows_launch(G, N, tc_image_[layer], true, K, N, Gprev, K, nullptr, 0, (int)rows, d_error_,
                                          stream_);
     ++launches_;

@@ -127,22 +127,30 @@ cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaSt
     return cudaGetLastError();
 }
 
-template <bool WGRAD, int BN>
-static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcTmaArgs& a,
-                           dim3 grid, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN>),
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, T2Geom<WGRAD, BN>::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    tc_tma_gemm_kernel<WGRAD, BN><<<grid, T2_THREADS_TOTAL, T2Geom<WGRAD, BN>::SMEM_BYTES, stream>>>(ma, mb, mc, a);
+cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, cudaStream_t stream) {
+    t2_prepare_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), dim3(32, 8), 0, stream>>>(
+        w, K, N, wt, reinterpret_cast<uint32_t*>(wt_lo), reinterpret_cast<uint32_t*>(w_lo));
     return cudaGetLastError();
 }
 
-cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, int ldb, float* C, int ldc, const float* bias,
-                            int bias_rows, int M, int N, int K, int* error, cudaStream_t stream) {
+template <bool WGRAD, int BN, bool PRELO>
+static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mblo, const CUtensorMap& mc,
+                           const TcTmaArgs& a, dim3 grid, cudaStream_t stream) {
+    typedef T2Geom<WGRAD, BN, PRELO> G;
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN, PRELO>),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    tc_tma_gemm_kernel<WGRAD, BN, PRELO><<<grid, T2_THREADS_TOTAL, G::SMEM_BYTES, stream>>>(ma, mb, mblo, mc, a);
+    return cudaGetLastError();
+}
+
+cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,
+                            const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream) {
     const int BN = N % 128 == 0 ? 128 : 64;
-    CUtensorMap ma, mb, mc;
+    CUtensorMap ma, mb, mblo, mc;
     if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&mblo, Bt_lo != nullptr ? Bt_lo : Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map(&mc, C, M, N, ldc, 32, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     TcTmaArgs a;
@@ -157,7 +165,11 @@ cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, int ldb, f
     a.units = ((M + T2_BM - 1) / T2_BM) * (N / BN);
     a.error = error;
     const dim3 grid(a.units < 148 ? a.units : 148);
-    return BN == 128 ? launch2<false, 128>(ma, mb, mc, a, grid, stream) : launch2<false, 64>(ma, mb, mc, a, grid, stream);
+    if (Bt_lo != nullptr)
+        return BN == 128 ? launch2<false, 128, true>(ma, mb, mblo, mc, a, grid, stream)
+                         : launch2<false, 64, true>(ma, mb, mblo, mc, a, grid, stream);
+    return BN == 128 ? launch2<false, 128, false>(ma, mb, mblo, mc, a, grid, stream)
+                     : launch2<false, 64, false>(ma, mb, mblo, mc, a, grid, stream);
 }
 
 cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,
@@ -179,7 +191,8 @@ cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, f
     a.k_slice = rows_per_slice;
     a.error = error;
     const dim3 grid(Mw / T2_BM, N / BN, slices);  // the tiles of one slice run together and share its rows in L2
-    return BN == 128 ? launch2<true, 128>(ma, mb, mc, a, grid, stream) : launch2<true, 64>(ma, mb, mc, a, grid, stream);
+    return BN == 128 ? launch2<true, 128, false>(ma, mb, mb, mc, a, grid, stream)
+                     : launch2<true, 64, false>(ma, mb, mb, mc, a, grid, stream);
 }
 
 }  // namespace qb

@@ -31,9 +31,12 @@ cudaError_t tc_wgrad_launch(const float* H, int ldh, const float* G, int ldg, fl
 int tc_generation();
 // wt[n][k] = w[k][n]: the K-major operand of the forward GEMM.
 cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaStream_t stream);
-// C[M][N] = A[M][K] * Bt^T (+ bias on the first bias_rows rows), Bt row-major [N][K].
-cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, int ldb, float* C, int ldc, const float* bias,
-                            int bias_rows, int M, int N, int K, int* error, cudaStream_t stream);
+// One pass over W [K][N]: wt = W^T [N][K], wt_lo = the lo plane of W^T, w_lo = the lo plane of W (each K*N floats).
+cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, cudaStream_t stream);
+// C[M][N] = A[M][K] * Bt^T (+ bias on the first bias_rows rows), Bt row-major [N][K].  Bt_lo, when
+// given, is Bt's lo plane (tc2_prepare_launch): the kernel loads it instead of computing it per tile.
+cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,
+                            const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream);
 cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,
                              int rows_per_slice, int* error, cudaStream_t stream);
 

@@ -49,13 +49,18 @@ struct TcTmaArgs {
     int* error;
 };
 
-template <bool WGRAD, int BN>
+// PRELO (ROWS only): the lo plane of the weight operand is not computed per tile but loaded from a
+// second matrix written once per step (tc2_prepare_launch); a stage then holds A, Bt and Bt_lo, the
+// ring has three stages, and the consumers convert the activation tile only.
+template <bool WGRAD, int BN, bool PRELO = false>
 struct T2Geom {
+    static_assert(!(WGRAD && PRELO), "the weight gradient has no weight operand");
+    static constexpr int STAGES = PRELO ? 3 : T2_STAGES;
     static constexpr int B_BYTES = BN * T2_BK * 4;
-    static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES;            // multiple of 1024
-    static constexpr int LO_OFFSET = T2_STAGES * STAGE_BYTES;
+    static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES + (PRELO ? B_BYTES : 0);  // multiple of 1024
+    static constexpr int LO_OFFSET = STAGES * STAGE_BYTES;
     // ROWS keeps the activation operand in tensor memory, so only the weight tile has a lo plane here.
-    static constexpr int LO_BYTES = WGRAD ? STAGE_BYTES : B_BYTES;
+    static constexpr int LO_BYTES = PRELO ? 0 : (WGRAD ? STAGE_BYTES : B_BYTES);
     // Output staging for the tensor-map store: BN/32 boxes of [128 rows][128 bytes].  WGRAD writes
     // once, after its last MMA, and reuses the stage ring; ROWS overlaps the store with the next tile.
     static constexpr int OUT_BYTES = T2_BM * BN * 4;
@@ -155,11 +160,13 @@ __device__ __forceinline__ void t2_arrive(uint64_t* bar) {
 //   empty[stage]  the item's MMAs completed        tcgen05.commit  -> producer (stage reusable)
 // A consumer arrives on ready[buf] of item i only after it drained item i-2, so that arrival
 // also tells the issuer that accumulator buffer `buf` is free.
-template <bool WGRAD, int BN>
+template <bool WGRAD, int BN, bool PRELO>
 __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     tc_tma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                       const __grid_constant__ CUtensorMap map_c, TcTmaArgs a) {
-    typedef T2Geom<WGRAD, BN> G;
+                       const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_c,
+                       TcTmaArgs a) {
+    typedef T2Geom<WGRAD, BN, PRELO> G;
+    constexpr int STAGES = G::STAGES;
     extern __shared__ unsigned char t2_smem_raw[];
     // Swizzled tiles need 1024-byte alignment.
     unsigned char* const smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(t2_smem_raw) + 1023) &
@@ -223,16 +230,18 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            if (PRELO) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_blo) : "memory");
             int u = 0, kt = 0, m0 = unit_m0(0), n0 = unit_n0(0);
             for (int p = 0; p < items; ++p) {
-                const int s = p % T2_STAGES;
-                if (p >= T2_STAGES) mbar_wait(empty + s, (uint32_t)((p / T2_STAGES - 1) & 1), a.error);
+                const int s = p % STAGES;
+                if (p >= STAGES) mbar_wait(empty + s, (uint32_t)((p / STAGES - 1) & 1), a.error);
                 unsigned char* stage = smem + s * G::STAGE_BYTES;
                 const int k0 = k_begin + kt * T2_BK;
                 mbar_expect_tx(full + s, G::STAGE_BYTES);
                 if (!WGRAD) {
                     t2_tma_load(stage, &map_a, k0, m0, full + s);               // box {32 k, 128 rows}
                     t2_tma_load(stage + T2_A_BYTES, &map_b, k0, n0, full + s);  // box {32 k, BN rows}
+                    if (PRELO) t2_tma_load(stage + T2_A_BYTES + G::B_BYTES, &map_blo, k0, n0, full + s);
                 } else {
 #pragma unroll
                     for (int j = 0; j < T2_BM / 32; ++j) t2_tma_load(stage + j * 4096, &map_a, m0 + 32 * j, k0, full + s);
@@ -253,12 +262,12 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
         if (lane == 0) {
             const uint32_t idesc = t2_idesc(BN, WGRAD);
             for (int it = 0; it < items; ++it) {
-                const int s = it % T2_STAGES, b = it & 1;
+                const int s = it % STAGES, b = it & 1;
                 mbar_wait(ready + b, (uint32_t)((it >> 1) & 1), a.error);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ah = smem_u32(smem + s * G::STAGE_BYTES);
                 const uint32_t al = smem_u32(smem + G::LO_OFFSET + b * G::LO_BYTES);  // WGRAD only: lo of A, then of B
-                const uint32_t bh = ah + T2_A_BYTES, bl = WGRAD ? al + T2_A_BYTES : al;
+                const uint32_t bh = ah + T2_A_BYTES, bl = PRELO ? bh + G::B_BYTES : (WGRAD ? al + T2_A_BYTES : al);
                 const uint32_t dst = tmem_base + (uint32_t)(b * BN);
                 // k = 8 per instruction: 32 bytes along a K-major row, two 4-row groups (1024 bytes)
                 // of an MN-major atom.  The small correction products go first (they add onto a
@@ -353,10 +362,10 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
         };
 
         for (int it = 0; it < items; ++it) {
-            const int s = it % T2_STAGES, b = it & 1;
+            const int s = it % STAGES, b = it & 1;
             const unsigned char* hi = smem + s * G::STAGE_BYTES;
             unsigned char* lo = smem + G::LO_OFFSET + b * G::LO_BYTES;
-            mbar_wait(full + s, (uint32_t)((it / T2_STAGES) & 1), a.error);
+            mbar_wait(full + s, (uint32_t)((it / STAGES) & 1), a.error);
             // The lo buffer b was last read by item it-2, which this thread has drained.
             if (A_TMEM) {
                 // Activation tile: this thread's row (its accumulator lane), 16 of the 32 k (by column
@@ -374,9 +383,9 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                 const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(A_COL0 + b * 64 + half * 16);
                 t2_store16(ta, xh);
                 t2_store16(ta + 32, xl);
-                // Weight tile: lo plane in shared memory, element by element.
+                // Weight tile: lo plane in shared memory, element by element (unless it was loaded).
 #pragma unroll
-                for (int i = 0; i < (G::B_BYTES / 16) / T2_THREADS; ++i) {
+                for (int i = 0; i < (PRELO ? 0 : (G::B_BYTES / 16) / T2_THREADS); ++i) {
                     const int v = tid + i * T2_THREADS;
                     const uint4 x = *reinterpret_cast<const uint4*>(hi + T2_A_BYTES + 16 * v);
                     *reinterpret_cast<uint4*>(lo + 16 * v) =
@@ -394,7 +403,8 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             }
             // Generic-proxy writes must be visible to the tensor core (async proxy) before the
             // issuer is told; the tcgen05 fence orders the drain of item it-2 before that too.
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // (With the lo plane loaded, the consumers wrote tensor memory only.)
+            if (!PRELO) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             t2_arrive(ready + b);
             if (it >= 1) {
@@ -427,6 +437,29 @@ __global__ void t2_transpose_kernel(const float* __restrict__ w, int K, int N, f
     for (int r = threadIdx.y; r < 32; r += blockDim.y) {
         const int n = n0 + r, k = k0 + threadIdx.x;
         if (n < N && k < K) wt[(size_t)n * K + k] = tile[threadIdx.x][r];
+    }
+}
+
+// One pass over a weight W [K][N] for the PRELO kernels: wt[n][k] = W[k][n] (the K-major forward
+// operand), wt_lo = its lo plane, w_lo[k][n] = the lo plane of W itself (the data gradient's operand).
+__global__ void t2_prepare_kernel(const float* __restrict__ w, int K, int N, float* __restrict__ wt,
+                                  uint32_t* __restrict__ wt_lo, uint32_t* __restrict__ w_lo) {
+    __shared__ float tile[32][33];
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int k = k0 + r, n = n0 + threadIdx.x;
+        const float v = (k < K && n < N) ? w[(size_t)k * N + n] : 0.0f;
+        tile[r][threadIdx.x] = v;
+        if (k < K && n < N) w_lo[(size_t)k * N + n] = t2_lo_bits(__float_as_uint(v));
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int n = n0 + r, k = k0 + threadIdx.x;
+        if (n < N && k < K) {
+            const float v = tile[threadIdx.x][r];
+            wt[(size_t)n * K + k] = v;
+            wt_lo[(size_t)n * K + k] = t2_lo_bits(__float_as_uint(v));
+        }
     }
 }
 
