@@ -1,7 +1,7 @@
-"""The BASELINE configurations at their full sizes.
+"""The five benchmark configurations at their full sizes.
 
 Where the CPU oracle finishes in seconds on all host threads (2-D Poisson, beam, Burgers) the
-device result is compared with it directly; the 3-D heat step (16.5 TFLOP per pass) is checked
+device result is compared with it directly; the 3-D heat step (12 TFLOP per pass) is checked
 through size-independent properties instead: bitwise repeatability, exact linearity in the loss
 cotangent (a power of two scales every gradient bit for bit), and additivity over point shards.
 """
