@@ -106,7 +106,12 @@ typedef enum qb200_op {
     QB200_OP_TANH = 11,
     QB200_OP_POWI = 12, /* r[dst] = r[a] ** b, b an integer literal */
     QB200_OP_SQRT = 13,
-    QB200_OP_LOG = 14
+    QB200_OP_LOG = 14,
+    QB200_OP_LOG1P = 15, /* UnaryMath kinds of the reference (elementwise.rs:400-450) */
+    QB200_OP_EXPM1 = 16,
+    QB200_OP_ERF = 17,
+    QB200_OP_ERFC = 18,
+    QB200_OP_TAN = 19
 } qb200_op;
 
 typedef struct qb200_desc qb200_desc;

@@ -43,7 +43,7 @@
 
 enum {
     OP_CONST = 0, OP_COL, OP_JET, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_NEG, OP_SIN, OP_COS, OP_EXP, OP_TANH, OP_POWI,
-    OP_SQRT, OP_LOG
+    OP_SQRT, OP_LOG, OP_LOG1P, OP_EXPM1, OP_ERF, OP_ERFC, OP_TAN
 };
 
 typedef struct {
@@ -101,6 +101,11 @@ static void run_program(const qbo_set* s, const double* cols, const double* jets
             case OP_POWI: v = powi(r[in[2]], in[3]); break;
             case OP_SQRT: v = sqrt(r[in[2]]); break;
             case OP_LOG: v = log(r[in[2]]); break;
+            case OP_LOG1P: v = log1p(r[in[2]]); break;
+            case OP_EXPM1: v = expm1(r[in[2]]); break;
+            case OP_ERF: v = erf(r[in[2]]); break;
+            case OP_ERFC: v = erfc(r[in[2]]); break;
+            case OP_TAN: v = tan(r[in[2]]); break;
             default: v = 0.0; break;
         }
         r[in[1]] = v;

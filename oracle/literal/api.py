@@ -14,6 +14,8 @@ transforms that graph, and splices the result into the caller's graph
 
 from __future__ import annotations
 
+import math
+
 import numpy as np
 
 from . import transforms as tf
@@ -180,6 +182,11 @@ tanh = _unary("tanh", np.tanh)
 sin = _unary("sin", np.sin)
 cos = _unary("cos", np.cos)
 exp = _unary("exp", np.exp)
+log1p = _unary("log1p", np.log1p)
+expm1 = _unary("expm1", np.expm1)
+tan = _unary("tan", np.tan)
+erf = _unary("erf", np.vectorize(math.erf, otypes=[np.float64]))
+erfc = _unary("erfc", np.vectorize(math.erfc, otypes=[np.float64]))
 
 
 def mean(x):

@@ -14,7 +14,11 @@ import numpy as np
 
 from .ir import F32, Graph
 
-_UNARY = {"tanh": np.tanh, "sin": np.sin, "cos": np.cos, "exp": np.exp}
+import math
+
+_UNARY = {"tanh": np.tanh, "sin": np.sin, "cos": np.cos, "exp": np.exp, "log1p": np.log1p, "expm1": np.expm1,
+          "tan": np.tan, "erf": np.vectorize(math.erf, otypes=[np.float64]),
+          "erfc": np.vectorize(math.erfc, otypes=[np.float64])}
 
 
 def _round(value: np.ndarray, dtype: str) -> np.ndarray:

@@ -8,7 +8,7 @@ dtype and weakness derived from the value operands (:7029-7074).
 
 Ops: input, scalar_constant, constant, cast, add, sub, mul, div, matmul, sum,
 sum_axis, mean, mean_axis, reshape, transpose, broadcast, powi, unary (tanh,
-sin, cos, exp), slice, pad_slice, concat.
+sin, cos, exp, log1p, expm1, erf, erfc, tan), slice, pad_slice, concat.
 """
 
 from __future__ import annotations
@@ -18,7 +18,7 @@ from dataclasses import dataclass
 import numpy as np
 
 F32, F64 = "f32", "f64"
-UNARY_KINDS = ("tanh", "sin", "cos", "exp")
+UNARY_KINDS = ("tanh", "sin", "cos", "exp", "log1p", "expm1", "erf", "erfc", "tan")
 
 
 @dataclass

@@ -9,6 +9,8 @@ inline_batched   tensor_ir.rs:2612-2690 with tensor_ir/op/batch.rs:21-205.
 
 from __future__ import annotations
 
+import math
+
 import numpy as np
 
 from .ir import F64, Graph, Node
@@ -65,11 +67,28 @@ def _unary_chain(g: Graph, kind: str, operand: int, value: int):
         return "times", g.unary(operand, "cos")
     if kind == "cos":
         return "negated", g.unary(operand, "sin")
+    if kind == "log1p":
+        one = g.scalar_constant(1.0)
+        return "over", g.add(one, operand)
+    if kind == "expm1":
+        return "times", g.unary(operand, "exp")
+    if kind in ("erf", "erfc"):
+        # sign * 2 / sqrt(pi) * exp(-(x * x))  (erf_derivative, tensor_ir/elementwise.rs:487-500)
+        squared = g.mul(operand, operand)
+        zero = g.scalar_constant(0.0)
+        bell = g.unary(g.sub(zero, squared), "exp")
+        scale = g.scalar_constant((2.0 if kind == "erf" else -2.0) / math.sqrt(math.pi))
+        return "times", g.mul(scale, bell)
+    if kind == "tan":
+        one = g.scalar_constant(1.0)
+        return "times", g.add(one, g.mul(value, value))
     raise ValueError(kind)
 
 
 def _apply_chain(g: Graph, chain, seed: int) -> int:
     mode, derivative = chain
+    if mode == "over":
+        return g.div(seed, derivative)
     product = g.mul(seed, derivative)
     if mode == "times":
         return product
@@ -252,7 +271,7 @@ def _push_jvp(g: Graph, node: Node, pairs: list):
     if op == "unary":
         v, t = pairs[ins[0]]
         kind = node.attrs[0]
-        if kind in ("sin", "cos"):  # kinds that emit their derivative first
+        if kind in ("sin", "cos", "log1p", "expm1", "erf", "erfc"):  # kinds that emit their derivative first
             chain = _unary_chain(g, kind, v, None)
             value = g.unary(v, kind)
         else:

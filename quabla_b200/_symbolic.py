@@ -21,10 +21,10 @@ from typing import Callable, Iterable
 
 # Opcodes of the register program; numbering fixed by qb200_op in include/qb200.h.
 OP_CONST, OP_COL, OP_JET, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_NEG, OP_SIN, OP_COS, OP_EXP, OP_TANH, OP_POWI, \
-    OP_SQRT, OP_LOG = range(15)
+    OP_SQRT, OP_LOG, OP_LOG1P, OP_EXPM1, OP_ERF, OP_ERFC, OP_TAN = range(20)
 
 _UNARY_OPS = {"neg": OP_NEG, "sin": OP_SIN, "cos": OP_COS, "exp": OP_EXP, "tanh": OP_TANH, "sqrt": OP_SQRT,
-              "log": OP_LOG}
+              "log": OP_LOG, "log1p": OP_LOG1P, "expm1": OP_EXPM1, "erf": OP_ERF, "erfc": OP_ERFC, "tan": OP_TAN}
 _BINARY_OPS = {"add": OP_ADD, "sub": OP_SUB, "mul": OP_MUL, "div": OP_DIV}
 
 MAX_REGS = 64
@@ -222,7 +222,10 @@ def powi(a: Expr, n: int) -> Expr:
 
 _CONST_FUNCS: dict[str, Callable[[float], float]] = {
     "sin": math.sin, "cos": math.cos, "exp": math.exp, "tanh": math.tanh, "sqrt": math.sqrt, "log": math.log,
+    "log1p": math.log1p, "expm1": math.expm1, "erf": math.erf, "erfc": math.erfc, "tan": math.tan,
 }
+
+TWO_OVER_SQRT_PI = 2.0 / math.sqrt(math.pi)
 
 
 def unary(kind: str, a) -> Expr:
@@ -299,6 +302,17 @@ def derivative(root: Expr, leaf_rule: Callable[[Expr], Expr]) -> Expr:
             r = div(d[e.args[0]], mul(const(2.0), e))
         elif k == "log":
             r = div(d[e.args[0]], e.args[0])
+        # The chains below are the reference's (unary_math_chain, tensor_ir/elementwise.rs:416-450).
+        elif k == "log1p":
+            r = div(d[e.args[0]], add(ONE, e.args[0]))
+        elif k == "expm1":
+            r = mul(unary("exp", e.args[0]), d[e.args[0]])
+        elif k in ("erf", "erfc"):
+            a = e.args[0]
+            bell = mul(const(TWO_OVER_SQRT_PI if k == "erf" else -TWO_OVER_SQRT_PI), unary("exp", neg(mul(a, a))))
+            r = mul(bell, d[a])
+        elif k == "tan":
+            r = mul(add(ONE, mul(e, e)), d[e.args[0]])
         else:  # pragma: no cover
             raise UnsupportedExpression(f"no derivative rule for {k}")
         d[e] = r

@@ -10,6 +10,7 @@ device plan and run it on a CUDA device.
 from __future__ import annotations
 
 import inspect
+import math
 from collections import OrderedDict
 from typing import Any, Callable, Sequence
 
@@ -326,6 +327,11 @@ cos = _unary("cos", np.cos)
 exp = _unary("exp", np.exp)
 log = _unary("log", np.log)
 sqrt = _unary("sqrt", np.sqrt)
+log1p = _unary("log1p", np.log1p)
+expm1 = _unary("expm1", np.expm1)
+tan = _unary("tan", np.tan)
+erf = _unary("erf", np.vectorize(math.erf, otypes=[np.float64]))
+erfc = _unary("erfc", np.vectorize(math.erfc, otypes=[np.float64]))
 
 
 def mean(x, axis=None):

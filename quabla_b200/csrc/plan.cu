@@ -107,6 +107,7 @@ qb200_status validate_desc(const qb200_desc& d) {
                 case OP_JET: ok = a >= 0 && a < S; break;
                 case OP_ADD: case OP_SUB: case OP_MUL: case OP_DIV: ok = reg_ok(a) && reg_ok(b); break;
                 case OP_NEG: case OP_SIN: case OP_COS: case OP_EXP: case OP_TANH: case OP_SQRT: case OP_LOG:
+                case OP_LOG1P: case OP_EXPM1: case OP_ERF: case OP_ERFC: case OP_TAN:
                 case OP_POWI: ok = reg_ok(a); break;
                 default: return fail(QB200_UNSUPPORTED, "set %zu: instruction %d has unknown opcode %d", si, pc, op);
             }

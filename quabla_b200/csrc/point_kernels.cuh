@@ -14,7 +14,7 @@ constexpr int MAX_COLS = 16;     // columns of a point table
 // Opcodes; numbering fixed by include/qb200.h (qb200_op).
 enum : int {
     OP_CONST = 0, OP_COL, OP_JET, OP_ADD, OP_SUB, OP_MUL, OP_DIV, OP_NEG, OP_SIN, OP_COS, OP_EXP, OP_TANH,
-    OP_POWI, OP_SQRT, OP_LOG
+    OP_POWI, OP_SQRT, OP_LOG, OP_LOG1P, OP_EXPM1, OP_ERF, OP_ERFC, OP_TAN
 };
 
 struct ProgramRef {
@@ -37,6 +37,21 @@ template <> __device__ __forceinline__ double qb_exp<double>(double x) { return 
 template <typename T> __device__ __forceinline__ T qb_log(T x);
 template <> __device__ __forceinline__ float qb_log<float>(float x) { return logf(x); }
 template <> __device__ __forceinline__ double qb_log<double>(double x) { return log(x); }
+template <typename T> __device__ __forceinline__ T qb_log1p(T x);
+template <> __device__ __forceinline__ float qb_log1p<float>(float x) { return log1pf(x); }
+template <> __device__ __forceinline__ double qb_log1p<double>(double x) { return log1p(x); }
+template <typename T> __device__ __forceinline__ T qb_expm1(T x);
+template <> __device__ __forceinline__ float qb_expm1<float>(float x) { return expm1f(x); }
+template <> __device__ __forceinline__ double qb_expm1<double>(double x) { return expm1(x); }
+template <typename T> __device__ __forceinline__ T qb_erf(T x);
+template <> __device__ __forceinline__ float qb_erf<float>(float x) { return erff(x); }
+template <> __device__ __forceinline__ double qb_erf<double>(double x) { return erf(x); }
+template <typename T> __device__ __forceinline__ T qb_erfc(T x);
+template <> __device__ __forceinline__ float qb_erfc<float>(float x) { return erfcf(x); }
+template <> __device__ __forceinline__ double qb_erfc<double>(double x) { return erfc(x); }
+template <typename T> __device__ __forceinline__ T qb_tan(T x);
+template <> __device__ __forceinline__ float qb_tan<float>(float x) { return tanf(x); }
+template <> __device__ __forceinline__ double qb_tan<double>(double x) { return tan(x); }
 template <typename T> __device__ __forceinline__ T qb_sqrt(T x);
 template <> __device__ __forceinline__ float qb_sqrt<float>(float x) { return sqrtf(x); }
 template <> __device__ __forceinline__ double qb_sqrt<double>(double x) { return sqrt(x); }
@@ -80,6 +95,11 @@ __device__ __forceinline__ void run_program(const int4* code, int n_instr, const
             case OP_POWI: v = qb_powi<T>(r[in.z], in.w); break;
             case OP_SQRT: v = qb_sqrt<T>(r[in.z]); break;
             case OP_LOG: v = qb_log<T>(r[in.z]); break;
+            case OP_LOG1P: v = qb_log1p<T>(r[in.z]); break;
+            case OP_EXPM1: v = qb_expm1<T>(r[in.z]); break;
+            case OP_ERF: v = qb_erf<T>(r[in.z]); break;
+            case OP_ERFC: v = qb_erfc<T>(r[in.z]); break;
+            case OP_TAN: v = qb_tan<T>(r[in.z]); break;
             default: v = T(0); break;
         }
         r[in.y] = v;

@@ -241,3 +241,30 @@ def test_trainer_resumes_bit_for_bit_from_a_saved_state(cuda_device, tmp_path, r
     bad["params"] = leaves(bad["params"])[:-1]
     with pytest.raises(ValueError):
         resumed.import_state(bad)
+
+
+@pytest.mark.parametrize("dtype,width", [(np.float64, 16), (np.float32, 64), (np.float32, 128)])
+def test_special_functions_in_the_residual_program(cuda_device, dtype, width):
+    # log1p, expm1, erf, erfc and tan of the coordinate, of u and of its derivatives, on the fused
+    # engines (widths 16 and 64) and the layer-wise one (128).
+    from test_oracle_pins import _special_function_loss
+
+    sizes = [1, width, width, 1]
+    params = workloads.init_mlp(qb.random.key(5), sizes, dtype)
+    x = qb.random.uniform(qb.random.key(6), (999,), dtype, -1.0, 1.0)
+    loss = _special_function_loss(qb)
+    from quabla_b200._transforms import CompiledLoss
+
+    compiled = CompiledLoss(loss, (params, x), (0,), 0, build_plan=False)
+    inputs = compiled.named_inputs((params, x))
+    expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    plan.execute()
+    outputs = plan.outputs()
+    plan.close()
+    tol = TOLERANCE[np.dtype(dtype)]
+    assert relative_error(outputs[0], expected_loss) <= tol
+    for got, expected, (pname, _, _) in zip(outputs[1:], expected_grads, compiled.spec.parameters):
+        assert relative_error(got.reshape(expected.shape), expected) <= tol, pname

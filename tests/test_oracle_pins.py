@@ -195,3 +195,53 @@ def test_a_network_cannot_mix_activations():
     params = workloads.init_mlp(qb.random.key(0), [1, 8, 8, 1])
     with pytest.raises(UnsupportedOperationError):
         CompiledLoss(loss, (params, np.linspace(0.0, 1.0, 8)), (0,), 0, build_plan=False)
+
+
+def _special_function_loss(api):
+    """A 1-D loss whose residual applies log1p, expm1, erf, erfc and tan to the coordinate, to u and to
+    derivatives of u, so that every chain rule of those kinds is exercised at first and second order."""
+    u = workloads.make_u(api)
+
+    def loss(params, x):
+        f = lambda t: u(params, t)  # noqa: E731
+        value = api.vmap(f)(x)
+        slope = api.vmap(api.grad(f))(x)
+        curvature = api.vmap(api.grad(api.grad(f)))(x)
+        residual = (api.log1p(value * value) + api.expm1(0.3 * slope) + api.erf(curvature) * api.erfc(0.5 * x)
+                    + api.tan(0.4 * value) - api.log1p(x * x) * api.erf(x))
+        return api.mean(residual ** 2)
+
+    return loss
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_special_function_chains_match_the_literal_oracle(dtype):
+    import quabla_b200 as qb
+    from quabla_b200._transforms import CompiledLoss
+
+    sizes = [1, 8, 8, 1]
+    params = workloads.init_mlp(qb.random.key(5), sizes, dtype)
+    x = qb.random.uniform(qb.random.key(6), (24,), dtype, -1.0, 1.0)
+    compiled = CompiledLoss(_special_function_loss(qb), (params, x), (0,), 0, build_plan=False)
+    inputs = compiled.named_inputs((params, x))
+    expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
+    value, grads = literal.value_and_grad(_special_function_loss(literal))(params, x)
+    tolerance = 1e-12 if dtype == np.float64 else 5e-6
+    assert relative_error(value, expected_loss) <= tolerance
+    got = {}
+    for layer, tree in enumerate(grads):
+        got[f"params/{layer}/w"], got[f"params/{layer}/b"] = tree["w"], tree["b"]
+    for (pname, _, _), expected in zip(compiled.spec.parameters, expected_grads):
+        assert relative_error(np.asarray(got[pname]).reshape(expected.shape), expected) <= tolerance, pname
+    # And the gradient is the derivative of the value (central differences on one weight).
+    if dtype == np.float64:
+        step = literal.value_and_grad(_special_function_loss(literal))
+        h = 1e-6
+        plus = [dict(layer) for layer in params]
+        minus = [dict(layer) for layer in params]
+        plus[1]["w"] = params[1]["w"].copy()
+        minus[1]["w"] = params[1]["w"].copy()
+        plus[1]["w"][2, 3] += h
+        minus[1]["w"][2, 3] -= h
+        fd = (float(step(plus, x)[0]) - float(step(minus, x)[0])) / (2 * h)
+        assert abs(float(grads[1]["w"][2, 3]) - fd) <= 1e-6 * max(abs(fd), 1e-3)
