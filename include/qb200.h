@@ -16,7 +16,12 @@
  *    (cuda_optimizer.rs:207-212, cuda.rs:3349-3368);
  *  - a plan owns all of its device memory (parameters, optimizer moments,
  *    saved activations); host buffers are copied, never aliased;
- *  - one CUDA stream per plan, every kernel of the plan runs on it;
+ *  - one CUDA stream per plan (QB200_Q_STREAM) carries every kernel of a step; plans with several
+ *    point sets on the fused engines also own a lower-priority side stream on which the small
+ *    sets' kernels run between a fork and a join event of the main stream, so work enqueued on
+ *    the main stream after a step is still ordered after all of it;
+ *  - calls on one plan are serialised by a per-plan mutex (the reference keeps its plan state
+ *    behind one, cuda.rs:86);
  *  - there is no CPU fallback: a description the backend does not recognise
  *    returns QB200_UNSUPPORTED (docs/guide/13-architecture.md:392-393,
  *    "no silent fallback").
@@ -87,8 +92,17 @@ typedef enum qb200_query {
     QB200_Q_STEP_COUNT = 8,          /* optimizer updates applied so far */
     QB200_Q_ENGINE = 9,              /* 0: layer-wise (FP pipe), 1: fused (FP32 pipe), 2: fused (mma 3xTF32), 3: layer-wise with tcgen05 GEMMs */
     QB200_Q_SET0_NANOSECONDS = 10,   /* device time of the last execute's kernels for point set 0 (events) */
-    QB200_Q_ALLREDUCE_NANOSECONDS = 11 /* device time of the last execute's gradient all-reduce, waits for peers included */
+    QB200_Q_ALLREDUCE_NANOSECONDS = 11, /* device time of the last execute's gradient all-reduce, waits for peers included */
+    QB200_Q_GEMM_NANOSECONDS = 12,   /* with QB200_OPT_KERNEL_TIMERS: summed device time of the last execute's layer GEMM launches
+                                        (tcgen05 / FP64-MMA / SIMT products of the layer-wise engine; 0 on the fused engines) */
+    QB200_Q_GEMM_LAUNCHES = 13,      /* ... how many launches that sum covers */
+    QB200_Q_GEMM_FLOPS = 14          /* ... and their 2*M*N*K in total */
 } qb200_query;
+
+/* Keys of qb200_plan_set_option. */
+typedef enum qb200_option {
+    QB200_OPT_KERNEL_TIMERS = 0      /* non-zero: record a CUDA event pair around every layer GEMM launch */
+} qb200_option;
 
 /* Opcodes of the per-point residual program (see qb200_desc_set_program). */
 typedef enum qb200_op {
@@ -233,8 +247,20 @@ qb200_status qb200_plan_write_moments(qb200_plan* plan, int32_t which, const voi
                                       int64_t step_count);
 
 qb200_status qb200_plan_query(qb200_plan* plan, int32_t key, int64_t* out);
-/* CudaExecutionPlan::synchronize (cuda.rs:1174-1180). */
+/* Measurement switches (qb200_option); no counterpart in the reference, whose timing is host wall clock
+ * (CudaDataParallelTiming, cuda.rs:154-170). */
+qb200_status qb200_plan_set_option(qb200_plan* plan, int32_t key, int64_t value);
+/* CudaExecutionPlan::synchronize (cuda.rs:1174-1180).  Like every call that waits for the stream
+ * (read_output, read_input, loss) it returns QB200_CUDA_ERROR when a bounded wait inside a kernel
+ * gave up during a step since the last report; the optimizer update of such a step is skipped on
+ * the device (on every rank of a data-parallel run: the flag travels with the gradient all-reduce),
+ * so parameters and moments never absorb invalid gradients. */
 qb200_status qb200_plan_synchronize(qb200_plan* plan);
+/* Test seam for that error path: enqueues one thread's short bounded wait on a barrier that nothing
+ * completes; the wait gives up and raises the plan's device error flag exactly as a staged copy that
+ * never lands would.  Nothing faults, traps or spins for long.  The reference reaches the same state
+ * only through a failing CUDA call (cuda.rs:1386-1447 propagates the driver error). */
+qb200_status qb200_plan_inject_wait_timeout(qb200_plan* plan);
 
 /* Multi-process data parallelism (one process per GPU): rank 0 obtains an id,
  * the caller ships the 128 bytes to the other ranks, every rank attaches.

@@ -20,7 +20,8 @@ SGD, ADAM = 0, 1
 REDUCE_SUM, REDUCE_MEAN = 0, 1
 (Q_DEVICE_BUFFER_COUNT, Q_NONFINITE_CLIP_SEEN, Q_STREAM, Q_PARAMETER_COUNT, Q_OUTPUT_COUNT,
  Q_KERNEL_LAUNCHES, Q_FLAT_DEVICE_PTR, Q_SCRATCH_BYTES, Q_STEP_COUNT, Q_ENGINE, Q_SET0_NANOSECONDS,
- Q_ALLREDUCE_NANOSECONDS) = range(12)
+ Q_ALLREDUCE_NANOSECONDS, Q_GEMM_NANOSECONDS, Q_GEMM_LAUNCHES, Q_GEMM_FLOPS) = range(15)
+OPT_KERNEL_TIMERS = 0
 
 
 class OptConfig(C.Structure):
@@ -88,7 +89,9 @@ SIGNATURES = {
     "qb200_plan_read_moments": (_I32, [_P, _I32, _P, C.c_size_t]),
     "qb200_plan_write_moments": (_I32, [_P, _I32, _P, C.c_size_t, _I64]),
     "qb200_plan_query": (_I32, [_P, _I32, C.POINTER(_I64)]),
+    "qb200_plan_set_option": (_I32, [_P, _I32, _I64]),
     "qb200_plan_synchronize": (_I32, [_P]),
+    "qb200_plan_inject_wait_timeout": (_I32, [_P]),
     "qb200_nccl_unique_id": (_I32, [_P]),
     "qb200_plan_attach_comm": (_I32, [_P, _P, _I32, _I32, _I32]),
     "qb200_plan_detach_comm": (_I32, [_P]),

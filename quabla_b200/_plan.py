@@ -216,6 +216,13 @@ class Plan:
     def synchronize(self) -> None:
         _lib.check(self._lib.qb200_plan_synchronize(self._handle))
 
+    def set_option(self, key: int, value: int) -> None:
+        _lib.check(self._lib.qb200_plan_set_option(self._handle, int(key), int(value)))
+
+    def inject_wait_timeout(self) -> None:
+        """Test seam: enqueue a bounded wait that gives up, which raises the plan's device error flag."""
+        _lib.check(self._lib.qb200_plan_inject_wait_timeout(self._handle))
+
     def attach_comm(self, unique_id: bytes, rank: int, world: int, reduction: str = "mean") -> None:
         if len(unique_id) != 128:
             raise ValueError("an NCCL unique id is 128 bytes")

@@ -16,6 +16,7 @@
 #include "plan.h"
 #include "tc_gemm.h"
 #include "point_kernels.cuh"
+#include "wgrad.h"
 
 namespace qb {
 
@@ -97,6 +98,10 @@ struct qb200_dp {
     std::mutex mutex;               // serialises collective invocations (cuda.rs:693-703)
     int inject_failure_rank = -1;
     int comm_generation = 0;
+    // Rank 0's flat [loss, gradients...] buffer as the last step left it, read back inside the step
+    // (the reference's execute_replicas returns host outputs, cuda.rs:741-749).
+    std::vector<char> host_outputs;
+    bool host_outputs_valid = false;
 };
 
 namespace {
@@ -157,50 +162,78 @@ static qb200_status optimizer_apply_typed(void* p, const void* g, void* m, void*
 
 template <typename T>
 static qb200_status weight_gradient_typed(const void* acts, const void* cots, int64_t rows, int d_in, int d_out,
-                                          void* grad, cudaStream_t stream) {
+                                          void* grad, void* scratch, cudaStream_t stream) {
     const int slices = (int)((rows + qb::WGRAD_ROWS_PER_SLICE - 1) / qb::WGRAD_ROWS_PER_SLICE);
     const size_t count = (size_t)d_in * d_out;
-    void* scratch = nullptr;
-    QB_CUDA(cudaMallocAsync(&scratch, ((size_t)slices * count + 4) * sizeof(T), stream));
+    cudaError_t e;
     if (std::is_same<T, float>::value && qb::tc_enabled() && qb::tc_wgrad_ok(d_in, d_out)) {
         // Tensor-core contraction (tcgen05, 3xTF32); same slices, same reduction.
-        int* flag = reinterpret_cast<int*>(static_cast<float*>(scratch) + (size_t)slices * count);
-        cudaMemsetAsync(flag, 0, sizeof(int), stream);
-        cudaError_t e = (qb::tc_generation() == 2 ? qb::tc2_wgrad_launch : qb::tc_wgrad_launch)(
-            static_cast<const float*>(acts), d_in, static_cast<const float*>(cots), d_out, static_cast<float*>(scratch),
-            (int)rows, d_in, d_out, qb::WGRAD_ROWS_PER_SLICE, flag, stream);
-        if (e == cudaSuccess) {
-            qb::reduce_partials_kernel<T><<<((int)count + 255) / 256, 256, 0, stream>>>(
-                static_cast<const T*>(scratch), static_cast<T*>(grad), (int)count, slices);
-            e = cudaGetLastError();
-        }
-        cudaFreeAsync(scratch, stream);
-        if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "weight gradient launch failed: %s", cudaGetErrorString(e));
-        return QB200_OK;
+        const size_t flag_offset = ((size_t)slices * count * sizeof(T) + 15) / 16 * 16;
+        int* flag = reinterpret_cast<int*>(static_cast<char*>(scratch) + flag_offset);
+        e = cudaMemsetAsync(flag, 0, sizeof(int), stream);
+        if (e == cudaSuccess)
+            e = (qb::tc_generation() == 2 ? qb::tc2_wgrad_launch : qb::tc_wgrad_launch)(
+                static_cast<const float*>(acts), d_in, static_cast<const float*>(cots), d_out,
+                static_cast<float*>(scratch), (int)rows, d_in, d_out, qb::WGRAD_ROWS_PER_SLICE, flag, stream);
+    } else {
+        qb::GemmArgs<T> g;
+        g.A = static_cast<const T*>(acts);
+        g.B = static_cast<const T*>(cots);
+        g.C = static_cast<T*>(scratch);
+        g.bias = nullptr;
+        g.sam = 1;
+        g.sak = d_in;
+        g.sbk = d_out;
+        g.sbn = 1;
+        g.M = d_in;
+        g.N = d_out;
+        g.K = (int)rows;
+        g.ldc = d_out;
+        g.bias_rows = 0;
+        g.k_chunk = qb::WGRAD_ROWS_PER_SLICE;
+        e = qb::gemm_launch<T, false, true>(g, slices, stream);  // FP64 tensor-core kernel for eligible float64 shapes
+        if (e == cudaSuccess) e = cudaGetLastError();
     }
-    qb::GemmArgs<T> g;
-    g.A = static_cast<const T*>(acts);
-    g.B = static_cast<const T*>(cots);
-    g.C = static_cast<T*>(scratch);
-    g.bias = nullptr;
-    g.sam = 1;
-    g.sak = d_in;
-    g.sbk = d_out;
-    g.sbn = 1;
-    g.M = d_in;
-    g.N = d_out;
-    g.K = (int)rows;
-    g.ldc = d_out;
-    g.bias_rows = 0;
-    g.k_chunk = qb::WGRAD_ROWS_PER_SLICE;
-    qb::gemm_launch<T, false, true>(g, slices, stream);  // FP64 tensor-core kernel for eligible float64 shapes
+    // A failed contraction leaves the scratch as it was: the reduction must not run on it.
+    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "weight gradient launch failed: %s", cudaGetErrorString(e));
+    // Every slice writes all d_in * d_out entries of its partial and the reduction reads exactly the
+    // slices of this call, so nothing in the scratch has to start at zero.
     qb::reduce_partials_kernel<T><<<((int)count + 255) / 256, 256, 0, stream>>>(static_cast<const T*>(scratch),
                                                                                static_cast<T*>(grad), (int)count, slices);
-    cudaError_t e = cudaGetLastError();
-    cudaFreeAsync(scratch, stream);
-    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "weight gradient launch failed: %s", cudaGetErrorString(e));
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "weight gradient reduction launch failed: %s", cudaGetErrorString(e));
     return QB200_OK;
 }
+
+namespace qb {
+
+size_t weight_gradient_scratch_bytes(int dtype, int64_t rows, int d_in, int d_out) {
+    const size_t element = dtype == QB200_F32 ? sizeof(float) : sizeof(double);
+    const size_t slices = (size_t)((rows + WGRAD_ROWS_PER_SLICE - 1) / WGRAD_ROWS_PER_SLICE);
+    return (slices * (size_t)d_in * (size_t)d_out * element + 15) / 16 * 16 + 16;
+}
+
+qb200_status weight_gradient_check(const char* who, int dtype, const void* acts, const void* cots, const void* grad,
+                                   int64_t rows, int d_in, int d_out) {
+    if (acts == nullptr || cots == nullptr || grad == nullptr) return fail(QB200_INVALID, "%s needs three device arrays", who);
+    if (dtype != QB200_F32 && dtype != QB200_F64) return fail(QB200_INVALID, "unknown dtype %d", dtype);
+    if (rows < 1 || rows > (int64_t)1 << 30 || d_in < 1 || d_out < 1 || d_in > 65536 || d_out > 65536)
+        return fail(QB200_INVALID, "%s: rows %lld, d_in %d, d_out %d out of range", who, (long long)rows, d_in, d_out);
+    if ((rows + WGRAD_ROWS_PER_SLICE - 1) / WGRAD_ROWS_PER_SLICE > WGRAD_MAX_SLICES)
+        return fail(QB200_TOO_LARGE, "%s: %lld rows exceed the %lld rows one call can split (%lld slices of %d rows); "
+                                     "call once per block of rows and add the results",
+                    who, (long long)rows, (long long)(WGRAD_MAX_SLICES * WGRAD_ROWS_PER_SLICE),
+                    (long long)WGRAD_MAX_SLICES, WGRAD_ROWS_PER_SLICE);
+    return QB200_OK;
+}
+
+qb200_status weight_gradient_into(int dtype, const void* acts, const void* cots, int64_t rows, int d_in, int d_out,
+                                  void* grad, void* scratch, cudaStream_t stream) {
+    if (dtype == QB200_F32) return weight_gradient_typed<float>(acts, cots, rows, d_in, d_out, grad, scratch, stream);
+    return weight_gradient_typed<double>(acts, cots, rows, d_in, d_out, grad, scratch, stream);
+}
+
+}  // namespace qb
 
 extern "C" {
 
@@ -391,6 +424,16 @@ qb200_status qb200_plan_synchronize(qb200_plan* plan) {
     return plan->synchronize();
 }
 
+qb200_status qb200_plan_set_option(qb200_plan* plan, int32_t key, int64_t value) {
+    QB_PLAN(plan);
+    return plan->set_option(key, value);
+}
+
+qb200_status qb200_plan_inject_wait_timeout(qb200_plan* plan) {
+    QB_PLAN(plan);
+    return plan->inject_wait_timeout();
+}
+
 qb200_status qb200_nccl_unique_id(void* out_128_bytes) {
     if (out_128_bytes == nullptr) return fail(QB200_INVALID, "unique_id needs a 128-byte buffer");
     const qb::NcclApi* api = qb::nccl_api();
@@ -482,6 +525,7 @@ qb200_status qb200_dp_step(qb200_dp* dp, int32_t reduction, qb200_dp_timing* tim
         dp_drop_comms(dp);
         return fail(code, "%s; the communicators were aborted, the next call recreates them", message.c_str());
     };
+    dp->host_outputs_valid = false;
     auto t0 = std::chrono::steady_clock::now();
     const double scale = reduction == QB200_REDUCE_MEAN ? 1.0 / (double)n : 1.0;
     for (size_t r = 0; r < n; ++r) {
@@ -516,17 +560,40 @@ qb200_status qb200_dp_step(qb200_dp* dp, int32_t reduction, qb200_dp_timing* tim
         st = r->synchronize();
         if (st != QB200_OK) return failed(st);
     }
+    const double collective = seconds_since(t0);
+    t0 = std::chrono::steady_clock::now();
+    {
+        qb200_plan* p = dp->replicas[0].get();
+        const size_t bytes = p->flat_count() * p->element_bytes();
+        dp->host_outputs.resize(bytes);
+        cudaError_t e = cudaSetDevice(p->device());
+        if (e == cudaSuccess) e = cudaMemcpyAsync(dp->host_outputs.data(), p->flat_device_ptr(), bytes, cudaMemcpyDeviceToHost, p->stream());
+        if (e == cudaSuccess) e = cudaStreamSynchronize(p->stream());
+        if (e != cudaSuccess) {
+            qb::set_error("reading rank 0's outputs failed: %s", cudaGetErrorString(e));
+            return failed(QB200_CUDA_ERROR);
+        }
+        dp->host_outputs_valid = true;
+    }
     if (timing != nullptr) {
         timing->replica_enqueue = enqueue;
-        timing->collective = seconds_since(t0);
-        timing->output_readback = 0.0;
+        timing->collective = collective;
+        timing->output_readback = seconds_since(t0);
     }
     return QB200_OK;
 }
 
 qb200_status qb200_dp_read_output(qb200_dp* dp, int32_t index, void* host, size_t nbytes) {
     if (dp == nullptr || host == nullptr) return fail(QB200_INVALID, "dp_read_output needs a plan and a buffer");
-    return dp->replicas[0]->read_output(index, host, nbytes);
+    std::lock_guard<std::mutex> lock(dp->mutex);
+    if (!dp->host_outputs_valid) return dp->replicas[0]->read_output(index, host, nbytes);  // reports "before execute"
+    qb200_plan* p = dp->replicas[0].get();
+    size_t offset = 0, count = 0;
+    QB_TRY(p->output_span(index, &offset, &count));
+    const size_t element = p->element_bytes();
+    if (nbytes != count * element) return fail(QB200_INVALID, "output %d has %zu bytes, got a buffer of %zu", index, count * element, nbytes);
+    memcpy(host, dp->host_outputs.data() + offset * element, nbytes);
+    return QB200_OK;
 }
 
 qb200_status qb200_dp_optimizer_step(qb200_dp* dp, const qb200_opt_config* config) {
@@ -568,13 +635,13 @@ qb200_status qb200_optimizer_apply(int32_t dtype, void* d_param, const void* d_g
 
 qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void* d_cots, int64_t rows, int32_t d_in,
                                    int32_t d_out, void* d_grad, void* cuda_stream) {
-    if (d_acts == nullptr || d_cots == nullptr || d_grad == nullptr) return fail(QB200_INVALID, "weight_gradient needs three device arrays");
-    if (rows < 1 || rows > (int64_t)1 << 30 || d_in < 1 || d_out < 1 || d_in > 65536 || d_out > 65536)
-        return fail(QB200_INVALID, "weight_gradient: rows %lld, d_in %d, d_out %d out of range", (long long)rows, d_in, d_out);
+    QB_TRY(qb::weight_gradient_check("weight_gradient", dtype, d_acts, d_cots, d_grad, rows, d_in, d_out));
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    if (dtype == QB200_F32) return weight_gradient_typed<float>(d_acts, d_cots, rows, d_in, d_out, d_grad, s);
-    if (dtype == QB200_F64) return weight_gradient_typed<double>(d_acts, d_cots, rows, d_in, d_out, d_grad, s);
-    return fail(QB200_INVALID, "unknown dtype %d", dtype);
+    void* scratch = nullptr;
+    QB_CUDA(cudaMallocAsync(&scratch, qb::weight_gradient_scratch_bytes(dtype, rows, d_in, d_out), s));
+    const qb200_status status = qb::weight_gradient_into(dtype, d_acts, d_cots, rows, d_in, d_out, d_grad, scratch, s);
+    cudaFreeAsync(scratch, s);
+    return status;
 }
 
 qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d_bias, void* d_c, int64_t M,

@@ -124,6 +124,23 @@ cudaError_t fused_prep_launch(const float* params, const int* w_off, int hidden_
     return cudaGetLastError();
 }
 
+// One thread waits, with a short poll limit, on a barrier that nothing ever completes: the wait
+// gives up and raises *error exactly as a staged copy that never lands would.  Used by the host to
+// exercise the error path of a plan without any faulting or endless kernel.
+__global__ void unarmed_wait_kernel(int* error) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait_limited(&bar, 0u, error, 64);
+    }
+}
+
+cudaError_t unarmed_wait_launch(int* error, cudaStream_t stream) {
+    unarmed_wait_kernel<<<1, 32, 0, stream>>>(error);
+    return cudaGetLastError();
+}
+
 template cudaError_t fused_launch<float>(const FusedEntry<float>&, int, cudaStream_t, const FusedArgs<float>&);
 template cudaError_t fused_launch<double>(const FusedEntry<double>&, int, cudaStream_t, const FusedArgs<double>&);
 

@@ -42,5 +42,7 @@ size_t fused_weight_image_bytes(int hidden_to_hidden);
 // Writes the images from the flat float32 parameters; w_off[i] is the offset of network layer 1 + i.
 cudaError_t fused_prep_launch(const float* params, const int* w_off, int hidden_to_hidden, void* images,
                               cudaStream_t stream);
+// One thread's bounded wait on a barrier that is never completed: raises *error when it gives up.
+cudaError_t unarmed_wait_launch(int* error, cudaStream_t stream);
 
 }  // namespace qb

@@ -83,9 +83,9 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 }
 // Waits for phase `parity` of `bar`; gives up after a bounded number of polls and
 // reports through *error (the kernel then finishes with wrong numbers, flagged).
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* error) {
+__device__ __forceinline__ void mbar_wait_limited(uint64_t* bar, uint32_t parity, int* error, int limit) {
     uint32_t done = 0;
-    for (int spin = 0; spin < (1 << 22) && !done; ++spin) {
+    for (int spin = 0; spin < limit && !done; ++spin) {
         asm volatile(
             "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
             : "=r"(done)
@@ -93,6 +93,9 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* e
             : "memory");
     }
     if (!done) *error = 1;
+}
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* error) {
+    mbar_wait_limited(bar, parity, error, 1 << 22);
 }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");

@@ -5,6 +5,7 @@
 #include <cmath>
 #include <cstring>
 #include <limits>
+#include <mutex>
 
 #include "fused.h"
 #include "fused_kernel.cuh"
@@ -155,14 +156,24 @@ class Plan final : public qb200_plan {
     qb200_status synchronize() override;
     qb200_status attach_comm(const void* id, int rank, int world, int reduction) override;
     qb200_status detach_comm() override;
+    qb200_status set_option(int key, int64_t value) override;
+    qb200_status inject_wait_timeout() override;
 
     void* flat_device_ptr() override { return d_flat_; }
-    size_t flat_count() const override { return 1 + n_params_; }
+    // [loss, gradients..., flag]: the last element carries the device error flag through the all-reduce.
+    size_t flat_count() const override { return 2 + n_params_; }
     cudaStream_t stream() const override { return stream_; }
     void set_dp_scale(double inv_world) override { dp_scale_ = inv_world; }
     int device() const override { return device_; }
     int dtype() const override { return DTypeOf<T>::value; }
     int64_t input_shard_bytes(const char* name) const override;
+    qb200_status output_span(int index, size_t* offset, size_t* count) const override {
+        if (index < 0 || index > (int)leaves_.size()) return fail(QB200_INVALID, "output index %d of %zu", index, leaves_.size() + 1);
+        *offset = index == 0 ? 0 : 1 + leaves_[index - 1].offset;
+        *count = index == 0 ? 1 : leaves_[index - 1].count;
+        return QB200_OK;
+    }
+    size_t element_bytes() const override { return sizeof(T); }
 
   private:
     struct Leaf {
@@ -215,6 +226,36 @@ class Plan final : public qb200_plan {
     bool tc_wgrad(int layer, const T* H, const T* G, long long rows, int rows_per_slice, qb200_status* st);
     qb200_status check_device_error();
     bool choose_fused();
+    bool tc_fwd_ok(int layer) const { return !tc_fwd_.empty() && tc_fwd_[layer]; }
+    bool tc_wgrad_ok_layer(int layer) const { return !tc_wgrad_.empty() && tc_wgrad_[layer]; }
+    StepStatus<T> step_status(bool with_flat_flag) const {
+        StepStatus<T> s;
+        s.error = d_error_;
+        s.flat_flag = with_flat_flag ? d_flat_ + 1 + n_params_ : nullptr;
+        s.host_status = d_status_;
+        return s;
+    }
+    // Device time of the tensor-core GEMM launches (option QB200_OPT_KERNEL_TIMERS): an event pair
+    // around each one, summed by query().
+    void timer_begin(double flops) {
+        if (!timers_) return;
+        if (timer_events_.size() < 2 * (timer_used_ + 1)) {
+            cudaEvent_t a = nullptr, b = nullptr;
+            if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
+                timers_ = false;
+                return;
+            }
+            timer_events_.push_back(a);
+            timer_events_.push_back(b);
+        }
+        cudaEventRecord(timer_events_[2 * timer_used_], stream_);
+        timer_flops_ += flops;
+    }
+    void timer_end() {
+        if (!timers_) return;
+        cudaEventRecord(timer_events_[2 * timer_used_ + 1], stream_);
+        ++timer_used_;
+    }
     qb200_status launched(const char* what) {
         ++launches_;
         cudaError_t e = cudaGetLastError();
@@ -267,6 +308,14 @@ class Plan final : public qb200_plan {
     T* fused_grad_ = nullptr;
     void* fused_images_ = nullptr;   // tensor-core variant: pre-split weight images
     int* d_error_ = nullptr;         // device flag set by a bounded wait that gave up
+    int* h_status_ = nullptr;        // mapped host words: [0] a wait gave up, [1] an optimizer update was skipped
+    int* d_status_ = nullptr;        // the same words as the device sees them
+    std::recursive_mutex mutex_;     // one caller at a time, as the reference's per-plan state mutex (cuda.rs:86)
+    bool timers_ = false;
+    std::vector<cudaEvent_t> timer_events_;
+    size_t timer_used_ = 0;
+    double timer_flops_ = 0.0;
+
     bool fused_tensor_core_ = false;
     // layer-wise engine, float32: tcgen05 GEMMs for the layers whose shapes allow it
     std::vector<uint32_t*> tc_image_;   // per layer: pre-split weight images (null: not eligible)
@@ -311,6 +360,10 @@ void Plan<T>::release() {
     if (stream_ != nullptr) cudaStreamSynchronize(stream_);
     for (void* p : buffers_) cudaFree(p);
     buffers_.clear();
+    if (h_status_ != nullptr) cudaFreeHost(h_status_);
+    h_status_ = d_status_ = nullptr;
+    for (cudaEvent_t e : timer_events_) cudaEventDestroy(e);
+    timer_events_.clear();
     if (ev_begin_ != nullptr) cudaEventDestroy(ev_begin_);
     if (ev_end_ != nullptr) cudaEventDestroy(ev_end_);
     if (ev_ar0_ != nullptr) cudaEventDestroy(ev_ar0_);
@@ -358,14 +411,23 @@ qb200_status Plan<T>::init() {
     }
     n_params_ = offset;
     QB_TRY(dev_alloc(&d_params_, n_params_));
-    QB_TRY(dev_alloc(&d_flat_, 1 + n_params_));
+    QB_TRY(dev_alloc(&d_flat_, 2 + n_params_));
     QB_TRY(dev_alloc(&d_acc_, n_params_));
     QB_TRY(dev_alloc(&d_ct_, 1));
     QB_TRY(dev_alloc(&d_loss_only_, 1));
     QB_TRY(dev_alloc(&d_clip_, 3));
     QB_TRY(dev_alloc(&d_error_, 1));
     QB_CUDA(cudaMemsetAsync(d_error_, 0, sizeof(int), stream_));
-    QB_CUDA(cudaMemsetAsync(d_flat_, 0, (1 + n_params_) * sizeof(T), stream_));
+    QB_CUDA(cudaMemsetAsync(d_flat_, 0, (2 + n_params_) * sizeof(T), stream_));
+    {
+        void* raw = nullptr;
+        QB_CUDA(cudaHostAlloc(&raw, 2 * sizeof(int), cudaHostAllocMapped));
+        h_status_ = static_cast<int*>(raw);
+        h_status_[0] = h_status_[1] = 0;
+        void* mapped = nullptr;
+        QB_CUDA(cudaHostGetDevicePointer(&mapped, raw, 0));
+        d_status_ = static_cast<int*>(mapped);
+    }
     QB_CUDA(cudaMemsetAsync(d_params_, 0, n_params_ * sizeof(T), stream_));
     QB_CUDA(cudaMemsetAsync(d_clip_, 0, 3 * sizeof(double), stream_));
     const T one = T(1);
@@ -544,6 +606,7 @@ int64_t Plan<T>::input_shard_bytes(const char* name) const {
 template <typename T>
 qb200_status Plan<T>::bind(const char* name, const void* host, size_t nbytes) {
     if (name == nullptr || host == nullptr) return fail(QB200_INVALID, "bind needs a name and a host buffer");
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     QB_TRY(use_device());
     const std::string key(name);
     if (key == kCotangentName) {
@@ -698,19 +761,22 @@ qb200_status Plan<float>::prepare_weight_images() {
     return QB200_OK;
 }
 
-// Reads the device flag that a bounded wait sets when it gives up; called after a stream
-// synchronisation.
+// Called after a stream synchronisation: the mapped host words say whether a bounded wait gave up
+// during a step (locally: word 0) or an optimizer update was left out because some rank's did
+// (word 1).  Reports once and clears, so that the next step starts clean.
 template <typename T>
 qb200_status Plan<T>::check_device_error() {
-    int flag = 0;
-    QB_CUDA(cudaMemcpyAsync(&flag, d_error_, sizeof(int), cudaMemcpyDeviceToHost, stream_));
+    if (h_status_ == nullptr) return QB200_OK;
+    const int gave_up = h_status_[0], skipped = h_status_[1];
+    if (gave_up == 0 && skipped == 0) return QB200_OK;
+    h_status_[0] = h_status_[1] = 0;
+    QB_CUDA(cudaMemsetAsync(d_error_, 0, sizeof(int), stream_));
     QB_CUDA(cudaStreamSynchronize(stream_));
-    if (flag != 0) {
-        QB_CUDA(cudaMemsetAsync(d_error_, 0, sizeof(int), stream_));
-        return fail(QB200_CUDA_ERROR, "a staged copy inside the fused kernel did not complete within its wait limit; "
-                                      "the results of that step are invalid");
-    }
-    return QB200_OK;
+    if (gave_up != 0)
+        return fail(QB200_CUDA_ERROR, "a staged copy inside a kernel did not complete within its wait limit; the results "
+                                      "of that step are invalid%s", skipped ? " and its optimizer update was skipped" : "");
+    return fail(QB200_CUDA_ERROR, "another rank's step was invalid (a bounded wait gave up there); the optimizer update "
+                                  "of that step was skipped on every rank");
 }
 
 template <typename T>
@@ -866,8 +932,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         g.bias_rows = C;
         g.k_chunk = g.K;
         qb200_status tc_status = QB200_OK;
+        const bool narrow = g.K <= 4 && g.N % 4 == 0 && g.N >= 32 && 256 % (g.N / 4) == 0;
+        if (tc_fwd_ok(l - 1) || !narrow) timer_begin(2.0 * (double)rows * g.N * g.K);
         if (tc_forward(l - 1, H_[l - 1], Z_[l], rows, C, &tc_status)) {
             QB_TRY(tc_status);
+            timer_end();
         } else if (g.K <= 4 && g.N % 4 == 0 && g.N >= 32 && 256 % (g.N / 4) == 0) {
             // Narrow contraction (the first layer): stream the output once.
             const int rows_per_block = 256 / (g.N / 4);
@@ -883,6 +952,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             const cudaError_t e = gemm_launch<T, true, true>(g, 1, stream_);
             (void)e;  // launched() reads the launch status
             QB_TRY(launched("gemm_kernel(forward)"));
+            timer_end();
         }
         const long long plane = (long long)C * sz[l];
         if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], nullptr))
@@ -907,8 +977,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             // Output tiles of the tensor-core kernel: 128 rows of dW by all (first generation) or 128/64 columns.
             const int tc_col_tiles = tc_generation() == 2 ? d_out / (d_out % 128 == 0 ? 128 : 64) : 1;
             const int tc_chunk = slice_rows(rows, std::max(1, d_in / 128) * std::max(1, tc_col_tiles), 32);
+            const bool tc_takes = layer >= 0 && layer < L_ && tc_wgrad_ok_layer(layer);
+            if (tc_takes) timer_begin(2.0 * (double)rows * d_in * d_out);
             if (tc_wgrad(layer, Hprev, Gz, rows, tc_chunk, &tc_status)) {
                 QB_TRY(tc_status);
+                timer_end();
                 const int count = d_in * d_out;
                 const int slices = (int)((rows + tc_chunk - 1) / tc_chunk);
                 accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset, count, slices, stream_);
@@ -957,9 +1030,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         const bool fp64_tensor = sizeof(T) == 8 && d_in >= 32 && d_out >= 32;  // the kernel gemm_launch will pick
         g.k_chunk = slice_rows(rows, gemm_output_tiles(d_in, d_out, fp64_tensor), GEMM_BK);
         const int slices = (int)((rows + g.k_chunk - 1) / g.k_chunk);
+        timer_begin(2.0 * (double)rows * d_in * d_out);
         const cudaError_t e = gemm_launch<T, false, true>(g, slices, stream_);
         (void)e;
         QB_TRY(launched("gemm_kernel(wgrad)"));
+        timer_end();
         const int count = d_in * d_out;
         accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset,
                                                                                 count, slices, stream_);
@@ -1035,6 +1110,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             g.bias_rows = 0;
             g.k_chunk = g.K;
             qb200_status tc_status = QB200_OK;
+            timer_begin(2.0 * (double)rows * g.N * g.K);
             if (tc_dgrad(l - 1, G_[cur], G_[cur ^ 1], rows, &tc_status)) {
                 QB_TRY(tc_status);
             } else {
@@ -1042,6 +1118,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                 (void)e;
                 QB_TRY(launched("gemm_kernel(dgrad)"));
             }
+            timer_end();
             cur ^= 1;
         }
     }
@@ -1053,6 +1130,10 @@ qb200_status Plan<T>::run(bool forward_only) {
     QB_TRY(use_device());
     QB_TRY(check_bound());
     QB_TRY(refresh_tables());
+    if (!forward_only) {
+        timer_used_ = 0;
+        timer_flops_ = 0.0;
+    }
     if (!forward_only && !fused_) QB_CUDA(cudaMemsetAsync(d_acc_, 0, n_params_ * sizeof(double), stream_));
     if (fused_ && fused_tensor_core_) QB_TRY(prepare_weight_images());
     const bool side = fused_ && side_stream_ != nullptr;
@@ -1101,12 +1182,14 @@ qb200_status Plan<T>::run(bool forward_only) {
     if (fused_ && !forward_only) {
         const int P = (int)n_params_;
         fused_finalize_kernel<T><<<(P + 31) / 32 + 1, 256, 0, stream_>>>(fused_grad_, P, (int)fused_rows_, d_flat_ + 1,
-                                                                       d_partials_, la, (T)dp_scale_, loss_out);
+                                                                       d_partials_, la, (T)dp_scale_, loss_out,
+                                                                       step_status(true));
         QB_TRY(launched("fused_finalize_kernel"));
         executed_ = true;
         return QB200_OK;
     }
-    loss_finalize_kernel<T><<<1, 256, 0, stream_>>>(d_partials_, la, forward_only ? T(1) : (T)dp_scale_, loss_out);
+    loss_finalize_kernel<T><<<1, 256, 0, stream_>>>(d_partials_, la, forward_only ? T(1) : (T)dp_scale_, loss_out,
+                                                    step_status(!forward_only));
     QB_TRY(launched("loss_finalize_kernel"));
     if (!forward_only) {
         finalize_gradients_kernel<T><<<((int)n_params_ + 255) / 256, 256, 0, stream_>>>(d_acc_, d_flat_ + 1, (int)n_params_);
@@ -1118,16 +1201,18 @@ qb200_status Plan<T>::run(bool forward_only) {
 
 template <typename T>
 qb200_status Plan<T>::execute_local() {
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     return run(false);
 }
 
 template <typename T>
 qb200_status Plan<T>::all_reduce() {
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     if (comm_ == nullptr) return QB200_OK;
     const NcclApi* api = nccl_api();
     if (api == nullptr) return QB200_NCCL_ERROR;
     cudaEventRecord(ev_ar0_, stream_);
-    ncclResult_t r = api->AllReduce(d_flat_, d_flat_, 1 + n_params_, DTypeOf<T>::nccl, ncclSum, comm_, stream_);
+    ncclResult_t r = api->AllReduce(d_flat_, d_flat_, 2 + n_params_, DTypeOf<T>::nccl, ncclSum, comm_, stream_);
     cudaEventRecord(ev_ar1_, stream_);
     ev_ar_valid_ = r == ncclSuccess;
     if (r != ncclSuccess) {
@@ -1143,6 +1228,7 @@ qb200_status Plan<T>::all_reduce() {
 
 template <typename T>
 qb200_status Plan<T>::read_output(int index, void* host, size_t nbytes) {
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     QB_TRY(use_device());
     if (!executed_) return fail(QB200_INVALID, "read_output before execute");
     if (index < 0 || index > (int)leaves_.size()) return fail(QB200_INVALID, "output index %d of %zu", index, leaves_.size() + 1);
@@ -1151,13 +1237,13 @@ qb200_status Plan<T>::read_output(int index, void* host, size_t nbytes) {
     if (nbytes != count * sizeof(T)) return fail(QB200_INVALID, "output %d has %zu bytes, got a buffer of %zu", index, count * sizeof(T), nbytes);
     QB_CUDA(cudaMemcpyAsync(host, d_flat_ + offset, nbytes, cudaMemcpyDeviceToHost, stream_));
     QB_CUDA(cudaStreamSynchronize(stream_));
-    if (index == 0 && (fused_tensor_core_ || tc_any_)) QB_TRY(check_device_error());
-    return QB200_OK;
+    return check_device_error();
 }
 
 template <typename T>
 qb200_status Plan<T>::optimizer_step(const qb200_opt_config* c) {
     QB_TRY(validate_opt_config(c));  // before any device work (cuda_optimizer.rs:207-212)
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     QB_TRY(use_device());
     if (!executed_) return fail(QB200_INVALID, "optimizer_step before execute: there are no gradients");
     if (!moments_ready_ && c->rule == QB200_ADAM) {
@@ -1167,16 +1253,20 @@ qb200_status Plan<T>::optimizer_step(const qb200_opt_config* c) {
         QB_CUDA(cudaMemsetAsync(d_v_, 0, n_params_ * sizeof(T), stream_));
         moments_ready_ = true;
     }
+    // The flag slot behind the gradients: non-zero after the all-reduce when any rank's step raised the
+    // device error flag; the kernels below then leave parameters and moments as they are.
+    const T* skip = d_flat_ + 1 + n_params_;
     const double* clip = nullptr;
     if (c->has_clip) {
-        global_norm_kernel<T><<<1, 1024, 0, stream_>>>(d_flat_ + 1, (long long)n_params_, c->clip_norm, d_clip_);
+        global_norm_kernel<T><<<1, 1024, 0, stream_>>>(d_flat_ + 1, (long long)n_params_, c->clip_norm, d_clip_, skip);
         QB_TRY(launched("global_norm_kernel"));
         clip = d_clip_;
     }
     ++steps_;
     const int grid = grid_for((long long)n_params_, 256);
     if (c->rule == QB200_SGD) {
-        sgd_kernel<T><<<grid, 256, 0, stream_>>>(d_params_, d_flat_ + 1, (T)c->learning_rate, clip, (long long)n_params_);
+        sgd_kernel<T><<<grid, 256, 0, stream_>>>(d_params_, d_flat_ + 1, (T)c->learning_rate, clip, (long long)n_params_,
+                                                 skip, d_status_);
         return launched("sgd_kernel");
     }
     // Coefficients in double, rounded once (AdamCoefficients::new(..).map(T::from_f64),
@@ -1191,22 +1281,25 @@ qb200_status Plan<T>::optimizer_step(const qb200_opt_config* c) {
     k.correction1 = (T)(1.0 - std::pow(c->beta1, (double)steps_));
     k.correction2 = (T)(1.0 - std::pow(c->beta2, (double)steps_));
     k.weight_decay = (T)c->weight_decay;
-    adam_kernel<T><<<grid, 256, 0, stream_>>>(d_params_, d_flat_ + 1, d_m_, d_v_, k, clip, (long long)n_params_);
+    adam_kernel<T><<<grid, 256, 0, stream_>>>(d_params_, d_flat_ + 1, d_m_, d_v_, k, clip, (long long)n_params_, skip,
+                                              d_status_);
     return launched("adam_kernel");
 }
 
 template <typename T>
 qb200_status Plan<T>::loss(void* host_scalar) {
     if (host_scalar == nullptr) return fail(QB200_INVALID, "loss needs a host scalar");
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     QB_TRY(run(true));
     QB_CUDA(cudaMemcpyAsync(host_scalar, d_loss_only_, sizeof(T), cudaMemcpyDeviceToHost, stream_));
     QB_CUDA(cudaStreamSynchronize(stream_));
-    return QB200_OK;
+    return check_device_error();
 }
 
 template <typename T>
 qb200_status Plan<T>::read_input(const char* name, void* host, size_t nbytes) {
     if (name == nullptr || host == nullptr) return fail(QB200_INVALID, "read_input needs a name and a host buffer");
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     QB_TRY(use_device());
     const std::string key(name);
     const T* src = nullptr;
@@ -1231,7 +1324,7 @@ qb200_status Plan<T>::read_input(const char* name, void* host, size_t nbytes) {
     if (nbytes != count * sizeof(T)) return fail(QB200_INVALID, "input '%s' has %zu bytes, got a buffer of %zu", name, count * sizeof(T), nbytes);
     QB_CUDA(cudaMemcpyAsync(host, src, nbytes, cudaMemcpyDeviceToHost, stream_));
     QB_CUDA(cudaStreamSynchronize(stream_));
-    return QB200_OK;
+    return check_device_error();
 }
 
 template <typename T>
@@ -1299,6 +1392,24 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
             *out = (int64_t)((double)ms * 1e6);
             return QB200_OK;
         }
+        case QB200_Q_GEMM_NANOSECONDS: {
+            if (timer_used_ == 0) {
+                *out = 0;
+                return QB200_OK;
+            }
+            QB_TRY(use_device());
+            QB_CUDA(cudaEventSynchronize(timer_events_[2 * timer_used_ - 1]));
+            double total_ms = 0.0;
+            for (size_t i = 0; i < timer_used_; ++i) {
+                float ms = 0.0f;
+                QB_CUDA(cudaEventElapsedTime(&ms, timer_events_[2 * i], timer_events_[2 * i + 1]));
+                total_ms += ms;
+            }
+            *out = (int64_t)(total_ms * 1e6);
+            return QB200_OK;
+        }
+        case QB200_Q_GEMM_LAUNCHES: *out = (int64_t)timer_used_; return QB200_OK;
+        case QB200_Q_GEMM_FLOPS: *out = (int64_t)timer_flops_; return QB200_OK;
         case QB200_Q_SET0_NANOSECONDS: {
             if (!ev_valid_) return fail(QB200_INVALID, "no execute has run yet");
             QB_TRY(use_device());
@@ -1314,8 +1425,28 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
 
 template <typename T>
 qb200_status Plan<T>::synchronize() {
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
     QB_TRY(use_device());
     QB_CUDA(cudaStreamSynchronize(stream_));
+    return check_device_error();
+}
+
+template <typename T>
+qb200_status Plan<T>::set_option(int key, int64_t value) {
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
+    switch (key) {
+        case QB200_OPT_KERNEL_TIMERS: timers_ = value != 0; return QB200_OK;
+        default: return fail(QB200_INVALID, "unknown option key %d", key);
+    }
+}
+
+template <typename T>
+qb200_status Plan<T>::inject_wait_timeout() {
+    std::lock_guard<std::recursive_mutex> lock(mutex_);
+    QB_TRY(use_device());
+    const cudaError_t e = unarmed_wait_launch(d_error_, stream_);
+    ++launches_;
+    if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of unarmed_wait_kernel failed: %s", cudaGetErrorString(e));
     return QB200_OK;
 }
 
@@ -1347,7 +1478,9 @@ qb200_status Plan<T>::detach_comm() {
     if (api != nullptr) {
         use_device();
         cudaStreamSynchronize(stream_);
-        api->CommAbort(comm_);
+        // A clean detach destroys the communicator; a failed all-reduce has aborted and dropped it
+        // already (all_reduce above; cuda.rs:132-145).
+        api->CommDestroy(comm_);
     }
     comm_ = nullptr;
     world_ = 1;

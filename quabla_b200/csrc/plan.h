@@ -25,6 +25,8 @@ struct qb200_plan {
     virtual qb200_status synchronize() = 0;
     virtual qb200_status attach_comm(const void* id, int rank, int world, int reduction) = 0;
     virtual qb200_status detach_comm() = 0;
+    virtual qb200_status set_option(int key, int64_t value) = 0;
+    virtual qb200_status inject_wait_timeout() = 0;  // test seam: a bounded wait that gives up
 
     // Used by the single-process data-parallel plan.
     virtual void* flat_device_ptr() = 0;
@@ -34,6 +36,9 @@ struct qb200_plan {
     virtual int device() const = 0;
     virtual int dtype() const = 0;
     virtual int64_t input_shard_bytes(const char* name) const = 0;  // -1 when unknown
+    // Element offset and count of output `index` (0: loss, 1..: gradients) inside the flat buffer.
+    virtual qb200_status output_span(int index, size_t* offset, size_t* count) const = 0;
+    virtual size_t element_bytes() const = 0;
 };
 
 namespace qb {

@@ -180,9 +180,25 @@ struct LossArgs {
     double weight[MAX_SETS];
 };
 // Weighted sum of the per-block loss partials of every point set, in a fixed order; whole block.
+// `step` (may be null) closes a step: the device error flag that a bounded wait raises when it gives up
+// is copied into the slot behind the gradients, so that one all-reduce tells every rank, and the
+// optimizer kernels skip an update whose gradients are not to be trusted.
+template <typename T>
+struct StepStatus {
+    const int* error;  // device flag of the plan
+    T* flat_flag;      // slot behind the gradients in the flat [loss, gradients..., flag] buffer
+    int* host_status;  // mapped host words: [0] a wait gave up, [1] an update was skipped
+};
+
 template <typename T>
 __device__ __forceinline__ void loss_finalize_block(const double* __restrict__ partials, const LossArgs& a, T extra,
-                                                    T* __restrict__ out, double* red) {
+                                                    T* __restrict__ out, double* red,
+                                                    const StepStatus<T>* step = nullptr) {
+    if (step != nullptr && threadIdx.x == 0) {
+        const int e = *step->error;
+        if (step->flat_flag != nullptr) step->flat_flag[0] = e != 0 ? T(1) : T(0);
+        if (e != 0) step->host_status[0] = 1;
+    }
     T loss = T(0);
     for (int s = 0; s < a.n_sets; ++s) {
         double v = 0.0;
@@ -196,9 +212,9 @@ __device__ __forceinline__ void loss_finalize_block(const double* __restrict__ p
 
 template <typename T>
 __global__ void __launch_bounds__(256) loss_finalize_kernel(const double* __restrict__ partials, LossArgs a, T extra,
-                                                            T* __restrict__ out) {
+                                                            T* __restrict__ out, StepStatus<T> step) {
     __shared__ double red[8];
-    loss_finalize_block<T>(partials, a, extra, out, red);
+    loss_finalize_block<T>(partials, a, extra, out, red, &step);
 }
 
 // End of a step of the fused engines, one launch: grads[i] = sum over the per-CTA gradient rows of
@@ -210,10 +226,10 @@ template <typename T>
 __global__ void __launch_bounds__(256) fused_finalize_kernel(const T* __restrict__ grad_rows, int P, int rows,
                                                              T* __restrict__ grads,
                                                              const double* __restrict__ partials, LossArgs a, T extra,
-                                                             T* __restrict__ loss_out) {
+                                                             T* __restrict__ loss_out, StepStatus<T> step) {
     __shared__ double part[8][33];
     if (blockIdx.x == gridDim.x - 1) {
-        loss_finalize_block<T>(partials, a, extra, loss_out, &part[0][0]);
+        loss_finalize_block<T>(partials, a, extra, loss_out, &part[0][0], &step);
         return;
     }
     const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
@@ -267,10 +283,21 @@ struct AdamCoeffs {
 // d = (m'/c1) / (sqrt(v'/c2) + eps); if wd != 0: d += wd*p; p' = p - d*lr.
 // clip_scalars (may be null): [peak, factor, sticky flag]; the gradient is
 // scaled in double and rounded once (cuda_optimizer.rs:150-163).
+// skip (may be null): the flag slot of the flat gradient buffer; non-zero means that some rank's
+// step raised the device error flag, and the update is left out on every rank alike.
+template <typename T>
+__device__ __forceinline__ bool update_skipped(const T* __restrict__ skip, int* __restrict__ host_status) {
+    if (skip == nullptr || skip[0] == T(0)) return false;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && host_status != nullptr) host_status[1] = 1;
+    return true;
+}
+
 template <typename T>
 __global__ void adam_kernel(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m, T* __restrict__ v,
-                            AdamCoeffs<T> k, const double* __restrict__ clip_scalars, long long count) {
+                            AdamCoeffs<T> k, const double* __restrict__ clip_scalars, long long count,
+                            const T* __restrict__ skip = nullptr, int* __restrict__ host_status = nullptr) {
     typedef Rn<T> R;
+    if (update_skipped(skip, host_status)) return;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
          i += (long long)gridDim.x * blockDim.x) {
         T grad = g[i];
@@ -290,8 +317,10 @@ __global__ void adam_kernel(T* __restrict__ p, const T* __restrict__ g, T* __res
 
 template <typename T>
 __global__ void sgd_kernel(T* __restrict__ p, const T* __restrict__ g, T learning_rate,
-                           const double* __restrict__ clip_scalars, long long count) {
+                           const double* __restrict__ clip_scalars, long long count,
+                           const T* __restrict__ skip = nullptr, int* __restrict__ host_status = nullptr) {
     typedef Rn<T> R;
+    if (update_skipped(skip, host_status)) return;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
          i += (long long)gridDim.x * blockDim.x) {
         T grad = g[i];
@@ -306,9 +335,11 @@ __global__ void sgd_kernel(T* __restrict__ p, const T* __restrict__ g, T learnin
 // One block: the flat gradient is at most a few hundred thousand elements.
 template <typename T>
 __global__ void __launch_bounds__(1024) global_norm_kernel(const T* __restrict__ g, long long count, double max_norm,
-                                                           double* __restrict__ scalars) {
+                                                           double* __restrict__ scalars,
+                                                           const T* __restrict__ skip = nullptr) {
     __shared__ double red[1024];
     __shared__ int any_nan;
+    if (skip != nullptr && skip[0] != T(0)) return;  // the update is skipped: leave the sticky flag alone
     if (threadIdx.x == 0) any_nan = 0;
     __syncthreads();
     double peak = 0.0;

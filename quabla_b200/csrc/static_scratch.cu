@@ -16,6 +16,7 @@
 
 #include "common.h"
 #include "layer_kernels.cuh"
+#include "wgrad.h"
 
 namespace {
 
@@ -47,59 +48,23 @@ qb200_status scratch_for_current_device(void** out) {
     return QB200_OK;
 }
 
-template <typename T>
-qb200_status run(const void* acts, const void* cots, int64_t rows, int d_in, int d_out, void* grad, void* scratch,
-                 cudaStream_t stream) {
-    const int slices = (int)((rows + qb::WGRAD_ROWS_PER_SLICE - 1) / qb::WGRAD_ROWS_PER_SLICE);
-    const size_t count = (size_t)d_in * d_out;
-    qb::GemmArgs<T> g;
-    g.A = static_cast<const T*>(acts);
-    g.B = static_cast<const T*>(cots);
-    g.C = static_cast<T*>(scratch);
-    g.bias = nullptr;
-    g.sam = 1;
-    g.sak = d_in;
-    g.sbk = d_out;
-    g.sbn = 1;
-    g.M = d_in;
-    g.N = d_out;
-    g.K = (int)rows;
-    g.ldc = d_out;
-    g.bias_rows = 0;
-    g.k_chunk = qb::WGRAD_ROWS_PER_SLICE;
-    dim3 grid((d_out + qb::GEMM_BN - 1) / qb::GEMM_BN, (d_in + qb::GEMM_BM - 1) / qb::GEMM_BM, slices);
-    // Every slice writes all d_in*d_out entries of its partial, and the
-    // reduction reads exactly the slices of this call, so nothing in the
-    // scratch has to start at zero and stale contents of an earlier, larger
-    // call are never read.
-    qb::gemm_kernel<T, false, true><<<grid, 256, 0, stream>>>(g);
-    qb::reduce_partials_kernel<T><<<((int)count + 255) / 256, 256, 0, stream>>>(static_cast<const T*>(scratch),
-                                                                               static_cast<T*>(grad), (int)count, slices);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return qb::fail(QB200_CUDA_ERROR, "weight gradient launch failed: %s", cudaGetErrorString(e));
-    return QB200_OK;
-}
-
 }  // namespace
 
 extern "C" qb200_status qb200_weight_gradient_static(int32_t dtype, const void* d_acts, const void* d_cots,
                                                      int64_t rows, int32_t d_in, int32_t d_out, void* d_grad,
                                                      void* cuda_stream) {
-    if (d_acts == nullptr || d_cots == nullptr || d_grad == nullptr) return qb::fail(QB200_INVALID, "weight_gradient_static needs three device arrays");
-    if (dtype != QB200_F32 && dtype != QB200_F64) return qb::fail(QB200_INVALID, "unknown dtype %d", dtype);
-    if (rows < 1 || rows > (int64_t)1 << 30 || d_in < 1 || d_out < 1 || d_in > 65536 || d_out > 65536)
-        return qb::fail(QB200_INVALID, "weight_gradient_static: rows %lld, d_in %d, d_out %d out of range", (long long)rows, d_in, d_out);
-    const size_t element = dtype == QB200_F32 ? sizeof(float) : sizeof(double);
-    const size_t slices = (size_t)((rows + qb::WGRAD_ROWS_PER_SLICE - 1) / qb::WGRAD_ROWS_PER_SLICE);
-    const size_t needed = slices * (size_t)d_in * (size_t)d_out * element;
+    QB_TRY(qb::weight_gradient_check("weight_gradient_static", dtype, d_acts, d_cots, d_grad, rows, d_in, d_out));
+    const size_t needed = qb::weight_gradient_scratch_bytes(dtype, rows, d_in, d_out);
     if (needed > kStaticScratchBytes)
         return qb::fail(QB200_TOO_LARGE,
-                        "weight_gradient_static needs %zu bytes of split scratch (ceil(rows/%d) x d_in x d_out elements) "
-                        "but the built-in array holds %zu; use qb200_weight_gradient or fewer rows per call",
+                        "weight_gradient_static needs %zu bytes of split scratch (ceil(rows/%d) x d_in x d_out elements "
+                        "and a 16-byte flag) but the built-in array holds %zu; use qb200_weight_gradient or fewer rows "
+                        "per call",
                         needed, qb::WGRAD_ROWS_PER_SLICE, kStaticScratchBytes);
     void* scratch = nullptr;
     QB_TRY(scratch_for_current_device(&scratch));
-    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    if (dtype == QB200_F32) return run<float>(d_acts, d_cots, rows, d_in, d_out, d_grad, scratch, stream);
-    return run<double>(d_acts, d_cots, rows, d_in, d_out, d_grad, scratch, stream);
+    // The same dispatch as qb200_weight_gradient (tensor cores for eligible float32 shapes, FP64 MMA or
+    // the SIMT kernel otherwise), on the built-in array instead of pool memory.
+    return qb::weight_gradient_into(dtype, d_acts, d_cots, rows, d_in, d_out, d_grad, scratch,
+                                    static_cast<cudaStream_t>(cuda_stream));
 }
