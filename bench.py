@@ -6,21 +6,30 @@ Adam step (forward, reverse pass, gradient all-reduce, optimizer update).
 Launched under `python -m torch.distributed.run` for N > 1 (one rank per GPU).
 Prints ONE JSON line on rank 0.
 
-The default workload is the 2-D Poisson configuration (float32, tanh MLP
-2-64x4-1, 65,536 interior + 4,096 boundary points per GPU).  Inputs are seeded
-synthetic points and Xavier-normal weights.  With N GPUs every rank holds its
-own 65,536 + 4,096 points (weak scaling) and the step ends with one all-reduce
-of the flat [loss, gradients] buffer.
+The default workload is the 3-D heat equation (float32, tanh MLP 4-256x6-1,
+1,048,576 collocation points in total).  With N GPUs the points are cut into N
+contiguous equal axis-0 shards in rank order, one per rank (strong scaling:
+the total is fixed), and the step ends with one all-reduce of the flat
+[loss, gradients] buffer; parameters and Adam moments are replicated.  Inputs
+are seeded synthetic points and Xavier-normal weights.
 
-  value  device-resident step: points and parameters already in HBM;
-  e2e    the same step through `optim.Trainer.step(batch)` with the batch
-         copied from pinned host memory every step and the step's loss read
-         back, both inside the timed region.
+  value    device-resident step: points and parameters already in HBM;
+  e2e      the same step through `optim.Trainer.step(batch)` with the batch
+           copied from pinned host memory every step and the step's loss read
+           back, both inside the timed region;
+  details.others   the other workloads (2-D Poisson, Burgers, beam), a few
+           steps each after the timed region, sharded the same way.
+
+With N > 1 the run first checks one step of the same workload on a few
+thousand points against the CPU oracle on the full batch (rank 0; the process
+exits non-zero when the 1e-5 / 1e-10 gate fails) and, after the timed loop,
+that every rank holds bit-identical parameters.
 """
 
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -36,6 +45,9 @@ if ROOT not in sys.path:
 
 METRIC = "collocation_points_per_second_per_adam_step"
 UNIT = "points/s"
+L2_BYTES = 126 << 20
+PARITY_POINTS = 2048  # total interior points of the multi-GPU parity step
+PARITY_TOLERANCE = {"f32": 1e-5, "f64": 1e-10}
 
 
 def parse_args():
@@ -44,10 +56,13 @@ def parse_args():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="poisson2d")
-    parser.add_argument("--points", type=int, default=None, help="interior points per GPU (default: the workload's)")
+    parser.add_argument("--workload", default="heat3d")
+    parser.add_argument("--points", type=int, default=None,
+                        help="interior points in total over all GPUs (default: the workload's)")
     parser.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the bounded CPU sample")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-others", action="store_true", help="skip the other workloads after the timed region")
+    parser.add_argument("--no-parity", action="store_true", help="skip the multi-GPU parity step")
     return parser.parse_args()
 
 
@@ -161,7 +176,17 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi, 100 ms"}
 
 
-def cpu_sample(workload_name: str, seconds: float, threads: int):
+def workload_config(name: str, total_points: int | None, world: int) -> dict:
+    """The `config` object, identical in both arms: what is computed, on how many points, cut how."""
+    from quabla_b200 import workloads
+
+    w = workloads.make(name, total_points if total_points is not None else None)
+    return {"workload": w.name, "description": w.description, "interior_points": w.interior_points,
+            "other_sets": [list(e) for e in w.extra], "parameters": w.parameter_count, "optimizer": "adam lr=1e-3",
+            "sharding": f"{world} contiguous equal axis-0 shard(s) of every point set, parameters replicated"}
+
+
+def cpu_sample(workload_name: str, seconds: float, threads: int, total_points: int | None = None):
     """Times the CPU oracle's value-and-gradient on a bounded sample of the
     workload's interior points; returns (points/s, sample description)."""
     from oracle import contracted
@@ -177,7 +202,7 @@ def cpu_sample(workload_name: str, seconds: float, threads: int):
     t0 = time.perf_counter()
     contracted.value_and_grad(traced.spec, inputs, threads=threads)
     probe = max(time.perf_counter() - t0, 1e-4)
-    full = workloads.make(workload_name).interior_points
+    full = workloads.make(workload_name, total_points).interior_points
     points = int(min(full, max(probe_points, probe_points * seconds / probe)))
     w = workloads.make(workload_name, points)
     args = (w.params, *w.data)
@@ -199,29 +224,308 @@ def run_reference(args) -> None:
     if rank != 0:
         return
     from oracle import contracted
-    from quabla_b200 import workloads
 
     threads = contracted.max_threads()
     per_step = max(1.0, min(8.0, 120.0 / max(1, args.steps + args.warmup)))
     values = []
     sample = ""
     for step in range(args.warmup + args.steps):
-        value, sample = cpu_sample(args.workload, per_step, threads)
+        value, sample = cpu_sample(args.workload, per_step, threads, args.points)
         if step >= args.warmup:
             values.append(value)
     value = float(np.median(values))
-    w = workloads.make(args.workload, 64)
-    full = workloads.make(args.workload).interior_points if args.points is None else args.points
+    config = workload_config(args.workload, args.points, args.gpus)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * full / value, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": args.workload, "description": w.description,
-                   "note": "CPU oracle port of the reference plan interpreter; optimizer update not included"},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * config["interior_points"] / value,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": config,
+        "details": {"note": "CPU oracle port of the reference plan interpreter (contracted form, float64), every "
+                            "host thread; the optimizer update is not included; each step is a bounded sample of "
+                            "the workload"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+class Rig:
+    """One rank's view of a run: device, process group, and the helpers every measured
+    workload uses (sharding, communicator attachment, event-bracketed loops)."""
+
+    def __init__(self, args) -> None:
+        import torch
+
+        self.torch = torch
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        if self.world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={self.world}: launch with torch.distributed.run")
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the qb200 backend has no CPU fallback")
+        torch.cuda.set_device(self.local_rank)
+        self.device = f"cuda:{self.local_rank}"
+        if self.world > 1:
+            torch.distributed.init_process_group("nccl", device_id=torch.device(self.device))
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.device)  # larger than the 126 MB L2
+        self.token = torch.zeros(1, device=self.device)
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            self.torch.distributed.barrier()
+        self.torch.cuda.synchronize()
+
+    def shard(self, w):
+        """This rank's rows of every point set: contiguous equal axis-0 shards in rank order
+        (python/quabla/distributed.py:101-106); sets too small to cut (two boundary points) are replicated,
+        which a mean over ranks leaves unchanged."""
+        if self.world == 1:
+            return w.data
+        out = []
+        for a in w.data:
+            rows = a.shape[0]
+            if rows >= 64 and rows % self.world == 0:
+                n = rows // self.world
+                out.append(np.ascontiguousarray(a[self.rank * n:(self.rank + 1) * n]))
+            else:
+                out.append(a)
+        return tuple(out)
+
+    def trainer(self, w, data):
+        import quabla_b200 as qb
+        from quabla_b200._plan import nccl_unique_id
+
+        optimizer = qb.optim.Adam(learning_rate=1e-3)
+        trainer = qb.optim.Trainer(w.loss, w.params, optimizer, *data, device=self.device,
+                                   batch_argnums=tuple(range(len(data))))
+        plan = trainer._executor.plan
+        if self.world > 1:
+            ids = [nccl_unique_id() if self.rank == 0 else None]
+            self.torch.distributed.broadcast_object_list(ids, src=0)
+            plan.attach_comm(ids[0], self.rank, self.world, "mean")
+        return trainer, plan
+
+    def max_over_ranks(self, values):
+        t = self.torch.tensor(values, dtype=self.torch.float64, device=self.device)
+        if self.world > 1:
+            self.torch.distributed.all_reduce(t, op=self.torch.distributed.ReduceOp.MAX)
+        return [float(v) for v in t.cpu()]
+
+    def timed_loop(self, plan, step_fn, count: int, flush_between: bool) -> float:
+        """Device milliseconds of `count` steps on the plan's stream.  Working sets larger than L2: ONE
+        bracket around all steps, back to back as a training loop runs them (rank skew and launch gaps
+        included).  Otherwise per-step brackets with 256 MB written between steps to flush L2, ranks
+        aligned before each step."""
+        from quabla_b200 import _lib
+
+        torch = self.torch
+        stream = torch.cuda.ExternalStream(plan.query(_lib.Q_STREAM), device=self.device)
+        if not flush_between:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.barrier()
+            start.record(stream)
+            for _ in range(count):
+                step_fn()
+            stop.record(stream)
+            stop.synchronize()
+            self.barrier()
+            return start.elapsed_time(stop)
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(count)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(count)]
+        for i in range(count):
+            self.flush.fill_(i & 0xFF)
+            self.barrier()
+            if self.world > 1:
+                # A one-element all-reduce on the plan's stream releases every rank's stream together.
+                with torch.cuda.stream(stream):
+                    torch.distributed.all_reduce(self.token)
+            starts[i].record(stream)
+            step_fn()
+            stops[i].record(stream)
+            stops[i].synchronize()
+        self.barrier()
+        return sum(a.elapsed_time(b) for a, b in zip(starts, stops))
+
+
+ENGINES = {0: "layer-wise (FP64 tensor-core / SIMT GEMMs)", 1: "fused (FP32/FP64 pipe)",
+           2: "fused (tensor cores, 3xTF32 mma)", 3: "layer-wise (tcgen05 3xTF32 GEMMs)"}
+
+
+def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: int, peaks: dict, live: dict,
+            with_e2e: bool) -> dict:
+    """One workload on this rig: device-resident steps, optionally the end-to-end loop, and the
+    dominant kernel's device time from the last timed step."""
+    from quabla_b200 import _lib, workloads
+
+    torch = rig.torch
+    w = workloads.make(name, total_points)
+    data = rig.shard(w)
+    trainer, plan = rig.trainer(w, data)
+    plan.set_option(_lib.OPT_KERNEL_TIMERS, 1)
+    dtype_name = "f32" if np.dtype(w.dtype) == np.float32 else "f64"
+    scratch = plan.query(_lib.Q_SCRATCH_BYTES)
+    flush_between = scratch + sum(a.nbytes for a in data) <= 2 * L2_BYTES
+    for _ in range(max(warmup, 3)):
+        trainer.step()
+    plan.synchronize()
+    launches0 = plan.query(_lib.Q_KERNEL_LAUNCHES)
+    device_ms = rig.timed_loop(plan, trainer.step, steps, flush_between)
+    launches = plan.query(_lib.Q_KERNEL_LAUNCHES) - launches0
+    engine = plan.query(_lib.Q_ENGINE)
+    interior = plan.spec.sets[0]
+    local_points = interior.n_points
+    # Dominant kernel, from the last timed step: the layer GEMM launches of the layer-wise engines
+    # (an event pair around each), the interior set's one fused launch on the fused engines.
+    if engine in (0, 3):
+        gemm_ns = plan.query(_lib.Q_GEMM_NANOSECONDS)
+        gemm_launches = max(1, plan.query(_lib.Q_GEMM_LAUNCHES))
+        gemm_flops = float(plan.query(_lib.Q_GEMM_FLOPS))
+        kernel = {"name": "tc_tma_gemm_kernel (tcgen05, 3xTF32)" if engine == 3 else
+                  "dmma_gemm_kernel (FP64 MMA) / gemm_kernel" if dtype_name == "f64" else "gemm_kernel",
+                  "launches_per_step": int(gemm_launches), "us_per_launch": gemm_ns * 1e-3 / gemm_launches,
+                  "flops_per_launch": gemm_flops / gemm_launches, "us_per_step": gemm_ns * 1e-3}
+        achieved = gemm_flops / max(gemm_ns, 1) * 1e-3  # FLOP / ns = GFLOP/s; / 1e3 = TFLOP/s
+    else:
+        set0_ns = plan.query(_lib.Q_SET0_NANOSECONDS)
+        flops = w.flops_per_point(interior.streams) * local_points
+        kernel = {"name": "fused_mma_kernel" if engine == 2 else "fused_step_kernel", "launches_per_step": 1,
+                  "us_per_launch": set0_ns * 1e-3, "flops_per_launch": flops, "us_per_step": set0_ns * 1e-3}
+        achieved = flops / max(set0_ns, 1) * 1e-3
+    allreduce_us = plan.query(_lib.Q_ALLREDUCE_NANOSECONDS) * 1e-3 if rig.world > 1 else 0.0
+
+    e2e_ms = None
+    h2d = int(sum(a.nbytes for a in data))
+    if with_e2e:
+        pinned = [torch.from_numpy(np.ascontiguousarray(a)).pin_memory() for a in data]
+        pinned_np = [p.numpy() for p in pinned]
+
+        def e2e_step():
+            trainer.step(*pinned_np)  # host -> device copy of this rank's batch, the step, ...
+            _ = trainer.value         # ... and the step's loss read back
+
+        for _ in range(3):
+            e2e_step()
+        rig.barrier()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            if flush_between:
+                rig.flush.fill_(i & 0xFF)
+                torch.cuda.synchronize()
+            e2e_step()
+        plan.synchronize()
+        e2e_ms = 1e3 * (time.perf_counter() - t0)
+        rig.barrier()
+
+    # Every rank must hold the same parameters after the same number of updates.
+    digest = hashlib.sha256()
+    for index in range(len(plan.spec.parameters)):
+        digest.update(plan.read_parameter(index).tobytes())
+    word = int.from_bytes(digest.digest()[:6], "little")  # 48 bits: exact in float64
+    lo_hi = rig.max_over_ranks([float(word), -float(word)])
+    identical = lo_hi[0] == -lo_hi[1]
+
+    device_ms, = rig.max_over_ranks([device_ms])
+    total_points_run = w.interior_points
+    ms_per_step = device_ms / steps
+    streams = interior.streams
+    step_flops = (w.flops_per_point(streams) * w.interior_points
+                  + sum(w.flops_per_point(s) * n for n, s in w.extra))
+    if dtype_name == "f32":
+        # 3xTF32 on the tensor pipe: TF32 runs at half the bf16 rate, three passes per product.  The burst
+        # figure for kernels timed alone in a short step, the sustained one (seconds-long loop under the
+        # power cap) when the timed kernels keep the GPU busy for tens of milliseconds per step.
+        sustained = kernel["us_per_step"] > 2e4 and "bf16_tflops_sustained" in peaks
+        peak = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"] / 2.0 / 3.0
+        peak_source = f"bf16 {'sustained' if sustained else 'burst'} / 2 (tf32) / 3 (3xTF32 passes)"
+    else:
+        peak = live.get("dgemm_tflops")
+        peak_source = "torch.matmul float64 4096^3, best of 5, timed at start-up of this run"
+    out = {
+        "workload": w.name, "dtype": dtype_name, "interior_points": total_points_run, "ms_per_step": ms_per_step,
+        "points_per_s": total_points_run / (ms_per_step * 1e-3), "engine": ENGINES[engine], "streams": streams,
+        "reference_streams": w.streams, "merged_second_order": interior.merge_weights is not None,
+        "step_tflops": step_flops / (ms_per_step * 1e-3) / 1e12 / 1.0,
+        "kernel": kernel, "kernel_tflops": achieved, "peak_tflops": peak, "peak_source": peak_source,
+        "kernel_frac": achieved / peak if peak else None,
+        "step_frac": step_flops / (ms_per_step * 1e-3) / 1e12 / rig.world / peak if peak else None,
+        "gpu_launches": int(launches), "allreduce_us_rank0": allreduce_us, "replicas_identical": bool(identical),
+        "l2": ("256 MB written between timed steps, per-step event brackets" if flush_between else
+               f"one event bracket around {steps} back-to-back steps; per-rank working set "
+               f"{(scratch + h2d) / 2**30:.1f} GiB > L2"),
+        "h2d_bytes_per_step": h2d * rig.world, "d2h_bytes_per_step": int(np.dtype(w.dtype).itemsize) * rig.world,
+    }
+    if e2e_ms is not None:
+        e2e_ms, = rig.max_over_ranks([e2e_ms])
+        out["e2e_points_per_s"] = total_points_run / (e2e_ms / steps * 1e-3)
+    if rig.world > 1:
+        plan.detach_comm()
+    plan.close()
+    return out
+
+
+def parity_step(rig: Rig, name: str) -> dict:
+    """One value-and-gradient step of `name` on PARITY_POINTS points cut over the ranks; rank 0 compares
+    the all-reduced [loss, gradients] with the CPU oracle on the full batch (mean of shard means, gradients
+    summed in shard order: crates/quabla-core/src/tensor_ir.rs:11622-11724)."""
+    from oracle import contracted
+    from quabla_b200 import workloads
+    from quabla_b200._transforms import CompiledLoss
+
+    w = workloads.make(name, PARITY_POINTS)
+    trainer, plan = rig.trainer(w, rig.shard(w))
+    plan.execute()
+    outputs = plan.outputs()
+    dtype_name = "f32" if np.dtype(w.dtype) == np.float32 else "f64"
+    tolerance = PARITY_TOLERANCE[dtype_name]
+    worst = 0.0
+    if rig.rank == 0:
+        args = (w.params, *w.data)
+        full = CompiledLoss(w.loss, args, (0,), 0, build_plan=False)
+        expected_loss, expected_grads = contracted.value_and_grad(full.spec, full.named_inputs(args),
+                                                                  threads=contracted.max_threads())
+        worst = abs(float(outputs[0]) - expected_loss) / max(abs(expected_loss), 1e-300)
+        for got, expected in zip(outputs[1:], expected_grads):
+            scale = max(float(np.max(np.abs(expected))), 1e-300)
+            worst = max(worst, float(np.max(np.abs(got.reshape(expected.shape).astype(np.float64) - expected))) / scale)
+    worst, = rig.max_over_ranks([worst])
+    if rig.world > 1:
+        plan.detach_comm()
+    plan.close()
+    return {"points": w.interior_points, "max_rel_err": worst, "tol": tolerance, "passed": bool(worst <= tolerance)}
+
+
+def live_peaks(rig: Rig) -> dict:
+    """Library GEMM rates of this GPU, timed at start-up outside every timed region (torch.matmul, CUDA
+    events, best of 5): the denominators of the float64 fractions and a cross-check of the float32 one."""
+    torch = rig.torch
+    out = {}
+    for key, dtype, n, tf32 in (("dgemm_tflops", torch.float64, 4096, False), ("tf32_gemm_tflops", torch.float32, 8192, True)):
+        previous = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        try:
+            a = torch.randn(n, n, dtype=dtype, device=rig.device)
+            b = torch.randn(n, n, dtype=dtype, device=rig.device)
+            torch.matmul(a, b)
+            best = float("inf")
+            for _ in range(5):
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                torch.matmul(a, b)
+                stop.record()
+                stop.synchronize()
+                best = min(best, start.elapsed_time(stop))
+            out[key] = 2.0 * n**3 / (best * 1e-3) / 1e12
+            del a, b
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = previous
+    torch.cuda.empty_cache()
+    return out
+
+
+# DRAM bytes (read + write) per row of one forward/data-gradient launch of tc_tma_gemm_kernel at width 256,
+# from the ncu capture summarised in profiles/tc_tma_gemm_kernel_heat3d.md (874 MB over 448,512 rows).
+TC_GEMM_DRAM_BYTES_PER_ROW = 874e6 / 448512
 
 
 def main() -> None:
@@ -230,197 +534,82 @@ def main() -> None:
         run_reference(args)
         return
 
-    import torch
+    rig = Rig(args)
+    torch = rig.torch
+    peaks, peak_kind = measured_peaks()
+    live = live_peaks(rig)
 
-    import quabla_b200 as qb
-    from quabla_b200 import _lib, workloads
-    from quabla_b200._plan import nccl_unique_id
+    parity = None
+    if rig.world > 1 and not args.no_parity:
+        parity = parity_step(rig, args.workload)
+        if not parity["passed"]:
+            if rig.rank == 0:
+                print(json.dumps({"error": "multi-GPU parity failed", "parity": parity}))
+            torch.distributed.destroy_process_group()
+            raise SystemExit(3)
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the qb200 backend has no CPU fallback")
-    torch.cuda.set_device(local_rank)
-    device = f"cuda:{local_rank}"
-    if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=torch.device(device))
-
-    # Workload: every rank draws the same global point sets and keeps its shard.
-    base = workloads.make(args.workload, args.points)
-    per_gpu = base.interior_points
-    if world > 1:
-        big = workloads.make(args.workload, per_gpu * world)
-        data = []
-        for full_array, local_array in zip(big.data, base.data):
-            if full_array.shape[0] == local_array.shape[0] * world:
-                n = local_array.shape[0]
-                data.append(np.ascontiguousarray(full_array[rank * n:(rank + 1) * n]))
-            else:
-                data.append(local_array)  # tiny exact sets (two boundary points) are replicated
-        data = tuple(data)
-    else:
-        data = base.data
-    w = base
-    optimizer = qb.optim.Adam(learning_rate=1e-3)
-    batch_argnums = tuple(range(len(data)))
-    trainer = qb.optim.Trainer(w.loss, w.params, optimizer, *data, device=device, batch_argnums=batch_argnums)
-    plan = trainer._executor.plan
-    if world > 1:
-        ids = [nccl_unique_id() if rank == 0 else None]
-        torch.distributed.broadcast_object_list(ids, src=0)
-        plan.attach_comm(ids[0], rank, world, "mean")
-    stream = torch.cuda.ExternalStream(plan.query(_lib.Q_STREAM), device=device)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # larger than the 126 MB L2
-    align_token = torch.zeros(1, device=device)
-
-    kernel_ns: list = []  # device time of the interior point set's kernels, one entry per timed step
-    allreduce_ns: list = []  # device time of the gradient all-reduce (waits for the other ranks included)
-
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    def timed_steps(step_fn, count: int) -> float:
-        """Milliseconds of `count` steps, each bracketed by events on the plan's
-        stream; L2 is flushed between steps, outside the timed brackets."""
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(count)]
-        stops = [torch.cuda.Event(enable_timing=True) for _ in range(count)]
-        for i in range(count):
-            flush.fill_(i & 0xFF)
-            barrier()  # ranks enter the step together: the bracket times the step, not the ranks' skew
-            if world > 1:
-                # ... and their streams too: a one-element all-reduce on the plan's stream releases every
-                # rank's stream at the same moment, so host jitter after the barrier stays outside the bracket.
-                with torch.cuda.stream(stream):
-                    torch.distributed.all_reduce(align_token)
-            starts[i].record(stream)
-            step_fn()
-            stops[i].record(stream)
-            stops[i].synchronize()
-            kernel_ns.append(plan.query(_lib.Q_SET0_NANOSECONDS))
-            allreduce_ns.append(plan.query(_lib.Q_ALLREDUCE_NANOSECONDS))
-        return sum(a.elapsed_time(b) for a, b in zip(starts, stops))
-
-    def device_step():
-        trainer.step()
-
-    pinned = [torch.from_numpy(np.ascontiguousarray(a)).pin_memory() for a in data]
-    pinned_np = [p.numpy() for p in pinned]
-
-    def e2e_step():
-        trainer.step(*pinned_np)  # host -> device copy of the batch, step, ...
-        _ = trainer.value         # ... and the step's loss read back
-
-    for _ in range(max(args.warmup, 3)):
-        device_step()
-    plan.synchronize()
-    barrier()
     try:
-        gpu_uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+        gpu_uuid = str(torch.cuda.get_device_properties(rig.local_rank).uuid)
     except Exception:
         gpu_uuid = None
-    sampler = ClockSampler(local_rank, gpu_uuid)
+    sampler = ClockSampler(rig.local_rank, gpu_uuid)
     sampler.start()
-    launches0 = plan.query(_lib.Q_KERNEL_LAUNCHES)
-    device_ms = timed_steps(device_step, args.steps)
-    launches = plan.query(_lib.Q_KERNEL_LAUNCHES) - launches0
-    barrier()
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    e2e_ms = 0.0
-    for i in range(args.steps):
-        flush.fill_(i & 0xFF)
-        barrier()
-        t1 = time.perf_counter()
-        e2e_step()
-        plan.synchronize()
-        e2e_ms += 1e3 * (time.perf_counter() - t1)
+    main_result = measure(rig, args.workload, args.points, args.steps, args.warmup, peaks, live, with_e2e=True)
     clocks = sampler.stop()
-    barrier()
+    if not main_result["replicas_identical"]:
+        if rig.rank == 0:
+            print(json.dumps({"error": "replicas diverged", "result": main_result}))
+        raise SystemExit(4)
 
-    times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
-    device_ms, e2e_ms = (float(t) for t in times.cpu())
-    total_points = per_gpu * world
-    ms_per_step = device_ms / args.steps
-    value = total_points / (ms_per_step * 1e-3)
-    e2e_value = total_points / (e2e_ms / args.steps * 1e-3)
-    h2d = int(sum(a.nbytes for a in data))
-    d2h = int(np.dtype(w.dtype).itemsize)
+    others = {}
+    if not args.no_others and args.points is None:
+        for name in ("poisson2d", "burgers", "beam"):
+            if name == args.workload:
+                continue
+            r = measure(rig, name, None, 5, 3, peaks, live, with_e2e=False)
+            others[name] = {k: r[k] for k in ("dtype", "interior_points", "ms_per_step", "points_per_s", "engine",
+                                              "streams", "step_tflops", "kernel", "kernel_tflops", "peak_tflops",
+                                              "kernel_frac", "replicas_identical", "allreduce_us_rank0")}
 
-    peaks, peak_kind = measured_peaks()
-    dtype_name = "f32" if np.dtype(w.dtype) == np.float32 else "f64"
-    # Roofline of the dominant kernel: the kernels of the interior point set (one fused launch on
-    # narrow networks), timed live with CUDA events on the plan's stream inside the timed steps.
-    kernel_s = float(np.mean(kernel_ns)) * 1e-9
-    # Matmul FLOPs one launch EXECUTES: the streams the plan carries (a Laplacian carried as one merged
-    # second-order stream is fewer streams than the reference formulation's one per direction).
-    interior = plan.spec.sets[0]
-    streams = interior.streams
-    flops = w.flops_per_point(streams) * per_gpu
-    step_flops = flops + sum(w.flops_per_point(s) * n for n, s in w.extra)
-    achieved_tflops = flops / kernel_s / 1e12
-    if dtype_name == "f32":
-        # 3xTF32 on the tensor pipe: TF32 runs at half the bf16 rate, three passes per product.
-        # Burst figure for a kernel timed alone in a short step; the sustained one (seconds-long loop under the
-        # power cap) when the timed kernels run for tens of milliseconds per step.
-        sustained = kernel_s > 0.02 and "bf16_tflops_sustained" in peaks
-        peak_tflops = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"] / 2.0 / 3.0
-        peak_note = f"{peak_kind} bf16 {'sustained' if sustained else 'burst'} / 2 (tf32) / 3 (3xTF32 passes)"
-    else:
-        # Not in the driver-written peaks file: cuBLAS DGEMM 4096^3 (torch.matmul, float64, best of 5,
-        # CUDA events) on this pool's B200; the FP64 MMA issue rate (64 FMA/clk/SM) gives the same.
-        peak_tflops = 35.0
-        peak_note = "cuBLAS DGEMM 4096^3 measured on this pool (35.0 TFLOP/s)"
-    engine = plan.query(_lib.Q_ENGINE)
-    engine_name = {0: "layerwise", 1: "fused (FP32 pipe)", 2: "fused (tensor cores, 3xTF32 mma)",
-                   3: "layerwise (tcgen05 3xTF32 GEMMs)"}[engine]
-    kernel_name = {0: "layer-wise kernels of the interior point set",
-                   1: "fused_step_kernel (interior point set)",
-                   2: "fused_mma_kernel (interior point set)",
-                   3: "layer-wise kernels of the interior point set (tcgen05 GEMMs)"}[engine]
-    # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under profiles/
-    # (dram__bytes read + write); known for the default workload's fused kernel only.
+    kernel = main_result["kernel"]
     traffic = None
-    if w.name == "poisson2d" and engine == 2 and per_gpu == 65536 and streams == 4:
-        traffic = 114.3e6
-    extra_peaks = {}
-    if dtype_name == "f32":
-        # Also measured on this pool (torch.matmul 8192^3, best of 10): TF32 GEMM 756.5, SGEMM 63.9 TFLOP/s.
-        extra_peaks = {"frac_of_tf32_gemm_over_3": achieved_tflops / (756.5 / 3.0),
-                       "frac_of_sgemm": achieved_tflops / 63.9}
+    if main_result["engine"] == ENGINES[3] and args.workload == "heat3d":
+        rows = kernel["flops_per_launch"] / (2.0 * 256 * 256)
+        traffic = TC_GEMM_DRAM_BYTES_PER_ROW * rows
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": dtype_name, "data": "synthetic",
-        "config": {"workload": w.name, "description": w.description, "interior_points_per_gpu": per_gpu,
-                   "other_sets": w.extra, "optimizer": "adam lr=1e-3", "parameters": w.parameter_count,
-                   "engine": engine_name, "streams": streams, "reference_streams": w.streams,
-                   "merged_second_order": interior.merge_weights is not None,
-                   "l2": "256 MB written between timed steps, outside the per-step event brackets",
-                   "allreduce_us_rank0": float(np.mean(allreduce_ns)) * 1e-3 if world > 1 else 0.0},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": int(launches),
+        "metric": METRIC, "value": main_result["points_per_s"], "unit": UNIT, "n_gpus": rig.world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main_result["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": main_result["dtype"],
+        "data": "synthetic",
+        "config": workload_config(args.workload, args.points, rig.world),
+        "details": {"engine": main_result["engine"], "streams": main_result["streams"],
+                    "reference_streams": main_result["reference_streams"],
+                    "merged_second_order": main_result["merged_second_order"], "l2": main_result["l2"],
+                    "allreduce_us_rank0": main_result["allreduce_us_rank0"],
+                    "step_tflops_all_gpus": main_result["step_tflops"], "step_frac_per_gpu": main_result["step_frac"],
+                    "parity": None if parity is None else {**parity, "replicas_identical": main_result["replicas_identical"]},
+                    "replicas_identical": main_result["replicas_identical"],
+                    "library_gemm_tflops_this_run": live, "others": others},
+        "e2e": {"value": main_result["e2e_points_per_s"], "unit": UNIT,
+                "h2d_bytes_per_step": main_result["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": main_result["d2h_bytes_per_step"]},
+        "gpu_launches": main_result["gpu_launches"],
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peak_tflops, "unit": "TFLOP/s",
-                     "frac": achieved_tflops / peak_tflops, "traffic": traffic, **extra_peaks,
-                     "kernel": kernel_name, "kernel_us": kernel_s * 1e6, "flops_per_launch": flops,
-                     "step_flops": step_flops, "peak_source": peak_note},
+        "roofline": {"bound": "tensor", "achieved": main_result["kernel_tflops"], "peak": main_result["peak_tflops"],
+                     "unit": "TFLOP/s", "frac": main_result["kernel_frac"], "traffic": traffic,
+                     "kernel": kernel["name"], "launches_per_step": kernel["launches_per_step"],
+                     "kernel_us": kernel["us_per_launch"], "flops_per_launch": kernel["flops_per_launch"],
+                     "kernel_us_per_step": kernel["us_per_step"],
+                     "peak_source": f"{peak_kind}: {main_result['peak_source']}",
+                     "frac_of_tf32_gemm_over_3": (main_result["kernel_tflops"] / (live["tf32_gemm_tflops"] / 3.0)
+                                                  if main_result["dtype"] == "f32" else None)},
     }
-    if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
-            cpu_value, sample = cpu_sample(args.workload, args.cpu_seconds, 1)
+    if rig.rank == 0:
+        if rig.world == 1 and not args.no_cpu_baseline:
+            cpu_value, sample = cpu_sample(args.workload, args.cpu_seconds, 1, args.points)
             line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": 1, "kind": "port", "sample": sample}
         print(json.dumps(line))
-    if world > 1:
-        plan.detach_comm()
+    if rig.world > 1:
         torch.distributed.destroy_process_group()
 
 

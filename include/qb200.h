@@ -345,13 +345,18 @@ qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d
  * Meant for hosts where device allocation is not available at call time: a
  * plugin inside a runtime that owns the memory pool, a latency-bound loop that
  * may not take the allocator lock, a process that has already handed every
- * free byte to something else.  Same arguments, same result (bit for bit) as
- * qb200_weight_gradient, but the split scratch is a 16 MiB array built into
- * the library (held on every GPU that loads the library until the process
- * exits) and no cudaMalloc/cudaFree or other allocating call is made.
+ * free byte to something else.  Same arguments and, for every shape, the same
+ * result bit for bit as qb200_weight_gradient: both entry points run one
+ * shared dispatch (tcgen05 contraction for float32 with d_in % 128 == 0 and
+ * d_out % 64 == 0, d_out <= 256; FP64 tensor-core or plain kernel otherwise)
+ * on the same split.  The split scratch is a 16 MiB array built into the
+ * library (held on every GPU that loads the library until the process exits)
+ * and no cudaMalloc/cudaFree or other allocating call is made.
  *
- *  - Limit: ceil(rows / 4096) * d_in * d_out * sizeof(element) <= 16 MiB,
- *    otherwise QB200_TOO_LARGE and nothing is launched.
+ *  - Limit: ceil(rows / 4096) * d_in * d_out * sizeof(element), rounded up to
+ *    16 bytes, + 16 bytes <= 16 MiB, otherwise QB200_TOO_LARGE and nothing is
+ *    launched.  (Both entry points also refuse more than 65535 slices, that is
+ *    rows > 268,431,360, with QB200_TOO_LARGE.)
  *  - The first call on each device looks up the array's device address (with
  *    that device current); make that first call before starting any stream
  *    capture.

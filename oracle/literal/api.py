@@ -403,6 +403,38 @@ def hessian(fun, argnums=0):
     return apply
 
 
+def jvp(fun, primals, tangents):
+    """`jvp(fun, primals, tangents)` called on tracers (python/quabla/_transforms.py:1273-1361): stage
+    `fun` once, build the forward-mode graph with one tangent input per floating primal leaf
+    (`graph._symbolic_jvp(traced, tangent_names)`, tensor_ir.rs:2999-3319 through op/jvp.rs), and splice it
+    into the caller's graph with the primals and the tangents bound (`_call_traced` -> `_splice`,
+    _transforms.py:768-777, 490-501).  Returns (primal outputs, tangent outputs)."""
+    primals, tangents = tuple(primals), tuple(tangents)
+    if len(primals) != len(tangents):
+        raise ValueError("jvp requires one tangent per primal")
+    trace, names, leaves, out_nodes, out_rebuild = _stage(fun, primals)
+    tangent_leaves, _ = _flatten(list(tangents))
+    if len(tangent_leaves) != len(leaves):
+        raise ValueError("jvp tangents must have the tree structure of the primals")
+    tangent_names = {name: "tangent/" + name for name in names if name is not None}
+    g3, values, tangent_nodes = tf.symbolic_jvp(trace.graph, out_nodes, tangent_names)
+    g = _current().graph
+    bound = _bindings(trace, names, leaves)
+    for name, leaf, tangent in zip(names, leaves, tangent_leaves):
+        if name is None:
+            continue
+        if isinstance(tangent, Tracer):
+            bound[tangent_names[name]] = tangent._here()
+        else:
+            dtype = g.node(bound[name]).dtype
+            tangent = np.broadcast_to(np.asarray(tangent, dtype=np.float64), g.shape(bound[name]))
+            bound[tangent_names[name]] = g.constant(np.array(tangent), dtype)
+    spliced = tf.inline(g, g3, bound, list(values) + list(tangent_nodes))
+    count = len(out_nodes)
+    return (out_rebuild([Tracer(g, n) for n in spliced[:count]]),
+            out_rebuild([Tracer(g, n) for n in spliced[count:]]))
+
+
 def value_and_grad_data_parallel(fun, params, shards: list, reduction: str = "mean"):
     """CPU data-parallel oracle (value_and_vjp_data_parallel,
     crates/quabla-core/src/tensor_ir.rs:11622-11724): per-shard value-and-gradient, the

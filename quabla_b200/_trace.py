@@ -563,22 +563,46 @@ def symbolic_hessian(fun: Callable, argnum: int, args: tuple) -> TraceValue:
 
 
 def symbolic_jvp(fun: Callable, primals: tuple, tangents: tuple):
+    """(outputs, tangents of the outputs) of `fun` at the per-point `primals` along `tangents`; the
+    outputs may be any pytree of per-point arrays (python/quabla/_transforms.py:1273-1361)."""
+    if len(primals) != len(tangents):
+        raise ValueError("jvp requires one tangent per primal")
     variables = [_Variables(as_trace(p)) for p in primals]
-    value = _point_scalar(fun(*[v.value for v in variables]), "jvp")
-    total = sx.ZERO
-    restored = value
+    weights = []
     for v, tangent in zip(variables, tangents):
-        t = np.broadcast_to(np.asarray(tangent.array() if isinstance(tangent, TraceValue) else tangent, dtype=object),
-                            v.cells.shape).reshape(-1)
-        for cell, weight in zip(v.cells.reshape(-1), t):
-            total = total + sx.as_expr(weight) * sx.derivative(value, _lift_rule(cell))
-    for v in variables:
-        total = v.restore(total)
-        restored = v.restore(restored)
+        t = tangent.array() if isinstance(tangent, TraceValue) else tangent
+        weights.append(np.broadcast_to(np.asarray(t, dtype=object), v.cells.shape).reshape(-1))
     dtype = primals[0].dtype
-    out_v, out_t = np.empty((), dtype=object), np.empty((), dtype=object)
-    out_v[()], out_t[()] = restored, total
-    return TraceValue(out_v, None, dtype), TraceValue(out_t, None, dtype)
+
+    def restore(e: sx.Expr) -> sx.Expr:
+        for v in variables:
+            e = v.restore(e)
+        return e
+
+    leaves, rebuild = _flatten(fun(*[v.value for v in variables]))
+    out_values, out_tangents = [], []
+    for leaf in leaves:
+        if isinstance(leaf, (int, float)) and not isinstance(leaf, bool):
+            cells = np.empty((), dtype=object)
+            cells[()] = sx.const(leaf)
+        else:
+            leaf = as_trace(leaf)
+            if leaf.batch is not None:
+                raise _unsupported("jvp of a batched value; wrap the per-point function in vmap", "jvp")
+            cells = leaf.array()
+        value_cells = np.empty(cells.shape, dtype=object)
+        tangent_cells = np.empty(cells.shape, dtype=object)
+        flat_in, flat_v, flat_t = cells.reshape(-1), value_cells.reshape(-1), tangent_cells.reshape(-1)
+        for i in range(flat_in.size):
+            value = sx.as_expr(flat_in[i])
+            total = sx.ZERO
+            for v, t in zip(variables, weights):
+                for cell, weight in zip(v.cells.reshape(-1), t):
+                    total = total + sx.as_expr(weight) * sx.derivative(value, _lift_rule(cell))
+            flat_v[i], flat_t[i] = restore(value), restore(total)
+        out_values.append(TraceValue(value_cells, None, dtype))
+        out_tangents.append(TraceValue(tangent_cells, None, dtype))
+    return rebuild(out_values), rebuild(out_tangents)
 
 
 def symbolic_vmap(fun: Callable, in_axes, args: tuple):

@@ -770,6 +770,7 @@ qb200_status Plan<T>::check_device_error() {
     const int gave_up = h_status_[0], skipped = h_status_[1];
     if (gave_up == 0 && skipped == 0) return QB200_OK;
     h_status_[0] = h_status_[1] = 0;
+    steps_ = std::max<int64_t>(0, steps_ - skipped);  // skipped updates do not count (bias corrections)
     QB_CUDA(cudaMemsetAsync(d_error_, 0, sizeof(int), stream_));
     QB_CUDA(cudaStreamSynchronize(stream_));
     if (gave_up != 0)

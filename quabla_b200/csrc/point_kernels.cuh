@@ -187,7 +187,7 @@ template <typename T>
 struct StepStatus {
     const int* error;  // device flag of the plan
     T* flat_flag;      // slot behind the gradients in the flat [loss, gradients..., flag] buffer
-    int* host_status;  // mapped host words: [0] a wait gave up, [1] an update was skipped
+    int* host_status;  // mapped host words: [0] a wait gave up, [1] optimizer updates skipped since the last report
 };
 
 template <typename T>
@@ -288,7 +288,7 @@ struct AdamCoeffs {
 template <typename T>
 __device__ __forceinline__ bool update_skipped(const T* __restrict__ skip, int* __restrict__ host_status) {
     if (skip == nullptr || skip[0] == T(0)) return false;
-    if (blockIdx.x == 0 && threadIdx.x == 0 && host_status != nullptr) host_status[1] = 1;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && host_status != nullptr) host_status[1] += 1;  // updates skipped since the last report
     return true;
 }
 
@@ -385,7 +385,9 @@ __global__ void __launch_bounds__(1024) global_norm_kernel(const T* __restrict__
         }
         scalars[0] = peak;
         scalars[1] = factor;
-        if (!isfinite(norm) || !isfinite(peak)) scalars[2] = 1.0;
+        // Sticky: set by a NaN or infinite gradient entry (then root is not finite either), not by a
+        // norm that merely overflowed while peak and root stayed finite (cuda_optimizer.rs:98-103).
+        if (!(isfinite(peak) && isfinite(root))) scalars[2] = 1.0;
     }
 }
 

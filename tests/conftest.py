@@ -3,6 +3,11 @@ import sys
 
 import pytest
 
+# The data-parallel tests tear communicators down after a host-injected failure; NCCL must then have no
+# buffer bound to an NVLink multicast object, so NVLS stays off in the test process (set before the
+# library loads NCCL).
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

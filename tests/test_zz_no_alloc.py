@@ -45,7 +45,10 @@ def test_static_scratch_variant_equals_the_allocating_one_on_two_calls_in_a_row(
     lib = _lib.load()
     # First a call that fills many slices of the shared array, then a smaller one
     # with a different shape, which would pick up leftovers if it read any.
-    for rows, d_in, d_out, seed in ((50000, 64, 64, 1), (4097, 17, 5, 2)):
+    # 128 x 128 and 256 x 256 take the tensor-core contraction in float32 (both entry points share one
+    # dispatch), the other shapes the FP64 tensor-core or the plain kernel.
+    for rows, d_in, d_out, seed in ((50000, 64, 64, 1), (4097, 17, 5, 2), (30000, 128, 128, 3), (9000, 256, 256, 4),
+                                    (100, 128, 64, 5)):
         pooled, fixed, exact = _both(lib, torch, dtype_name, rows, d_in, d_out, seed)
         assert np.isfinite(fixed).all()
         # Same kernels, same split, same order of additions: identical bits.
