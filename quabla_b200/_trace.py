@@ -703,6 +703,69 @@ def _single_direction(word: tuple) -> tuple[tuple[float, ...], int]:
     return first, len(word)
 
 
+def _is_pure(word: tuple) -> bool:
+    return all(d == word[0] for d in word)
+
+
+def _canonical(direction: tuple[float, ...], order: int) -> tuple[tuple[float, ...], float]:
+    """(direction with its first non-zero component positive, sign): D^k along -v is (-1)^k D^k along v."""
+    for c in direction:
+        if c != 0.0:
+            if c < 0.0:
+                return tuple(-x for x in direction), -1.0 if order % 2 else 1.0
+            break
+    return direction, 1.0
+
+
+def _resolve_mixed_partials(total: sx.Expr) -> sx.Expr:
+    """Rewrites every mixed partial derivative of the network (an off-diagonal Hessian entry, u_xxy, ...) as a
+    combination of pure derivatives along sums of its directions, which the kernels carry as streams.
+
+    Polarisation: D_{v1}...D_{vk} u = 1/(k! 2^k) * sum over signs e of (e_1...e_k) D^k along (e_1 v1 + ... + e_k vk).
+    A second-order mixed partial whose two directions are carried to second order anyway uses
+    u_ab = (D^2_{a+b} - D^2_a - D^2_b) / 2 instead: one new direction, not two.  The reference computes the
+    same entries by differentiating the gradient graph once more along a basis
+    (python/quabla/_transforms.py:1812-2036)."""
+    nets = sx.leaves([total], "net")
+    pure_order: dict = {}
+    for leaf in nets:
+        word = leaf.args[1]
+        if word and word != sx.MERGED_WORD and _is_pure(word):
+            pure_order[word[0]] = max(pure_order.get(word[0], 0), len(word))
+    mapping: dict = {}
+    for leaf in nets:
+        network, word = leaf.args
+        if not word or word == sx.MERGED_WORD or _is_pure(word):
+            continue
+        k = len(word)
+        if k > 4:
+            raise _unsupported(f"derivative order {k}; orders 1..4 are supported", "grad")
+        terms: dict = {}
+
+        def add_term(direction, coefficient: float) -> None:
+            if not any(direction):
+                return
+            direction, sign = _canonical(tuple(float(x) for x in direction), k)
+            terms[direction] = terms.get(direction, 0.0) + sign * coefficient
+
+        if k == 2 and pure_order.get(word[0], 0) >= 2 and pure_order.get(word[1], 0) >= 2:
+            a, b = word
+            add_term(tuple(x + y for x, y in zip(a, b)), 0.5)
+            add_term(a, -0.5)
+            add_term(b, -0.5)
+        else:
+            scale = 1.0 / (math.factorial(k) * 2.0**k)
+            for signs in itertools.product((1.0, -1.0), repeat=k):
+                direction = tuple(sum(e * v[c] for e, v in zip(signs, word)) for c in range(len(word[0])))
+                add_term(direction, scale * math.prod(signs))
+        replacement = sx.ZERO
+        for direction, coefficient in sorted(terms.items(), reverse=True):
+            if coefficient != 0.0:
+                replacement = replacement + sx.const(coefficient) * sx.net(network, (direction,) * k)
+        mapping[leaf] = replacement
+    return sx.substitute(total, mapping) if mapping else total
+
+
 def _merge_enabled() -> bool:
     """QB200_MERGE=0 keeps one second-order stream per direction (for comparisons)."""
     return os.environ.get("QB200_MERGE", "1") != "0"
@@ -815,6 +878,7 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
             _, name, _ = e.args[0]
             if int(data_shapes[name][0]) != batch:
                 raise ValueError(f"input '{name}' does not have the batch size {batch} of its loss term")
+        total = _resolve_mixed_partials(total)
         # Streams.
         orders: dict = {}
         for leaf in sx.leaves([total], "net"):
