@@ -164,6 +164,17 @@ class SGD:
         return rebuild(updated), state
 
 
+def decay_frozen_parameter(value: np.ndarray, weight_decay: float, learning_rate: float) -> np.ndarray:
+    """AdamW's decoupled decay of a parameter the loss ignores: gradient and moments are zero, so the
+    element rule reduces to p - (0 + weight_decay * p) * learning_rate, evaluated in float64 and rounded
+    once to the parameter's dtype every step (decay_frozen_parameters,
+    crates/quabla-python/src/tensor_trace.rs:5071-5105; the `0 +` keeps the rule's signed-zero result)."""
+    value = np.asarray(value)
+    wide = value.astype(np.float64)
+    with np.errstate(all="ignore"):
+        return (wide - (0.0 + weight_decay * wide) * learning_rate).astype(value.dtype)
+
+
 class CudaTrainerExecutor:
     """What the reference's `_quabla._cuda_trainer_optimizer(...)` returns
     (crates/quabla-python/src/tensor_trace.rs:5108-5289): `step`, `loss`,
@@ -187,9 +198,9 @@ class CudaTrainerExecutor:
             if name in active or name in compiled.data_names:
                 self._plan.bind(name, value)
             elif name in self._parameter_names:
-                # The loss ignores this parameter: it only decays, on the host
+                # The loss ignores this parameter: it only decays, on the host, stored in its own dtype
                 # (crates/quabla-python/src/tensor_trace.rs:5071-5105).
-                self._frozen[name] = np.array(value, dtype=np.float64)
+                self._frozen[name] = np.array(value, dtype=compiled.dtype)
         self._dtype = compiled.dtype
         self._shapes = dict(zip(compiled.param_names, compiled.param_shapes))
         self._active = active
@@ -215,9 +226,9 @@ class CudaTrainerExecutor:
         self._plan.execute()
         self._plan.optimizer_step(config)
         if self._frozen and self._rule["rule"] == "adam" and self._rule["weight_decay"] != 0.0:
-            factor = self._rule["weight_decay"] * self._learning_rate
             for name in self._frozen:
-                self._frozen[name] = self._frozen[name] - factor * self._frozen[name]
+                self._frozen[name] = decay_frozen_parameter(self._frozen[name], self._rule["weight_decay"],
+                                                            self._learning_rate)
 
     def loss(self, inputs: dict | None = None) -> np.ndarray:
         for name, value in (inputs or {}).items():
@@ -234,7 +245,7 @@ class CudaTrainerExecutor:
             if name in self._active:
                 out[name] = self._plan.read_input(name, self._shapes[name])
             else:
-                out[name] = self._frozen[name].astype(self._dtype)
+                out[name] = self._frozen[name].copy()
         return out
 
     def _moment_layout(self):
@@ -311,7 +322,7 @@ class CudaTrainerExecutor:
             if name in self._active:
                 self._plan.bind(name, value)
             else:
-                self._frozen[name] = np.array(value, dtype=np.float64)
+                self._frozen[name] = np.array(value, dtype=self._dtype)
         for which, flat in enumerate(flats or ()):
             self._plan.write_moments(which, flat, step)
 

@@ -245,3 +245,22 @@ def test_special_function_chains_match_the_literal_oracle(dtype):
         minus[1]["w"][2, 3] -= h
         fd = (float(step(plus, x)[0]) - float(step(minus, x)[0])) / (2 * h)
         assert abs(float(grads[1]["w"][2, 3]) - fd) <= 1e-6 * max(abs(fd), 1e-3)
+
+
+def test_frozen_parameter_decay_is_the_adam_rule_with_zero_gradient_and_moments():
+    # decay_frozen_parameters (crates/quabla-python/src/tensor_trace.rs:5071-5105): the shared element rule in
+    # float64 with g = m = v = 0, rounded once to the parameter's dtype per step.
+    from quabla_b200.optim import decay_frozen_parameter
+
+    for dtype in (np.float32, np.float64):
+        p = np.array([1.5, -2.25, 0.0, -0.0, 1e-30, 3.0e5], dtype=dtype)
+        zeros = np.zeros_like(p, dtype=np.float64)
+        current = p.copy()
+        expected = p.copy()
+        for step in range(1, 6):
+            current = decay_frozen_parameter(current, 0.01, 1e-3)
+            wide, _, _ = host.adam_update(expected.astype(np.float64), zeros, zeros, zeros, 1, 1e-3, 0.9, 0.999, 1e-8,
+                                          0.01, np.float64)
+            expected = wide.astype(dtype)
+            assert current.dtype == np.dtype(dtype)
+            assert current.tobytes() == expected.tobytes(), (dtype, step)
