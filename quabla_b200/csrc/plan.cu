@@ -198,10 +198,6 @@ class Plan final : public qb200_plan {
         int partial_offset = 0;    // first loss partial of this set
         int partial_count = 0;
         bool table_dirty = true;
-        // Roles of the streams for a GEMM epilogue that composes the activation's jets (orders <= 2 only).
-        bool jet_fusable = false;
-        unsigned char jet_mode[MAX_STREAMS];
-        float jet_keep[MAX_STREAMS], jet_w[MAX_STREAMS];
     };
 
     template <typename P> qb200_status dev_alloc(P** ptr, size_t count) {
@@ -226,8 +222,6 @@ class Plan final : public qb200_plan {
     qb200_status tc_prepare();
     // Each returns true when the tensor-core path took the launch.
     bool tc_forward(int layer, const T* A, T* C, long long rows, int bias_rows, qb200_status* st);
-    // The same product with the jet composition in its epilogue: writes H_l and the saved Z_l streams.
-    bool tc_forward_jet(int si, int layer, const T* A, T* H, T* Z, int C, qb200_status* st);
     bool tc_dgrad(int layer, const T* G, T* Gprev, long long rows, qb200_status* st);
     bool tc_wgrad(int layer, const T* H, const T* G, long long rows, int rows_per_slice, qb200_status* st);
     qb200_status check_device_error();
@@ -496,37 +490,6 @@ qb200_status Plan<T>::init() {
             st.merge_w.w[j] = (T)st.spec.merge_w[j];
         }
         st.ncols = (int)s.cols.size();
-        {
-            // Stream roles: 0 primal; 1 first order along a direction (it also feeds the running sum a later
-            // stream needs: z1^2 of its own direction, or w_j z1_j^2 for the merged stream); 2 second order or merged.
-            bool ok = desc_.activation == QB200_ACT_TANH && st.spec.S <= MAX_STREAMS;
-            for (int k = 0; k < MAX_STREAMS; ++k) {
-                st.jet_mode[k] = 0;
-                st.jet_keep[k] = 0.0f;
-                st.jet_w[k] = 0.0f;
-            }
-            for (int j = 0; j < st.spec.ndirs && ok; ++j) {
-                const int k = st.spec.order[j], b = st.spec.base[j];
-                if (k > 2 || (st.spec.merged && k != 1)) {
-                    ok = false;
-                    break;
-                }
-                st.jet_mode[b] = 1;
-                if (st.spec.merged) {
-                    st.jet_keep[b] = j == 0 ? 0.0f : 1.0f;
-                    st.jet_w[b] = (float)st.spec.merge_w[j];
-                } else if (k == 2) {
-                    st.jet_keep[b] = 0.0f;
-                    st.jet_w[b] = 1.0f;
-                    st.jet_mode[b + 1] = 2;
-                } else {
-                    st.jet_keep[b] = 1.0f;
-                    st.jet_w[b] = 0.0f;
-                }
-            }
-            if (ok && st.spec.merged) st.jet_mode[st.spec.S - 1] = 2;
-            st.jet_fusable = ok;
-        }
         const size_t S = st.spec.S;
         const size_t per_point = S * (sum_h + sum_z + 2 * (size_t)dmax + 2) * sizeof(T);
         long long chunk = (long long)std::min<size_t>(budget / per_point, (size_t)chunk_cap);
@@ -860,7 +823,6 @@ qb200_status Plan<T>::run_fused(int si, bool forward_only) {
 template <typename T> qb200_status Plan<T>::tc_setup() { return QB200_OK; }
 template <typename T> qb200_status Plan<T>::tc_prepare() { return QB200_OK; }
 template <typename T> bool Plan<T>::tc_forward(int, const T*, T*, long long, int, qb200_status*) { return false; }
-template <typename T> bool Plan<T>::tc_forward_jet(int, int, const T*, T*, T*, int, qb200_status*) { return false; }
 template <typename T> bool Plan<T>::tc_dgrad(int, const T*, T*, long long, qb200_status*) { return false; }
 template <typename T> bool Plan<T>::tc_wgrad(int, const T*, const T*, long long, int, qb200_status*) { return false; }
 
@@ -912,29 +874,6 @@ bool Plan<float>::tc_forward(int layer, const float* A, float* C, long long rows
                                          d_error_, stream_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(forward) failed: %s", cudaGetErrorString(e));
-    return true;
-}
-
-static bool jet_fusion_enabled() {
-    static const bool on = [] {
-        const char* e = getenv("QB200_JET_FUSE");
-        return e == nullptr || e[0] != '0';
-    }();
-    return on;
-}
-
-template <>
-bool Plan<float>::tc_forward_jet(int si, int layer, const float* A, float* H, float* Z, int C, qb200_status* st) {
-    const SetState& set = sets_[si];
-    const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    if (!tc_fwd_[layer] || tc_generation() != 2 || !set.jet_fusable || !jet_fusion_enabled() ||
-        !tc2_jet_forward_ok(N, K, C))
-        return false;
-    const float* image = reinterpret_cast<const float*>(tc_image_[layer]);
-    cudaError_t e = tc2_rows_jet_forward_launch(A, K, image, image + (size_t)K * N, K, H, Z, N, bias(layer), set.spec.S, C,
-                                                N, K, set.jet_mode, set.jet_keep, set.jet_w, d_error_, stream_);
-    ++launches_;
-    *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_tma_gemm_kernel(forward, jets) failed: %s", cudaGetErrorString(e));
     return true;
 }
 
@@ -996,12 +935,6 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         qb200_status tc_status = QB200_OK;
         const bool narrow = g.K <= 4 && g.N % 4 == 0 && g.N >= 32 && 256 % (g.N / 4) == 0;
         if (tc_fwd_ok(l - 1) || !narrow) timer_begin(2.0 * (double)rows * g.N * g.K);
-        if (tc_fwd_ok(l - 1) && tc_forward_jet(si, l - 1, H_[l - 1], H_[l], Z_[l], C, &tc_status)) {
-            // H_l and the saved streams of Z_l are written by the GEMM's epilogue: no jet kernel for this layer.
-            QB_TRY(tc_status);
-            timer_end();
-            continue;
-        }
         if (tc_forward(l - 1, H_[l - 1], Z_[l], rows, C, &tc_status)) {
             QB_TRY(tc_status);
             timer_end();

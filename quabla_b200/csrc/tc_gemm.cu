@@ -133,56 +133,15 @@ cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* w
     return cudaGetLastError();
 }
 
-template <bool WGRAD, int BN, bool PRELO, int JET = JET_NONE>
+template <bool WGRAD, int BN, bool PRELO>
 static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mblo, const CUtensorMap& mc,
                            const TcTmaArgs& a, dim3 grid, cudaStream_t stream) {
     typedef T2Geom<WGRAD, BN, PRELO> G;
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN, PRELO, JET>),
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN, PRELO>),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    tc_tma_gemm_kernel<WGRAD, BN, PRELO, JET><<<grid, T2_THREADS_TOTAL, G::SMEM_BYTES, stream>>>(ma, mb, mblo, mc, a);
+    tc_tma_gemm_kernel<WGRAD, BN, PRELO><<<grid, T2_THREADS_TOTAL, G::SMEM_BYTES, stream>>>(ma, mb, mblo, mc, a);
     return cudaGetLastError();
-}
-
-bool tc2_jet_forward_ok(int N, int K, long long points) {
-    return tc_rows_ok(N, K) && N % 128 == 0 && points > 0 && points % T2_BM == 0;
-}
-
-cudaError_t tc2_rows_jet_forward_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* H,
-                                        float* Z, int ldc, const float* bias, int streams, int points, int N, int K,
-                                        const unsigned char* mode, const float* keep, const float* w, int* error,
-                                        cudaStream_t stream) {
-    if (!tc2_jet_forward_ok(N, K, points) || streams < 1 || streams > MAX_STREAMS || Bt_lo == nullptr)
-        return cudaErrorInvalidValue;
-    constexpr int BN = 128;
-    const long long M = (long long)streams * points;
-    CUtensorMap ma, mb, mblo, mc;
-    if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&mblo, Bt_lo, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&mc, H, M, N, ldc, 32, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B))
-        return cudaErrorInvalidValue;
-    TcTmaArgs a;
-    memset(&a, 0, sizeof(a));
-    a.C = H;
-    a.Z = Z;
-    a.bias = bias;
-    a.M = (int)M;
-    a.N = N;
-    a.K = K;
-    a.ldc = ldc;
-    a.bias_rows = points;
-    a.units = (points / T2_BM) * (N / BN);  // tiles of one stream plane; a CTA walks all streams of a tile
-    a.jet_streams = streams;
-    a.jet_points = points;
-    for (int s = 0; s < streams; ++s) {
-        a.jet_mode[s] = mode[s];
-        a.jet_keep[s] = keep[s];
-        a.jet_w[s] = w[s];
-    }
-    a.error = error;
-    const dim3 grid(a.units < 148 ? a.units : 148);
-    return launch2<false, 128, true, JET_FORWARD>(ma, mb, mblo, mc, a, grid, stream);
 }
 
 cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,

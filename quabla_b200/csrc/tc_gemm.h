@@ -37,15 +37,6 @@ cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* w
 // given, is Bt's lo plane (tc2_prepare_launch): the kernel loads it instead of computing it per tile.
 cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,
                             const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream);
-// The forward product of one hidden layer with the activation's jet composition in the epilogue
-// (tc_tma_gemm.cuh, JET_FORWARD): A, H and Z are [streams][points][.] planes, H = tanh-jet(A Bt^T + bias),
-// Z receives the pre-activation streams >= 1.  mode/keep/w describe each stream's role (see TcTmaArgs).
-// N % 128 == 0, points % 128 == 0, Bt_lo required.
-bool tc2_jet_forward_ok(int N, int K, long long points);
-cudaError_t tc2_rows_jet_forward_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* H,
-                                        float* Z, int ldc, const float* bias, int streams, int points, int N, int K,
-                                        const unsigned char* mode, const float* keep, const float* w, int* error,
-                                        cudaStream_t stream);
 cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,
                              int rows_per_slice, int* error, cudaStream_t stream);
 

@@ -27,7 +27,6 @@
 #include <cstdint>
 
 #include "fused_mma_kernel.cuh"  // split_tf32, mbarrier helpers
-#include "jet_math.cuh"          // MAX_STREAMS
 #include "tc_gemm.cuh"           // tc_mma, tc_commit, tc_load32
 
 namespace qb {
@@ -46,26 +45,9 @@ struct TcTmaArgs {
     int ldc;
     int bias_rows;
     int k_slice;        // WGRAD: rows per slice (multiple of T2_BK)
-    int units;          // ROWS: output tiles in total (with JET: tiles of one stream plane)
+    int units;          // ROWS: output tiles in total
     int* error;
-    // ROWS with JET != 0: the rows are S stream planes of jet_points rows each (row = s * jet_points + point,
-    // jet_points a multiple of 128), and the activation's jet composition runs in the epilogue.
-    int jet_streams;
-    int jet_points;
-    float* Z;           // JET_FORWARD: pre-activation planes of the streams >= 1, saved for the reverse sweep (ld = ldc)
-    unsigned char jet_mode[MAX_STREAMS];  // per stream: 0 primal, 1 first order, 2 second order or merged
-    float jet_keep[MAX_STREAMS];          // first-order streams: carry = keep * carry + w * z^2
-    float jet_w[MAX_STREAMS];
 };
-
-// Epilogue variants of the ROWS kernel.
-//   JET_FORWARD  C receives H = tanh-jet(Z) instead of Z = A W (+ bias); a CTA walks the S streams of one
-//                tile of 128 points x BN units one after the other.  tanh(z_0) of the tile stays in spare
-//                tensor-memory columns, the one running sum a later stream needs (sum_j w_j z1_j^2 for the
-//                merged stream, z1^2 for a second-order stream) in registers; streams >= 1 also store
-//                their z to Z.  Orders above 2 are not handled (the caller keeps the separate kernels).
-constexpr int JET_NONE = 0;
-constexpr int JET_FORWARD = 1;
 
 // PRELO (ROWS only): the lo plane of the weight operand is not computed per tile but loaded from a
 // second matrix written once per step (tc2_prepare_launch); a stage then holds A, Bt and Bt_lo, the
@@ -178,7 +160,7 @@ __device__ __forceinline__ void t2_arrive(uint64_t* bar) {
 //   empty[stage]  the item's MMAs completed        tcgen05.commit  -> producer (stage reusable)
 // A consumer arrives on ready[buf] of item i only after it drained item i-2, so that arrival
 // also tells the issuer that accumulator buffer `buf` is free.
-template <bool WGRAD, int BN, bool PRELO, int JET>
+template <bool WGRAD, int BN, bool PRELO>
 __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     tc_tma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_c,
@@ -199,9 +181,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     // behind the two accumulator buffers, so an MMA reads only the weight operand from shared memory.
     constexpr bool A_TMEM = !WGRAD;
     constexpr int A_COL0 = 2 * BN;                               // first column of the operand buffers
-    static_assert(JET == JET_NONE || (!WGRAD && BN == 128), "the jet epilogue is built for 128-wide ROWS tiles");
     constexpr int TMEM_COLS = A_TMEM ? (BN == 128 ? 512 : 256) : 2 * BN;  // a power of two >= 32
-    constexpr int STASH_COL0 = A_COL0 + 128;  // JET: 128 spare columns behind the operand buffers (BN = 128)
     constexpr int NH = BN / 2;         // columns drained by one consumer thread
     constexpr int ISSUE_WARP = T2_THREADS / 32 + 1, LOAD_WARP = T2_THREADS / 32;
 
@@ -238,18 +218,12 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
         k_tiles = (k_end - k_begin + T2_BK - 1) / T2_BK;
     } else {
         units = ((int)blockIdx.x < a.units) ? (a.units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-        if (JET != JET_NONE) units *= a.jet_streams;  // every stream of each of this CTA's tiles
         k_tiles = a.K / T2_BK;
     }
     const int items = units * k_tiles;
-    // Tile coordinates of unit u of this CTA.  With JET a unit is (tile, stream), streams fastest.
-    auto unit_tile = [&](int u) { return (int)blockIdx.x + (JET != JET_NONE ? u / a.jet_streams : u) * (int)gridDim.x; };
-    auto unit_m0 = [&](int u) {
-        if (WGRAD) return (int)blockIdx.x * T2_BM;
-        const int m = (unit_tile(u) / n_tiles) * T2_BM;
-        return JET != JET_NONE ? (u % a.jet_streams) * a.jet_points + m : m;
-    };
-    auto unit_n0 = [&](int u) { return WGRAD ? (int)blockIdx.y * BN : (unit_tile(u) % n_tiles) * BN; };
+    // Tile coordinates of unit u of this CTA.
+    auto unit_m0 = [&](int u) { return WGRAD ? (int)blockIdx.x * T2_BM : (((int)blockIdx.x + u * (int)gridDim.x) / n_tiles) * T2_BM; };
+    auto unit_n0 = [&](int u) { return WGRAD ? (int)blockIdx.y * BN : (((int)blockIdx.x + u * (int)gridDim.x) % n_tiles) * BN; };
 
     if (warp == LOAD_WARP) {
         // ------------------------------ producer ------------------------------
@@ -350,81 +324,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
         // one tensor-map store per box, issued by one thread and left in flight while the next
         // unit's k-tiles run.  Rows outside the matrix are clipped by the store.
         unsigned char* const staging = smem + G::OUT_OFFSET;
-        float carry[JET == JET_FORWARD ? NH : 1];  // see JET_FORWARD
-        auto write_out_jet = [&](int u) {
-            if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging is free again
-            asm volatile("bar.sync 1, %0;" ::"n"(T2_THREADS) : "memory");
-            const int m0 = unit_m0(u), n0 = unit_n0(u);
-            const int st = u % a.jet_streams;
-            const int mode = a.jet_mode[st];
-            const float keep = a.jet_keep[st], w = a.jet_w[st];
-            const uint32_t stash = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(STASH_COL0 + half * NH);
-            float* const zrow = a.Z + (size_t)(m0 + trow) * a.ldc + n0 + half * NH;
-#pragma unroll
-            for (int j = 0; j < NH / 16; ++j) {
-                uint32_t tv[16];
-                float hv[16];
-                if (mode == 0) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float z = acc[j * 16 + i];
-                        if (a.bias != nullptr) z += __ldg(a.bias + n0 + half * NH + j * 16 + i);
-                        hv[i] = tanhf(z);
-                        tv[i] = __float_as_uint(hv[i]);
-                    }
-                    t2_store16(stash + j * 16, tv);
-                } else {
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-                        : "=r"(tv[0]), "=r"(tv[1]), "=r"(tv[2]), "=r"(tv[3]), "=r"(tv[4]), "=r"(tv[5]), "=r"(tv[6]),
-                          "=r"(tv[7]), "=r"(tv[8]), "=r"(tv[9]), "=r"(tv[10]), "=r"(tv[11]), "=r"(tv[12]), "=r"(tv[13]),
-                          "=r"(tv[14]), "=r"(tv[15])
-                        : "r"(stash + j * 16));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float z = acc[j * 16 + i];
-                        const float t = __uint_as_float(tv[i]);
-                        const float t1 = 1.0f - t * t;
-                        if (mode == 1) {
-                            hv[i] = t1 * z;
-                            carry[j * 16 + i] = (keep != 0.0f ? carry[j * 16 + i] : 0.0f) + w * z * z;
-                        } else {
-                            hv[i] = t1 * z + (-2.0f * t * t1) * carry[j * 16 + i];
-                        }
-                    }
-                    // The pre-activation stream goes to Z as it is (16 consecutive floats of this thread's row).
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        *reinterpret_cast<float4*>(zrow + j * 16 + 4 * c) =
-                            make_float4(acc[j * 16 + 4 * c], acc[j * 16 + 4 * c + 1], acc[j * 16 + 4 * c + 2],
-                                        acc[j * 16 + 4 * c + 3]);
-                }
-                unsigned char* box = staging + (half * (NH / 32) + j / 2) * (T2_BM * 128) + trow * 128;
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<float4*>(box + ((((j & 1) * 4 + c) ^ (trow & 7)) << 4)) =
-                        make_float4(hv[4 * c], hv[4 * c + 1], hv[4 * c + 2], hv[4 * c + 3]);
-            }
-            if (mode == 0) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("bar.sync 1, %0;" ::"n"(T2_THREADS) : "memory");
-            if (tid == 0) {
-#pragma unroll
-                for (int j = 0; j < BN / 32; ++j)
-                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&map_c),
-                                 "r"(n0 + 32 * j), "r"(m0), "r"(smem_u32(staging + j * (T2_BM * 128)))
-                                 : "memory");
-                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            }
-        };
         auto write_out = [&](int u) {
-            if (JET == JET_FORWARD) {
-                write_out_jet(u);
-                return;
-            }
             if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging is free again
             asm volatile("bar.sync 1, %0;" ::"n"(T2_THREADS) : "memory");
             const int m0 = unit_m0(u), n0 = unit_n0(u);

@@ -34,26 +34,6 @@ def test_wide_float32_network_on_every_gemm_variant(cuda_device, switches):
     assert result["max_error"] <= TOLERANCE[np.dtype(np.float32)]
 
 
-@pytest.mark.parametrize("points,switches", [
-    (640, {}), (640, {"QB200_MERGE": "0"}), (1024, {"QB200_CHUNK_POINTS": "256"}),
-    (1024, {"QB200_CHUNK_POINTS": "256", "QB200_MERGE": "0"}), (600, {})],
-    ids=["merged stream", "second-order streams", "four chunks", "four chunks, second-order streams", "ragged rows"])
-def test_jets_composed_in_the_gemm_epilogue_match_the_separate_kernels(cuda_device, points, switches):
-    # Hidden layers of width 256: the tcgen05 GEMM composes the tanh jets in its epilogue when the chunk is
-    # whole tiles of 128 points (QB200_JET_FUSE=0 keeps the separate jet kernels; 600 points is not whole
-    # tiles, so both runs take the separate kernels).  Both meet the gate, and the fused run launches less.
-    fused = _run("heat3d", points, **switches)
-    separate = _run("heat3d", points, QB200_JET_FUSE="0", **switches)
-    assert fused["engine"] == separate["engine"] == 3
-    assert fused["max_error"] <= TOLERANCE[np.dtype(np.float32)]
-    assert separate["max_error"] <= TOLERANCE[np.dtype(np.float32)]
-    assert abs(fused["loss"] - separate["loss"]) <= 1e-5 * abs(separate["loss"])
-    if points % 128 == 0:
-        assert fused["launches"] < separate["launches"]
-    else:
-        assert fused["launches"] == separate["launches"]
-
-
 @pytest.mark.parametrize("switches", [{}, {"QB200_DMMA": "0"}], ids=["fp64 mma", "simt"])
 def test_wide_float64_network_on_every_gemm_variant(cuda_device, switches):
     result = _run("burgers", 1536, **switches)
