@@ -8,11 +8,16 @@
 // and for planes that are not a multiple of 16 bytes.
 //
 // These kernels are HBM-bound: 2*S*plane elements of traffic forward, (3S+1)*plane backward.
+// Blocks have JET_BLOCK = 128 threads: with at most 112 registers per thread such a block fits on an SM beside
+// a CTA of the tensor-core GEMM (320 threads x 160 registers, ~210 KB of shared memory), so the jet kernels of
+// one chunk can run under the GEMMs of another chunk issued on a second stream.
 #pragma once
 #include "fused_kernel.cuh"  // Sig<CODE>, jet_apply
 #include "jet_math.cuh"
 
 namespace qb {
+
+constexpr int JET_BLOCK = 128;
 
 template <typename T>
 struct JetVec;
@@ -65,7 +70,7 @@ __device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act, const MW& 
 
 // H = tanh-jet(Z), all streams.
 template <typename T, int CODE>
-__global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane,
+__global__ void __launch_bounds__(JET_BLOCK) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane,
                                                               int act, MergeW<T> mw) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
@@ -97,7 +102,7 @@ __global__ void __launch_bounds__(256) jet_forward_sig_kernel(const T* __restric
 // not read but formed on the fly as Uhat[s][point] * w_head[unit] (the head layer's data gradient),
 // which saves writing and re-reading that [S][C][d] array.
 template <typename T, int CODE, bool HEAD>
-__global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
+__global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
                                                                T* __restrict__ G, long long plane,
                                                                const T* __restrict__ Uhat, const T* __restrict__ w_head,
                                                                int d, long long C, int act, T* __restrict__ bias_partial,
@@ -161,8 +166,8 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
         for (int i = 0; i < V; ++i) bsum[i] += gl[0][i];
     }
     if (bias_partial != nullptr) {
-        // The block covers 256 V / d rows of the plane: add them in row order, one partial per block.
-        __shared__ T red[256][V];
+        // The block covers JET_BLOCK V / d rows of the plane: add them in row order, one partial per block.
+        __shared__ T red[JET_BLOCK][V];
 #pragma unroll
         for (int i = 0; i < V; ++i) red[threadIdx.x][i] = bsum[i];
         __syncthreads();
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(256) jet_backward_sig_kernel(const T* __restri
 #pragma unroll
             for (int i = 0; i < V; ++i) {
                 T total = red[threadIdx.x][i];
-                for (int r = groups; r < 256; r += groups) total += red[threadIdx.x + r][i];
+                for (int r = groups; r < JET_BLOCK; r += groups) total += red[threadIdx.x + r][i];
                 bias_partial[(long long)blockIdx.x * d + threadIdx.x * V + i] = total;
             }
         }
@@ -189,15 +194,15 @@ inline bool jet_sig_eligible(int code, long long plane, const void* a, const voi
 }
 
 // Whether the backward kernel can also form the bias-gradient partials of a layer of width d:
-// its grid stride (256 V elements per block) must cover whole rows.
+// its grid stride (JET_BLOCK V elements per block) must cover whole rows.
 template <typename T>
 inline bool jet_bias_fusable(int d) {
-    return d >= JetVec<T>::V && d % JetVec<T>::V == 0 && (256 * JetVec<T>::V) % d == 0;
+    return d >= JetVec<T>::V && d % JetVec<T>::V == 0 && (JET_BLOCK * JetVec<T>::V) % d == 0;
 }
 
 inline int jet_sig_grid(long long vectors) {
-    const long long blocks = (vectors + 255) / 256;
-    return (int)(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16);
+    const long long blocks = (vectors + JET_BLOCK - 1) / JET_BLOCK;
+    return (int)(blocks < 148 * 32 ? (blocks < 1 ? 1 : blocks) : 148 * 32);
 }
 
 // Merged codes: SIG_MERGED + 6 / 31 / 156 = two / three / four first-order directions plus the merged
@@ -206,7 +211,7 @@ template <typename T>
 inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, int act, const MergeW<T>& mw,
                                    cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
-#define QB_JET_FWD(CODE) jet_forward_sig_kernel<T, CODE><<<grid, 256, 0, stream>>>(Z, H, plane, act, mw)
+#define QB_JET_FWD(CODE) jet_forward_sig_kernel<T, CODE><<<grid, JET_BLOCK, 0, stream>>>(Z, H, plane, act, mw)
     switch (code) {
         case 0: QB_JET_FWD(0); break;
         case 1: QB_JET_FWD(1); break;
@@ -228,7 +233,7 @@ inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal,
                                          const MergeW<T>& mw, cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
 #define QB_JET_BWD(CODE)                                                                                             \
-    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, 256, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, \
+    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, JET_BLOCK, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, \
                                                                      bias_partial, mw)
     switch (code) {
         case 0: QB_JET_BWD(0); break;

@@ -248,12 +248,12 @@ class Plan final : public qb200_plan {
             timer_events_.push_back(a);
             timer_events_.push_back(b);
         }
-        cudaEventRecord(timer_events_[2 * timer_used_], stream_);
+        cudaEventRecord(timer_events_[2 * timer_used_], cs_);
         timer_flops_ += flops;
     }
     void timer_end() {
         if (!timers_) return;
-        cudaEventRecord(timer_events_[2 * timer_used_ + 1], stream_);
+        cudaEventRecord(timer_events_[2 * timer_used_ + 1], cs_);
         ++timer_used_;
     }
     qb200_status launched(const char* what) {
@@ -285,7 +285,35 @@ class Plan final : public qb200_plan {
     double* d_partials_ = nullptr;
     double* d_clip_ = nullptr;
     int total_partials_ = 0;
-    // chunk scratch
+    // Chunk scratch.  The layer-wise engine keeps two complete sets ("lanes"), each with a stream of its own,
+    // and sends consecutive chunks down alternate lanes: the HBM-bound jet kernels of one chunk then run beside the
+    // tensor-bound GEMMs of the other (a jet block of 128 threads fits on an SM next to a GEMM CTA).  The members
+    // below are the lane in use; select_lane() swaps them on the host between chunks.
+    struct Lane {
+        cudaStream_t stream = nullptr;
+        std::vector<T*> H, Z;
+        T* G[2] = {nullptr, nullptr};
+        T* U = nullptr;
+        T* Uhat = nullptr;
+        T* wpartial = nullptr;
+        double* acc = nullptr;     // gradient accumulators of the chunks that went down this lane
+        cudaEvent_t done = nullptr;
+    };
+    std::vector<Lane> lanes_;
+    cudaStream_t cs_ = nullptr;    // stream of the lane in use
+    cudaEvent_t ev_lanes_ = nullptr;
+    void select_lane(int k) {
+        const Lane& ln = lanes_[k];
+        H_ = ln.H;
+        Z_ = ln.Z;
+        G_[0] = ln.G[0];
+        G_[1] = ln.G[1];
+        U_ = ln.U;
+        Uhat_ = ln.Uhat;
+        wpartial_ = ln.wpartial;
+        d_acc_ = ln.acc;
+        cs_ = ln.stream;
+    }
     std::vector<T*> H_, Z_;
     T* G_[2] = {nullptr, nullptr};
     T* U_ = nullptr;
@@ -369,6 +397,16 @@ void Plan<T>::release() {
     if (ev_ar0_ != nullptr) cudaEventDestroy(ev_ar0_);
     if (ev_ar1_ != nullptr) cudaEventDestroy(ev_ar1_);
     ev_begin_ = ev_end_ = ev_ar0_ = ev_ar1_ = nullptr;
+    for (size_t k = 0; k < lanes_.size(); ++k) {
+        if (lanes_[k].done != nullptr) cudaEventDestroy(lanes_[k].done);
+        if (k > 0 && lanes_[k].stream != nullptr) {
+            cudaStreamSynchronize(lanes_[k].stream);
+            cudaStreamDestroy(lanes_[k].stream);
+        }
+    }
+    lanes_.clear();
+    if (ev_lanes_ != nullptr) cudaEventDestroy(ev_lanes_);
+    ev_lanes_ = nullptr;
     if (ev_fork_ != nullptr) cudaEventDestroy(ev_fork_);
     if (ev_join_ != nullptr) cudaEventDestroy(ev_join_);
     ev_fork_ = ev_join_ = nullptr;
@@ -412,7 +450,6 @@ qb200_status Plan<T>::init() {
     n_params_ = offset;
     QB_TRY(dev_alloc(&d_params_, n_params_));
     QB_TRY(dev_alloc(&d_flat_, 2 + n_params_));
-    QB_TRY(dev_alloc(&d_acc_, n_params_));
     QB_TRY(dev_alloc(&d_ct_, 1));
     QB_TRY(dev_alloc(&d_loss_only_, 1));
     QB_TRY(dev_alloc(&d_clip_, 3));
@@ -462,6 +499,20 @@ qb200_status Plan<T>::init() {
         const long long v = atoll(env);
         if (v > 0) chunk_cap = (int)std::min<long long>(v, 1 << 24);
     }
+    // Two lanes (see Lane) for float64 plans when some point set is large enough to be cut into chunks worth
+    // overlapping; the scratch budget is shared between them.  float32 plans keep one lane: their tcgen05 GEMMs
+    // hold the GPU at its power limit, where running the jet kernels beside them only lowers the clock (measured:
+    // 3-D heat step 125.4 ms with one lane, 127.8 ms with two; Burgers 35.4 ms and 33.4 ms).  QB200_LANES=1 or 2
+    // overrides.
+    int n_lanes = 1;
+    if (!fused_) {
+        long long largest = 0;
+        for (const auto& s : desc_.sets) largest = std::max<long long>(largest, s.n);
+        const char* env = getenv("QB200_LANES");
+        const int asked = env != nullptr ? atoi(env) : 0;
+        if (largest >= 16384 && (asked == 2 || (asked != 1 && sizeof(T) == 8))) n_lanes = 2;
+    }
+    budget /= (size_t)n_lanes;
     size_t max_rows = 0, max_chunk = 0;
     std::vector<size_t> h_elems(L_, 0), z_elems(L_, 0);
     size_t g_elems = 0;
@@ -495,6 +546,8 @@ qb200_status Plan<T>::init() {
         long long chunk = (long long)std::min<size_t>(budget / per_point, (size_t)chunk_cap);
         // Bound the split-K slices of a weight gradient.
         chunk = std::min<long long>(chunk, (long long)K_CHUNK_ROWS * 256 / (long long)S);
+        // With two lanes a set is cut into at least two chunks.
+        if (n_lanes > 1 && s.n >= 16384) chunk = std::min<long long>(chunk, ((s.n + 1) / 2 + 255) / 256 * 256);
         if (chunk >= s.n) {
             chunk = s.n;
         } else {
@@ -568,28 +621,40 @@ qb200_status Plan<T>::init() {
         }
         return QB200_OK;
     }
-    H_.assign(L_, nullptr);
-    Z_.assign(L_, nullptr);
-    scratch_bytes_ = 0;
-    for (int l = 0; l < L_; ++l) {
-        QB_TRY(dev_alloc(&H_[l], h_elems[l]));
-        scratch_bytes_ += h_elems[l] * sizeof(T);
-        if (l >= 1) {
-            QB_TRY(dev_alloc(&Z_[l], z_elems[l]));
-            scratch_bytes_ += z_elems[l] * sizeof(T);
-        }
-    }
     QB_TRY(tc_setup());
-    QB_TRY(dev_alloc(&G_[0], g_elems));
-    QB_TRY(dev_alloc(&G_[1], g_elems));
-    QB_TRY(dev_alloc(&U_, max_rows));
-    QB_TRY(dev_alloc(&Uhat_, max_rows));
     const size_t slices = (max_rows + K_CHUNK_ROWS - 1) / K_CHUNK_ROWS + SM_COUNT + 1;  // see slice_rows()
     // Weight-gradient slices, or the (at most BIAS_SLICES) row slices of a bias gradient.
     const size_t partial_elems = std::max(slices * std::max<size_t>(wmax, (size_t)dmax), (size_t)BIAS_SLICES * dmax);
-    QB_TRY(dev_alloc(&wpartial_, partial_elems));
     wpartial_elems_ = partial_elems;
-    scratch_bytes_ += (2 * g_elems + 2 * max_rows + partial_elems) * sizeof(T);
+    scratch_bytes_ = 0;
+    lanes_.resize(n_lanes);
+    QB_CUDA(cudaEventCreateWithFlags(&ev_lanes_, cudaEventDisableTiming));
+    for (int k = 0; k < n_lanes; ++k) {
+        Lane& ln = lanes_[k];
+        if (k == 0)
+            ln.stream = stream_;
+        else
+            QB_CUDA(cudaStreamCreateWithFlags(&ln.stream, cudaStreamNonBlocking));
+        QB_CUDA(cudaEventCreateWithFlags(&ln.done, cudaEventDisableTiming));
+        ln.H.assign(L_, nullptr);
+        ln.Z.assign(L_, nullptr);
+        for (int l = 0; l < L_; ++l) {
+            QB_TRY(dev_alloc(&ln.H[l], h_elems[l]));
+            scratch_bytes_ += h_elems[l] * sizeof(T);
+            if (l >= 1) {
+                QB_TRY(dev_alloc(&ln.Z[l], z_elems[l]));
+                scratch_bytes_ += z_elems[l] * sizeof(T);
+            }
+        }
+        QB_TRY(dev_alloc(&ln.G[0], g_elems));
+        QB_TRY(dev_alloc(&ln.G[1], g_elems));
+        QB_TRY(dev_alloc(&ln.U, max_rows));
+        QB_TRY(dev_alloc(&ln.Uhat, max_rows));
+        QB_TRY(dev_alloc(&ln.wpartial, partial_elems));
+        QB_TRY(dev_alloc(&ln.acc, n_params_));
+        scratch_bytes_ += (2 * g_elems + 2 * max_rows + partial_elems) * sizeof(T);
+    }
+    select_lane(0);
     return QB200_OK;
 }
 
@@ -869,9 +934,9 @@ bool Plan<float>::tc_forward(int layer, const float* A, float* C, long long rows
     cudaError_t e = tc_generation() == 2
                         ? tc2_rows_launch(A, K, reinterpret_cast<const float*>(tc_image_[layer]),
                                           reinterpret_cast<const float*>(tc_image_[layer]) + (size_t)K * N, K, C, N,
-                                          bias(layer), bias_rows, (int)rows, N, K, d_error_, stream_)
+                                          bias(layer), bias_rows, (int)rows, N, K, d_error_, cs_)
                         : tc_rows_launch(A, K, tc_image_[layer], false, K, N, C, N, bias(layer), bias_rows, (int)rows,
-                                         d_error_, stream_);
+                                         d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(forward) failed: %s", cudaGetErrorString(e));
     return true;
@@ -883,9 +948,9 @@ bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long ro
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
     cudaError_t e = tc_generation() == 2
                         ? tc2_rows_launch(G, N, weight(layer), reinterpret_cast<const float*>(tc_image_[layer]) + 2 * (size_t)K * N,
-                                          N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, stream_)
+                                          N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, cs_)
                         : tc_rows_launch(G, N, tc_image_[layer], true, K, N, Gprev, K, nullptr, 0, (int)rows, d_error_,
-                                         stream_);
+                                         cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(dgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -897,7 +962,7 @@ bool Plan<float>::tc_wgrad(int layer, const float* H, const float* G, long long 
     if (layer < 0 || layer >= L_ || !tc_wgrad_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
     cudaError_t e = (tc_generation() == 2 ? tc2_wgrad_launch : tc_wgrad_launch)(H, K, G, N, wpartial_, (int)rows, K, N,
-                                                                                rows_per_slice, d_error_, stream_);
+                                                                                rows_per_slice, d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(wgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -912,7 +977,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     const std::vector<int>& sz = desc_.sizes;
     const int head = L_ - 1;  // index of the linear output layer
 
-    seed_input_kernel<T><<<grid_for(rows * sz[0], 256), 256, 0, stream_>>>(st.table, st.ncols, point0, C, sz[0], spec,
+    seed_input_kernel<T><<<grid_for(rows * sz[0], 256), 256, 0, cs_>>>(st.table, st.ncols, point0, C, sz[0], spec,
                                                                            st.dirs, H_[0]);
     QB_TRY(launched("seed_input_kernel"));
     for (int l = 1; l <= head; ++l) {
@@ -943,30 +1008,30 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             const int rows_per_block = 256 / (g.N / 4);
             const int grid = (int)std::min<long long>((rows + rows_per_block - 1) / rows_per_block, 148 * 16);
             switch (g.K) {
-                case 1: skinny_forward_kernel<T, 1><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
-                case 2: skinny_forward_kernel<T, 2><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
-                case 3: skinny_forward_kernel<T, 3><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
-                default: skinny_forward_kernel<T, 4><<<grid, 256, 0, stream_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+                case 1: skinny_forward_kernel<T, 1><<<grid, 256, 0, cs_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+                case 2: skinny_forward_kernel<T, 2><<<grid, 256, 0, cs_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+                case 3: skinny_forward_kernel<T, 3><<<grid, 256, 0, cs_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
+                default: skinny_forward_kernel<T, 4><<<grid, 256, 0, cs_>>>(g.A, g.B, g.bias, g.C, rows, g.N, C); break;
             }
             QB_TRY(launched("skinny_forward_kernel"));
         } else {
-            const cudaError_t e = gemm_launch<T, true, true>(g, 1, stream_);
+            const cudaError_t e = gemm_launch<T, true, true>(g, 1, cs_);
             (void)e;  // launched() reads the launch status
             QB_TRY(launched("gemm_kernel(forward)"));
             timer_end();
         }
         const long long plane = (long long)C * sz[l];
         if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], nullptr))
-            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, desc_.activation, st.merge_w, stream_);
+            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, desc_.activation, st.merge_w, cs_);
         else
-            jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], plane, spec, desc_.activation);
+            jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, cs_>>>(Z_[l], H_[l], plane, spec, desc_.activation);
         QB_TRY(launched("jet_forward_kernel"));
     }
-    head_forward_kernel<T><<<grid_for(rows * 32, 256), 256, 0, stream_>>>(H_[head], weight(head), bias(head), U_, rows,
+    head_forward_kernel<T><<<grid_for(rows * 32, 256), 256, 0, cs_>>>(H_[head], weight(head), bias(head), U_, rows,
                                                                           sz[head], C);
     QB_TRY(launched("head_forward_kernel"));
     const T w = (T)desc_.sets[si].weight;
-    residual_kernel<T><<<(C + 255) / 256, 256, 0, stream_>>>(st.table, st.ncols, point0, C, S, U_,
+    residual_kernel<T><<<(C + 255) / 256, 256, 0, cs_>>>(st.table, st.ncols, point0, C, S, U_,
                                                              forward_only ? nullptr : Uhat_, st.prog, d_ct_, w,
                                                              (T)dp_scale_, d_partials_ + partial_slot);
     QB_TRY(launched("residual_kernel"));
@@ -985,7 +1050,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                 timer_end();
                 const int count = d_in * d_out;
                 const int slices = (int)((rows + tc_chunk - 1) / tc_chunk);
-                accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset, count, slices, stream_);
+                accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset, count, slices, cs_);
                 return launched("accumulate_partials_kernel");
             }
         }
@@ -1000,17 +1065,17 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             if (chunk <= K_CHUNK_ROWS) {
                 const dim3 grid((std::max(d_in, d_out) + 255) / 256, slices);
                 if (d_out == 1)
-                    skinny_wgrad_kernel<T, 1, false><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                    skinny_wgrad_kernel<T, 1, false><<<grid, 256, 0, cs_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
                 else if (d_in == 1)
-                    skinny_wgrad_kernel<T, 1, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                    skinny_wgrad_kernel<T, 1, true><<<grid, 256, 0, cs_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
                 else if (d_in == 2)
-                    skinny_wgrad_kernel<T, 2, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                    skinny_wgrad_kernel<T, 2, true><<<grid, 256, 0, cs_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
                 else if (d_in == 3)
-                    skinny_wgrad_kernel<T, 3, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                    skinny_wgrad_kernel<T, 3, true><<<grid, 256, 0, cs_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
                 else
-                    skinny_wgrad_kernel<T, 4, true><<<grid, 256, 0, stream_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
+                    skinny_wgrad_kernel<T, 4, true><<<grid, 256, 0, cs_>>>(Hprev, Gz, wpartial_, rows, d_in, d_out, (int)chunk);
                 QB_TRY(launched("skinny_wgrad_kernel"));
-                accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset, count, slices, stream_);
+                accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset, count, slices, cs_);
                 return launched("accumulate_partials_kernel");
             }
         }
@@ -1032,13 +1097,13 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         g.k_chunk = slice_rows(rows, gemm_output_tiles(d_in, d_out, fp64_tensor), GEMM_BK);
         const int slices = (int)((rows + g.k_chunk - 1) / g.k_chunk);
         timer_begin(2.0 * (double)rows * d_in * d_out);
-        const cudaError_t e = gemm_launch<T, false, true>(g, slices, stream_);
+        const cudaError_t e = gemm_launch<T, false, true>(g, slices, cs_);
         (void)e;
         QB_TRY(launched("gemm_kernel(wgrad)"));
         timer_end();
         const int count = d_in * d_out;
         accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset,
-                                                                                count, slices, stream_);
+                                                                                count, slices, cs_);
         return launched("accumulate_partials_kernel");
     };
     auto bgrad = [&](const T* Gz, int d_out, int leaf) -> qb200_status {
@@ -1050,10 +1115,10 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         const int row_chunk = std::max(256, ((C + want - 1) / want + 7) / 8 * 8);
         const int slices = (C + row_chunk - 1) / row_chunk;
         dim3 grid(col_blocks, slices);
-        colsum_kernel<T><<<grid, 256, 0, stream_>>>(Gz, wpartial_, C, d_out, row_chunk);
+        colsum_kernel<T><<<grid, 256, 0, cs_>>>(Gz, wpartial_, C, d_out, row_chunk);
         QB_TRY(launched("colsum_kernel"));
         accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[leaf].offset,
-                                                                                d_out, slices, stream_);
+                                                                                d_out, slices, cs_);
         return launched("accumulate_partials_kernel");
     };
 
@@ -1067,7 +1132,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
                             jet_sig_eligible<T>(st.sig_code, (long long)C * sz[head], Z_[head], H_[head], G_[cur]) &&
                             (reinterpret_cast<uintptr_t>(weight(head)) & 15) == 0;
     if (!head_fused) {
-        head_backward_kernel<T><<<grid_for(rows * sz[head], 256), 256, 0, stream_>>>(Uhat_, weight(head), G_[cur], rows,
+        head_backward_kernel<T><<<grid_for(rows * sz[head], 256), 256, 0, cs_>>>(Uhat_, weight(head), G_[cur], rows,
                                                                                      sz[head]);
         QB_TRY(launched("head_backward_kernel"));
     }
@@ -1081,15 +1146,15 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         T* bias_partial = bias_fused ? wpartial_ : nullptr;
         if (l == head && head_fused)
             jet_backward_head_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, Uhat_, weight(head), sz[head], C,
-                                        desc_.activation, bias_partial, st.merge_w, stream_);
+                                        desc_.activation, bias_partial, st.merge_w, cs_);
         else if (sig)
             jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, sz[l], desc_.activation, bias_partial,
-                                       st.merge_w, stream_);
+                                       st.merge_w, cs_);
         else
-            jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, stream_>>>(Z_[l], H_[l], G_[cur], plane, spec, desc_.activation);
+            jet_backward_kernel<T><<<grid_for(plane, 256), 256, 0, cs_>>>(Z_[l], H_[l], G_[cur], plane, spec, desc_.activation);
         QB_TRY(launched("jet_backward_kernel"));
         if (bias_fused) {
-            accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[b_leaf_[l - 1]].offset, sz[l], jet_grid, stream_);
+            accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[b_leaf_[l - 1]].offset, sz[l], jet_grid, cs_);
             QB_TRY(launched("accumulate_partials_kernel"));
         }
         QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1], l - 1));
@@ -1115,7 +1180,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             if (tc_dgrad(l - 1, G_[cur], G_[cur ^ 1], rows, &tc_status)) {
                 QB_TRY(tc_status);
             } else {
-                const cudaError_t e = gemm_launch<T, true, false>(g, 1, stream_);
+                const cudaError_t e = gemm_launch<T, true, false>(g, 1, cs_);
                 (void)e;
                 QB_TRY(launched("gemm_kernel(dgrad)"));
             }
@@ -1135,7 +1200,8 @@ qb200_status Plan<T>::run(bool forward_only) {
         timer_used_ = 0;
         timer_flops_ = 0.0;
     }
-    if (!forward_only && !fused_) QB_CUDA(cudaMemsetAsync(d_acc_, 0, n_params_ * sizeof(double), stream_));
+    if (!forward_only && !fused_)
+        for (const Lane& ln : lanes_) QB_CUDA(cudaMemsetAsync(ln.acc, 0, n_params_ * sizeof(double), stream_));
     if (fused_ && fused_tensor_core_) QB_TRY(prepare_weight_images());
     const bool side = fused_ && side_stream_ != nullptr;
     if (side) {
@@ -1144,6 +1210,12 @@ qb200_status Plan<T>::run(bool forward_only) {
         QB_CUDA(cudaStreamWaitEvent(side_stream_, ev_fork_, 0));
     }
     if (!fused_ && tc_any_) QB_TRY(tc_prepare());
+    if (!fused_ && lanes_.size() > 1) {
+        // Tables, weight images and cleared accumulators are ready on the main stream before the other lane starts.
+        QB_CUDA(cudaEventRecord(ev_lanes_, stream_));
+        for (size_t k = 1; k < lanes_.size(); ++k) QB_CUDA(cudaStreamWaitEvent(lanes_[k].stream, ev_lanes_, 0));
+    }
+    int next_lane = 0;
     LossArgs la;
     la.n_sets = (int)sets_.size();
     for (size_t si = 0; si < sets_.size(); ++si) {
@@ -1164,9 +1236,12 @@ qb200_status Plan<T>::run(bool forward_only) {
         }
         for (long long p0 = 0; p0 < n; p0 += st.chunk) {
             const int C = (int)std::min<long long>(st.chunk, n - p0);
+            select_lane(next_lane);
+            next_lane = (next_lane + 1) % (int)lanes_.size();
             QB_TRY(run_chunk((int)si, p0, C, slot, forward_only));
             slot += (C + 255) / 256;
         }
+        select_lane(0);
         if (si == 0 && !forward_only) {
             QB_CUDA(cudaEventRecord(ev_end_, stream_));
             ev_valid_ = true;
@@ -1179,6 +1254,11 @@ qb200_status Plan<T>::run(bool forward_only) {
         QB_CUDA(cudaEventRecord(ev_join_, side_stream_));
         QB_CUDA(cudaStreamWaitEvent(stream_, ev_join_, 0));
     }
+    if (!fused_)
+        for (size_t k = 1; k < lanes_.size(); ++k) {
+            QB_CUDA(cudaEventRecord(lanes_[k].done, lanes_[k].stream));
+            QB_CUDA(cudaStreamWaitEvent(stream_, lanes_[k].done, 0));
+        }
     T* loss_out = forward_only ? d_loss_only_ : d_flat_;
     if (fused_ && !forward_only) {
         const int P = (int)n_params_;
@@ -1193,7 +1273,9 @@ qb200_status Plan<T>::run(bool forward_only) {
                                                     step_status(!forward_only));
     QB_TRY(launched("loss_finalize_kernel"));
     if (!forward_only) {
-        finalize_gradients_kernel<T><<<((int)n_params_ + 255) / 256, 256, 0, stream_>>>(d_acc_, d_flat_ + 1, (int)n_params_);
+        // The lanes' accumulators are added in lane order: the result does not depend on how the lanes overlapped.
+        finalize_gradients_kernel<T><<<((int)n_params_ + 255) / 256, 256, 0, stream_>>>(
+            lanes_[0].acc, lanes_.size() > 1 ? lanes_[1].acc : nullptr, d_flat_ + 1, (int)n_params_);
         QB_TRY(launched("finalize_gradients_kernel"));
         executed_ = true;
     }

@@ -250,9 +250,10 @@ __global__ void __launch_bounds__(256) fused_finalize_kernel(const T* __restrict
 }
 
 template <typename T>
-__global__ void finalize_gradients_kernel(const double* __restrict__ acc, T* __restrict__ grads, int count) {
+__global__ void finalize_gradients_kernel(const double* __restrict__ acc, const double* __restrict__ acc_b,
+                                          T* __restrict__ grads, int count) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < count) grads[i] = (T)acc[i];
+    if (i < count) grads[i] = (T)(acc_b != nullptr ? acc[i] + acc_b[i] : acc[i]);
 }
 
 // Round-to-nearest primitives without FMA contraction, so that the update is
