@@ -377,7 +377,15 @@ def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: i
     local_points = interior.n_points
     # Dominant kernel, from the last timed step: the layer GEMM launches of the layer-wise engines
     # (an event pair around each), the interior set's one fused launch on the fused engines.
+    lanes = plan.query(_lib.Q_LANES)
     if engine in (0, 3):
+        if lanes > 1:
+            # Chunks overlap on two streams in the timed loop, so an event pair there spans more than its kernel:
+            # time the GEMM launches in two more steps with every chunk on one stream (outside the timed loop).
+            plan.set_option(_lib.OPT_SINGLE_LANE, 1)
+            for _ in range(2):
+                trainer.step()
+            plan.synchronize()
         gemm_ns = plan.query(_lib.Q_GEMM_NANOSECONDS)
         gemm_launches = max(1, plan.query(_lib.Q_GEMM_LAUNCHES))
         gemm_flops = float(plan.query(_lib.Q_GEMM_FLOPS))
@@ -386,6 +394,9 @@ def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: i
                   "launches_per_step": int(gemm_launches), "us_per_launch": gemm_ns * 1e-3 / gemm_launches,
                   "flops_per_launch": gemm_flops / gemm_launches, "us_per_step": gemm_ns * 1e-3}
         achieved = gemm_flops / max(gemm_ns, 1) * 1e-3  # FLOP / ns = GFLOP/s; / 1e3 = TFLOP/s
+        if lanes > 1:
+            kernel["timed"] = "two extra steps with the chunks serialised on one stream"
+            plan.set_option(_lib.OPT_SINGLE_LANE, 0)
     else:
         set0_ns = plan.query(_lib.Q_SET0_NANOSECONDS)
         flops = w.flops_per_point(interior.streams) * local_points
@@ -450,6 +461,7 @@ def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: i
         "kernel_frac": achieved / peak if peak else None,
         "step_frac": step_flops / (ms_per_step * 1e-3) / 1e12 / rig.world / peak if peak else None,
         "gpu_launches": int(launches), "allreduce_us_rank0": allreduce_us, "replicas_identical": bool(identical),
+        "lanes": int(lanes),
         "l2": ("256 MB written between timed steps, per-step event brackets" if flush_between else
                f"one event bracket around {steps} back-to-back steps; per-rank working set "
                f"{(scratch + h2d) / 2**30:.1f} GiB > L2"),
@@ -569,7 +581,7 @@ def main() -> None:
             r = measure(rig, name, None, 5, 3, peaks, live, with_e2e=False)
             others[name] = {k: r[k] for k in ("dtype", "interior_points", "ms_per_step", "points_per_s", "engine",
                                               "streams", "step_tflops", "kernel", "kernel_tflops", "peak_tflops",
-                                              "kernel_frac", "replicas_identical", "allreduce_us_rank0")}
+                                              "kernel_frac", "replicas_identical", "allreduce_us_rank0", "lanes")}
 
     kernel = main_result["kernel"]
     traffic = None

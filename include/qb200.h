@@ -96,12 +96,15 @@ typedef enum qb200_query {
     QB200_Q_GEMM_NANOSECONDS = 12,   /* with QB200_OPT_KERNEL_TIMERS: summed device time of the last execute's layer GEMM launches
                                         (tcgen05 / FP64-MMA / SIMT products of the layer-wise engine; 0 on the fused engines) */
     QB200_Q_GEMM_LAUNCHES = 13,      /* ... how many launches that sum covers */
-    QB200_Q_GEMM_FLOPS = 14          /* ... and their 2*M*N*K in total */
+    QB200_Q_GEMM_FLOPS = 14,         /* ... and their 2*M*N*K in total */
+    QB200_Q_LANES = 15               /* streams over which the layer-wise engine spreads consecutive chunks (1 or 2) */
 } qb200_query;
 
 /* Keys of qb200_plan_set_option. */
 typedef enum qb200_option {
-    QB200_OPT_KERNEL_TIMERS = 0      /* non-zero: record a CUDA event pair around every layer GEMM launch */
+    QB200_OPT_KERNEL_TIMERS = 0,     /* non-zero: record a CUDA event pair around every layer GEMM launch */
+    QB200_OPT_SINGLE_LANE = 1        /* non-zero: every chunk on the plan's main stream, so that kernels do not overlap
+                                        and the event pairs of QB200_OPT_KERNEL_TIMERS time one kernel each */
 } qb200_option;
 
 /* Opcodes of the per-point residual program (see qb200_desc_set_program). */

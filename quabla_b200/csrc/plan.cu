@@ -301,6 +301,7 @@ class Plan final : public qb200_plan {
     };
     std::vector<Lane> lanes_;
     cudaStream_t cs_ = nullptr;    // stream of the lane in use
+    bool single_lane_ = false;     // option QB200_OPT_SINGLE_LANE: every chunk down lane 0 (for per-kernel timing)
     cudaEvent_t ev_lanes_ = nullptr;
     void select_lane(int k) {
         const Lane& ln = lanes_[k];
@@ -1237,7 +1238,7 @@ qb200_status Plan<T>::run(bool forward_only) {
         for (long long p0 = 0; p0 < n; p0 += st.chunk) {
             const int C = (int)std::min<long long>(st.chunk, n - p0);
             select_lane(next_lane);
-            next_lane = (next_lane + 1) % (int)lanes_.size();
+            next_lane = single_lane_ ? 0 : (next_lane + 1) % (int)lanes_.size();
             QB_TRY(run_chunk((int)si, p0, C, slot, forward_only));
             slot += (C + 255) / 256;
         }
@@ -1492,6 +1493,7 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
             return QB200_OK;
         }
         case QB200_Q_GEMM_LAUNCHES: *out = (int64_t)timer_used_; return QB200_OK;
+        case QB200_Q_LANES: *out = (int64_t)std::max<size_t>(1, lanes_.size()); return QB200_OK;
         case QB200_Q_GEMM_FLOPS: *out = (int64_t)timer_flops_; return QB200_OK;
         case QB200_Q_SET0_NANOSECONDS: {
             if (!ev_valid_) return fail(QB200_INVALID, "no execute has run yet");
@@ -1519,6 +1521,7 @@ qb200_status Plan<T>::set_option(int key, int64_t value) {
     std::lock_guard<std::recursive_mutex> lock(mutex_);
     switch (key) {
         case QB200_OPT_KERNEL_TIMERS: timers_ = value != 0; return QB200_OK;
+        case QB200_OPT_SINGLE_LANE: single_lane_ = value != 0; return QB200_OK;
         default: return fail(QB200_INVALID, "unknown option key %d", key);
     }
 }
