@@ -535,9 +535,10 @@ def live_peaks(rig: Rig) -> dict:
     return out
 
 
-# DRAM bytes (read + write) per row of one forward/data-gradient launch of tc_tma_gemm_kernel at width 256,
-# from the ncu capture summarised in profiles/tc_tma_gemm_kernel_heat3d.md (874 MB over 448,512 rows).
-TC_GEMM_DRAM_BYTES_PER_ROW = 874e6 / 448512
+# DRAM bytes (read + write) per row of one forward/data-gradient launch of tc_tma_gemm_kernel at width 256, from
+# the ncu capture summarised in profiles/tc_tma_gemm_kernel_heat3d.md (2.50-2.54 TB/s x 299-305 us = 760 MB over
+# the 393,216 rows of a launch; the algorithmic bytes are 2,048 per row: one row of A read, one row of C written).
+TC_GEMM_DRAM_BYTES_PER_ROW = 760e6 / 393216
 
 
 def main() -> None:

@@ -123,9 +123,9 @@ def value_and_grad(spec, inputs: dict, cotangent: float = 1.0, threads: int = 1,
     timing samples); weights are unchanged.
 
     A spec whose sets carry a merged second-order stream (the forward-Laplacian recurrence of the
-    device kernels) is evaluated in its `reference` form, one second-order stream per direction:
+    device kernels) is evaluated in its `unmerged` form, one second-order stream per direction:
     the oracle always computes the formulation pinned against the reference's known answers."""
-    spec = getattr(spec, "reference", None) or spec
+    spec = getattr(spec, "unmerged", None) or spec
     if any(getattr(s, "merge_weights", None) is not None for s in spec.sets):
         raise ValueError("the oracle evaluates unmerged specs only")
     lib = _load()

@@ -46,10 +46,10 @@ class PlanSpec:
     inputs: list[tuple[str, int, int, bool]] = field(default_factory=list)  # (name, rows, cols, retained)
     sets: list[SetSpec] = field(default_factory=list)
     activation: str = "tanh"   # of the hidden layers: "tanh" or "sin"
-    # The same loss with one second-order stream per direction (the formulation the reference's
-    # hessian-and-trace code computes), when some set of this spec uses the merged stream; the CPU
-    # oracle evaluates that one.
-    reference: "PlanSpec | None" = None
+    # The same loss traced without the merged stream (one second-order stream per direction, what
+    # QB200_MERGE=0 traces), when some set of this spec uses the merged stream; None otherwise.  Either
+    # form can be handed to Plan: they compute the same value and gradients with different stream counts.
+    unmerged: "PlanSpec | None" = None
 
     def parameter_shape(self, index: int) -> tuple[int, ...]:
         _, layer, kind = self.parameters[index]

@@ -777,7 +777,7 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
 
     With `merge` (default: on unless QB200_MERGE=0) a set whose residual uses the second derivatives
     along two or more directions only through one weighted sum (a Laplacian, a heat operator) carries
-    that sum as a single stream; `spec.reference` then holds the unmerged spec of the same loss.
+    that sum as a single stream; `spec.unmerged` then holds the unmerged spec of the same loss.
     """
     if merge is None:
         merge = _merge_enabled()
@@ -936,5 +936,5 @@ def build_plan_spec(loss: LossValue, parameters: list[tuple[str, tuple[int, ...]
                                  directions=[(d, m) for d, m in directions], program=program,
                                  merge_weights=merge_weights))
     if merged_any:
-        spec.reference = build_plan_spec(loss, parameters, data, dtype, merge=False)
+        spec.unmerged = build_plan_spec(loss, parameters, data, dtype, merge=False)
     return spec

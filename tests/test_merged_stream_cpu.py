@@ -72,8 +72,8 @@ def test_traced_workloads_carry_the_merged_stream_where_it_applies():
     assert interior.merge_weights == [1.0, 1.0]
     assert interior.program.grad_regs[1] == interior.program.grad_regs[2] == -1  # u_x, u_y are not in the residual
     assert interior.program.grad_regs[3] >= 0
-    assert compiled.spec.reference is not None and compiled.spec.reference.sets[0].streams == 5
-    assert compiled.spec.reference.sets[0].merge_weights is None
+    assert compiled.spec.unmerged is not None and compiled.spec.unmerged.sets[0].streams == 5
+    assert compiled.spec.unmerged.sets[0].merge_weights is None
 
     _, compiled, _ = traced("heat3d", 32)
     interior = compiled.spec.sets[0]
@@ -81,18 +81,18 @@ def test_traced_workloads_carry_the_merged_stream_where_it_applies():
     time = [i for i, (d, _) in enumerate(interior.directions) if d[3] == 1.0]
     assert [w for i, w in enumerate(interior.merge_weights) if i not in time] == pytest.approx([-0.1] * 3)
     assert interior.merge_weights[time[0]] == 0.0
-    assert compiled.spec.reference.sets[0].streams == 8
+    assert compiled.spec.unmerged.sets[0].streams == 8
 
     for name in ("poisson1d", "burgers", "beam"):  # one second-order direction, or none: nothing to merge
         _, compiled, _ = traced(name, 16)
-        assert compiled.spec.reference is None
+        assert compiled.spec.unmerged is None
         assert all(s.merge_weights is None for s in compiled.spec.sets)
 
 
 def test_the_switch_keeps_one_stream_per_direction(monkeypatch):
     monkeypatch.setenv("QB200_MERGE", "0")
     _, compiled, _ = traced("poisson2d", 64)
-    assert compiled.spec.reference is None and compiled.spec.sets[0].streams == 5
+    assert compiled.spec.unmerged is None and compiled.spec.sets[0].streams == 5
 
 
 def test_the_oracle_evaluates_the_reference_formulation():
@@ -100,8 +100,8 @@ def test_the_oracle_evaluates_the_reference_formulation():
 
     w, compiled, inputs = traced("poisson2d", 96)
     loss_a, grads_a = contracted.value_and_grad(compiled.spec, inputs)
-    loss_b, grads_b = contracted.value_and_grad(compiled.spec.reference, inputs)
+    loss_b, grads_b = contracted.value_and_grad(compiled.spec.unmerged, inputs)
     assert loss_a == loss_b and all(np.array_equal(a, b) for a, b in zip(grads_a, grads_b))
-    merged_only = compiled.spec.reference.__class__(**{**compiled.spec.__dict__, "reference": None})
+    merged_only = compiled.spec.unmerged.__class__(**{**compiled.spec.__dict__, "unmerged": None})
     with pytest.raises(ValueError):
         contracted.value_and_grad(merged_only, inputs)
