@@ -156,10 +156,19 @@ void qb200_desc_destroy(qb200_desc* desc);
  * (a1/a2: tensor_ir.rs:4968-4972, elementwise.rs:400-407), the last is Linear. */
 qb200_status qb200_desc_set_network(qb200_desc* desc, const int32_t* sizes, int32_t n_sizes);
 
-/* Activation of the hidden layers: tanh (the default) or sin
- * (UnaryMath kinds and their derivative chains, elementwise.rs:400-407, 416-468).
- * Networks with a sin activation run on the layer-wise engine. */
-typedef enum { QB200_ACT_TANH = 0, QB200_ACT_SIN = 1 } qb200_activation;
+/* Activation of the hidden layers: tanh (the default), sin, or one of the reference's composites: sigmoid and
+ * softplus (crates/quabla-python/src/composite.rs:178-209), silu = x sigmoid(x) and the tanh-approximated gelu
+ * written through sigmoid (python/quabla/_ops.py:475-505); derivative chains of elementwise.rs:400-468.  The jets
+ * of every activation are composed to the order the derivative signature needs (up to 4, plus one for the
+ * reverse sweep).  Networks with an activation other than tanh run on the layer-wise engine. */
+typedef enum {
+    QB200_ACT_TANH = 0,
+    QB200_ACT_SIN = 1,
+    QB200_ACT_SIGMOID = 2,
+    QB200_ACT_SOFTPLUS = 3,
+    QB200_ACT_SILU = 4,
+    QB200_ACT_GELU = 5
+} qb200_activation;
 qb200_status qb200_desc_set_activation(qb200_desc* desc, int32_t activation);
 
 /* A parameter leaf, named as the reference names inputs (pytree path,

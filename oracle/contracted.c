@@ -51,7 +51,7 @@ typedef struct {
     const int* sizes;        /* n_layers + 1 */
     const double* const* W;  /* W[l]: [sizes[l]][sizes[l+1]] row-major */
     const double* const* b;  /* b[l]: [sizes[l+1]] or NULL */
-    int activation;          /* of the hidden layers: 0 tanh, 1 sin (elementwise.rs:400-407) */
+    int activation;          /* of the hidden layers: 0 tanh, 1 sin, 2 sigmoid, 3 softplus, 4 silu, 5 gelu */
 } qbo_net;
 
 typedef struct {
@@ -134,12 +134,90 @@ static void sin_derivs(double z, double* d) {
     d[5] = cs;
 }
 
-/* Activation value and derivatives at the pre-activation z. */
+/* The logistic function as the reference composes it (crates/quabla-python/src/composite.rs:178-199:
+ * where(z > 0, 1/(1+e), e/(1+e)), e = exp(-|z|)) and its derivatives by repeated differentiation of
+ * ds/dz = s - s^2: every derivative is a polynomial in s, built here coefficient by coefficient. */
+static void logistic_derivs(double z, double* d /* [6] */) {
+    const double e = exp(-fabs(z));
+    const double s = z > 0.0 ? 1.0 / (1.0 + e) : e / (1.0 + e);
+    double poly[8] = {0.0, 1.0, 0, 0, 0, 0, 0, 0}; /* k-th derivative = sum_i poly[i] s^i; starts as s itself */
+    int degree = 1;
+    for (int k = 0; k < 6; ++k) {
+        double value = 0.0;
+        for (int i = degree; i >= 0; --i) value = value * s + poly[i];
+        d[k] = value;
+        /* d/dz of sum c_i s^i = sum i c_i s^(i-1) (s - s^2) = sum i c_i (s^i - s^(i+1)) */
+        double next[8] = {0};
+        for (int i = 1; i <= degree; ++i) {
+            next[i] += i * poly[i];
+            next[i + 1] -= i * poly[i];
+        }
+        for (int i = 0; i < 8; ++i) poly[i] = next[i];
+        degree += 1;
+    }
+}
+
+/* Derivatives of x * g(x) from those of g (Leibniz). */
+static void times_x(double x, const double* g, double* d) {
+    d[0] = x * g[0];
+    for (int k = 1; k < 6; ++k) d[k] = x * g[k] + k * g[k - 1];
+}
+
+/* gelu, tanh approximation written through the logistic function: x s(c (x + a x^3)), c = 2 sqrt(2/pi)
+ * (python/quabla/_ops.py:481-505); |x| > 40 returns x or -0 with a constant derivative.  The derivatives of
+ * s(v(x)) come from the Taylor coefficients of the composition, computed by truncated series arithmetic. */
+static void gelu_derivs(double x, double* d) {
+    if (fabs(x) > 40.0) {
+        d[0] = x > 0.0 ? x : -0.0;
+        d[1] = x > 0.0 ? 1.0 : 0.0;
+        d[2] = d[3] = d[4] = d[5] = 0.0;
+        return;
+    }
+    const double c = 2.0 * sqrt(2.0 / 3.14159265358979323846), a = 0.044715;
+    double ds[6];
+    logistic_derivs(c * (x + a * x * x * x), ds);
+    /* v(x + h) - v(x) as a series in h: coefficients u[1..3] */
+    double u[6] = {0.0, c * (1.0 + 3.0 * a * x * x), c * 3.0 * a * x, c * a, 0.0, 0.0};
+    /* g(x + h) = sum_k ds[k]/k! * (u(h))^k, truncated at h^5 */
+    double series[6] = {ds[0], 0, 0, 0, 0, 0};
+    double power[6] = {1.0, 0, 0, 0, 0, 0}; /* u^k */
+    double factorial = 1.0;
+    for (int k = 1; k < 6; ++k) {
+        double next[6] = {0};
+        for (int i = 0; i < 6; ++i)
+            for (int j = 1; i + j < 6; ++j) next[i + j] += power[i] * u[j];
+        for (int i = 0; i < 6; ++i) power[i] = next[i];
+        factorial *= k;
+        for (int i = 0; i < 6; ++i) series[i] += ds[k] / factorial * power[i];
+    }
+    double g[6];
+    factorial = 1.0;
+    for (int k = 0; k < 6; ++k) {
+        if (k > 0) factorial *= k;
+        g[k] = series[k] * factorial;
+    }
+    times_x(x, g, d);
+}
+
+/* Activation value and derivatives at the pre-activation z:
+ * 0 tanh, 1 sin, 2 sigmoid, 3 softplus, 4 silu, 5 gelu. */
 static void activation_derivs(int activation, double z, double* d) {
-    if (activation == 1)
-        sin_derivs(z, d);
-    else
-        tanh_derivs(tanh(z), d);
+    double s[6];
+    switch (activation) {
+        case 1: sin_derivs(z, d); break;
+        case 2: logistic_derivs(z, d); break;
+        case 3: /* relu(z) + log1p(exp(-|z|)) (composite.rs:201-209); derivative: the logistic function */
+            logistic_derivs(z, s);
+            d[0] = (z > 0.0 ? z : 0.0) + log1p(exp(-fabs(z)));
+            for (int k = 1; k < 6; ++k) d[k] = s[k - 1];
+            break;
+        case 4: /* z * sigmoid(z) (python/quabla/_ops.py:475-478) */
+            logistic_derivs(z, s);
+            times_x(z, s, d);
+            break;
+        case 5: gelu_derivs(z, d); break;
+        default: tanh_derivs(tanh(z), d); break;
+    }
 }
 
 /* Faa di Bruno: h_m = d^m tanh(z(s))/ds^m, m = 1..K, from z[m-1] = d^m z/ds^m. */

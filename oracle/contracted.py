@@ -85,7 +85,8 @@ class _Problem:
         self.Wp = (C.POINTER(C.c_double) * n_layers)(*[_dp(w) for w in self.W])
         self.bp = (C.POINTER(C.c_double) * n_layers)(
             *[_dp(b) if b is not None else C.POINTER(C.c_double)() for b in self.b])
-        activation = {"tanh": 0, "sin": 1}[getattr(spec, "activation", "tanh")]
+        activation = {"tanh": 0, "sin": 1, "sigmoid": 2, "softplus": 3, "silu": 4, "gelu": 5}[
+            getattr(spec, "activation", "tanh")]
         self.net = _Net(n_layers, self.sizes, self.Wp, self.bp, activation)
         self.sets = []
         self.keep = []

@@ -9,5 +9,6 @@ backend.  It materialises the [B, in, out] weight-gradient products exactly as
 the reference plan does, so it is meant for small point counts.
 """
 
-from .api import (Tracer, array, cos, erf, erfc, exp, expm1, grad, hessian, jvp, log1p, mean, sin, sum, tan, tanh,  # noqa: F401,A004
-                  trace, value_and_grad, value_and_grad_data_parallel, vmap, zeros)
+from .api import (Tracer, array, cos, erf, erfc, exp, expm1, gelu, grad, hessian, jvp, log1p, mean, relu, sigmoid,  # noqa: F401,A004
+                  silu, sin, softplus, sum, tan, tanh, trace, value_and_grad, value_and_grad_data_parallel, vmap,
+                  where, zeros)

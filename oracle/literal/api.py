@@ -113,6 +113,9 @@ class Tracer:
     def __rtruediv__(self, o):
         return self._binary(o, "div", True)
 
+    def __gt__(self, o):
+        return self._binary(o, "greater")
+
     def __neg__(self):
         g = _current().graph
         return self._wrap(g.sub(g.scalar_constant(0.0), self._here()))
@@ -187,6 +190,58 @@ expm1 = _unary("expm1", np.expm1)
 tan = _unary("tan", np.tan)
 erf = _unary("erf", np.vectorize(math.erf, otypes=[np.float64]))
 erfc = _unary("erfc", np.vectorize(math.erfc, otypes=[np.float64]))
+
+
+def where(condition, on_true, on_false):
+    """Selection by a Bool tracer (python/quabla/_ops.py `where`): operands may be tracers or Python numbers."""
+    g = _current().graph
+    lift = lambda v: v._here() if isinstance(v, Tracer) else g.scalar_constant(float(v))  # noqa: E731
+    return condition._wrap(g.where(condition._here(), lift(on_true), lift(on_false)))
+
+
+# The reference builds these from where / exp / log1p, so that no branch overflows and the gradients of the
+# unselected branch stay finite (crates/quabla-python/src/composite.rs:160-209, python/quabla/_ops.py:475-505).
+# relu's NaN clause (`nan_or`) is left out: the oracle is run on finite inputs.
+def _abs(x):
+    return where(x > 0.0, x, 0.0 - x)
+
+
+def _exp_negative_abs(x):
+    return exp(_abs(x) * -1.0)
+
+
+def relu(x):
+    return where(x > 0.0, x, 0.0)
+
+
+def sigmoid(x):
+    if not isinstance(x, Tracer):
+        x = np.asarray(x, dtype=np.float64)
+        e = np.exp(-np.abs(x))
+        return np.where(x > 0, 1.0 / (1.0 + e), e / (1.0 + e))
+    decay = _exp_negative_abs(x)
+    denominator = decay + 1.0
+    positive = 1.0 / denominator
+    negative = decay / denominator
+    return where(x > 0.0, positive, negative)
+
+
+def softplus(x):
+    return relu(x) + log1p(_exp_negative_abs(x))
+
+
+def silu(x):
+    return x * sigmoid(x)
+
+
+_GELU_SCALE = 2.0 * math.sqrt(2.0 / math.pi)
+
+
+def gelu(x):
+    tail = _abs(x) > 40.0
+    safe = where(tail, 0.0, x)
+    value = safe * sigmoid(safe * (safe * safe * 0.044715 + 1.0) * _GELU_SCALE)
+    return where(tail, where(x > 0.0, x, -0.0), value)
 
 
 def mean(x):

@@ -23,7 +23,7 @@ _UNARY = {"tanh": np.tanh, "sin": np.sin, "cos": np.cos, "exp": np.exp, "log1p":
 
 def _round(value: np.ndarray, dtype: str) -> np.ndarray:
     value = np.asarray(value, dtype=np.float64)
-    if dtype == F32:
+    if dtype == F32:  # Bool nodes hold 0.0 / 1.0 and need no rounding
         return value.astype(np.float32).astype(np.float64)
     return value
 
@@ -80,6 +80,10 @@ def evaluate(graph: Graph, inputs: dict, outputs: list) -> list:
             v = x[0] * x[1]
         elif op == "div":
             v = x[0] / x[1]
+        elif op == "greater":
+            v = np.asarray(np.asarray(x[0]) > np.asarray(x[1]), dtype=np.float64)
+        elif op == "where":
+            v = np.where(np.asarray(x[0]) != 0.0, x[1], x[2])
         elif op == "powi":
             v = _powi(np.asarray(x[0], dtype=np.float64), node.attrs[0])
         elif op == "unary":

@@ -8,7 +8,9 @@ dtype and weakness derived from the value operands (:7029-7074).
 
 Ops: input, scalar_constant, constant, cast, add, sub, mul, div, matmul, sum,
 sum_axis, mean, mean_axis, reshape, transpose, broadcast, powi, unary (tanh,
-sin, cos, exp, log1p, expm1, erf, erfc, tan), slice, pad_slice, concat.
+sin, cos, exp, log1p, expm1, erf, erfc, tan), slice, pad_slice, concat, and the two ops the reference's
+composite activations are built from: greater (a comparison with a Bool result, tensor_ir.rs Greater) and
+where (a selection by a Bool condition, tensor_ir.rs Where).
 """
 
 from __future__ import annotations
@@ -17,7 +19,7 @@ from dataclasses import dataclass
 
 import numpy as np
 
-F32, F64 = "f32", "f64"
+F32, F64, BOOL = "f32", "f64", "bool"
 UNARY_KINDS = ("tanh", "sin", "cos", "exp", "log1p", "expm1", "erf", "erfc", "tan")
 
 
@@ -127,6 +129,22 @@ class Graph:
 
     def div(self, a, b):
         return self._binary("div", a, b)
+
+    def greater(self, a: int, b: int) -> int:
+        """a > b elementwise; the result is a strong Bool node."""
+        shape = broadcast_shape(self.shape(a), self.shape(b))
+        a, b = self._coerce([a, b])
+        return self.push("greater", (a, b), (), shape, BOOL, False)
+
+    def where(self, condition: int, on_true: int, on_false: int) -> int:
+        """where_select: the value operands are coerced like a binary op's; the condition is Bool."""
+        if self.nodes[condition].dtype != BOOL:
+            raise TypeError("where needs a Bool condition")
+        on_true, on_false = self._coerce([on_true, on_false])
+        shape = broadcast_shape(self.shape(condition), broadcast_shape(self.shape(on_true), self.shape(on_false)))
+        dtype = self.nodes[on_true].dtype
+        weak = self.nodes[on_true].weak and self.nodes[on_false].weak
+        return self.push("where", (condition, on_true, on_false), (), shape, dtype, weak)
 
     def powi(self, a: int, exponent: int) -> int:
         return self.push_derived("powi", (a,), (int(exponent),), self.shape(a))

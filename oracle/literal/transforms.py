@@ -192,6 +192,16 @@ def _push_vjp(src: Graph, node_id: int, upstream: int, g: Graph, values: list, c
         contribution = _apply_chain(g, chain, upstream)
         contribution = _reduce_to_shape(g, contribution, node.shape, shape_of(ins[0]))
         _accumulate(g, cot, ins[0], contribution)
+    elif op == "greater":
+        return  # a Bool result carries no cotangent
+    elif op == "where":
+        # where_select(condition, upstream, 0) to the true branch, where_select(condition, 0, upstream) to the
+        # false branch, each reduced to its operand's shape (op/vjp.rs:124-148).
+        zero = g.scalar_constant(0.0)
+        on_true = g.where(values[ins[0]], upstream, zero)
+        on_false = g.where(values[ins[0]], zero, upstream)
+        _accumulate(g, cot, ins[1], _reduce_to_shape(g, on_true, node.shape, shape_of(ins[1])))
+        _accumulate(g, cot, ins[2], _reduce_to_shape(g, on_false, node.shape, shape_of(ins[2])))
     elif op == "concat":
         start = 0
         for i in ins:
@@ -278,6 +288,14 @@ def _push_jvp(g: Graph, node: Node, pairs: list):
             value = g.unary(v, kind)
             chain = _unary_chain(g, kind, v, value)
         return value, _apply_chain(g, chain, t)
+    if op == "greater":
+        value = g.greater(pairs[ins[0]][0], pairs[ins[1]][0])
+        return value, value  # a Bool node has no tangent; the slot is never read
+    if op == "where":
+        # Both the values and the tangents are selected by the primal condition (op/jvp.rs:116-128).
+        condition = pairs[ins[0]][0]
+        (tv, tt), (fv, ft) = pairs[ins[1]], pairs[ins[2]]
+        return g.where(condition, tv, fv), g.where(condition, tt, ft)
     if op == "matmul":
         (lv, lt), (rv, rt) = pairs[ins[0]], pairs[ins[1]]
         left = g.matmul(lt, rv)
@@ -374,7 +392,7 @@ def _batched_op(g: Graph, callee: Graph, node: Node, remap: dict, mapped: list, 
     rank = len(node.shape)
     if op in ("cast", "powi", "unary", "reshape"):
         return op, tuple(remap[i] for i in ins), node.attrs
-    if op in ("add", "sub", "mul", "div", "matmul", "broadcast"):
+    if op in ("add", "sub", "mul", "div", "matmul", "broadcast", "greater", "where"):
         local = []
         for i in ins:
             spliced = remap[i]

@@ -15,7 +15,9 @@ from . import _build
 OK, INVALID, UNSUPPORTED, CUDA_ERROR, NCCL_ERROR, NOT_BOUND, TOO_LARGE = range(7)
 F32, F64 = 0, 1
 WEIGHT, BIAS = 0, 1
-ACT_TANH, ACT_SIN = 0, 1
+ACT_TANH, ACT_SIN, ACT_SIGMOID, ACT_SOFTPLUS, ACT_SILU, ACT_GELU = range(6)
+ACTIVATIONS = {"tanh": ACT_TANH, "sin": ACT_SIN, "sigmoid": ACT_SIGMOID, "softplus": ACT_SOFTPLUS, "silu": ACT_SILU,
+               "gelu": ACT_GELU}
 SGD, ADAM = 0, 1
 REDUCE_SUM, REDUCE_MEAN = 0, 1
 (Q_DEVICE_BUFFER_COUNT, Q_NONFINITE_CLIP_SEEN, Q_STREAM, Q_PARAMETER_COUNT, Q_OUTPUT_COUNT,

@@ -45,7 +45,7 @@ class PlanSpec:
     parameters: list[tuple[str, int, int]] = field(default_factory=list)   # (name, layer, kind)
     inputs: list[tuple[str, int, int, bool]] = field(default_factory=list)  # (name, rows, cols, retained)
     sets: list[SetSpec] = field(default_factory=list)
-    activation: str = "tanh"   # of the hidden layers: "tanh" or "sin"
+    activation: str = "tanh"   # of the hidden layers: one of _lib.ACTIVATIONS
     # The same loss traced without the merged stream (one second-order stream per direction, what
     # QB200_MERGE=0 traces), when some set of this spec uses the merged stream; None otherwise.  Either
     # form can be handed to Plan: they compute the same value and gradients with different stream counts.
@@ -85,7 +85,7 @@ def build_desc(spec: PlanSpec) -> C.c_void_p:
     try:
         _lib.check(lib.qb200_desc_set_network(desc, _int32_array(spec.sizes), len(spec.sizes)))
         if spec.activation != "tanh":
-            _lib.check(lib.qb200_desc_set_activation(desc, {"sin": _lib.ACT_SIN}[spec.activation]))
+            _lib.check(lib.qb200_desc_set_activation(desc, _lib.ACTIVATIONS[spec.activation]))
         for name, layer, kind in spec.parameters:
             _lib.check(lib.qb200_desc_add_parameter(desc, name.encode(), layer, kind))
         for name, rows, cols, retained in spec.inputs:

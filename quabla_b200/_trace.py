@@ -160,7 +160,7 @@ class _Pending:
         self.inputs = inputs
         self.activated = activated  # the activation already applied to the last layer
         self.shape = shape
-        self.activation = activation  # "tanh" or "sin" once a hidden layer has been activated
+        self.activation = activation  # the hidden layers' activation, once one has been applied
 
     @property
     def width(self) -> int:
@@ -360,12 +360,15 @@ class TraceValue:
         return self._like(_Pending([[weight.name, None, d_in, d_out]], inputs, False, a.shape[:-1] + (d_out,)))
 
     def _unary(self, kind: str) -> "TraceValue":
-        if kind in ("tanh", "sin") and isinstance(self.inner, _Pending) and not self.inner.activated:
+        if kind in _lib.ACTIVATIONS and isinstance(self.inner, _Pending) and not self.inner.activated:
             p = self.inner
             if p.activation not in (None, kind):
                 raise _unsupported(f"one network mixes {p.activation} and {kind} activations; hidden layers share one",
                                    kind)
             return self._like(_Pending(p.layers, p.inputs, True, p.shape, kind))
+        if kind in ("sigmoid", "softplus", "silu", "gelu"):
+            raise _unsupported(f"{kind} is supported as the activation of a hidden layer (applied to h @ w + b), "
+                               "not inside a residual expression", kind)
         a = self.array()
         out = np.empty(a.shape, dtype=object)
         flat_in, flat_out = a.reshape(-1), out.reshape(-1)

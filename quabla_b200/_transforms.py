@@ -334,6 +334,29 @@ erf = _unary("erf", np.vectorize(math.erf, otypes=[np.float64]))
 erfc = _unary("erfc", np.vectorize(math.erfc, otypes=[np.float64]))
 
 
+def _host_sigmoid(x):
+    x = np.asarray(x, dtype=np.float64)
+    e = np.exp(-np.abs(x))
+    return np.where(x > 0, 1.0 / (1.0 + e), e / (1.0 + e))
+
+
+def _host_gelu(x):
+    x = np.asarray(x, dtype=np.float64)
+    tail = np.abs(x) > 40.0
+    safe = np.where(tail, 0.0, x)
+    value = safe * _host_sigmoid(safe * (safe * safe * 0.044715 + 1.0) * (2.0 * math.sqrt(2.0 / math.pi)))
+    return np.where(tail, np.where(x > 0.0, x, -0.0), value)
+
+
+# Hidden-layer activations beyond tanh and sin, with the reference's definitions: sigmoid and softplus
+# (crates/quabla-python/src/composite.rs:178-209), silu and the tanh-approximated gelu
+# (python/quabla/_ops.py:475-505).  On traced values they are recognised as the activation of a layer.
+sigmoid = _unary("sigmoid", _host_sigmoid)
+softplus = _unary("softplus", lambda x: np.maximum(x, 0.0) + np.log1p(np.exp(-np.abs(x))))
+silu = _unary("silu", lambda x: np.asarray(x) * _host_sigmoid(x))
+gelu = _unary("gelu", _host_gelu)
+
+
 def mean(x, axis=None):
     if isinstance(x, tr.TraceValue):
         return x.mean(axis)

@@ -268,8 +268,9 @@ qb200_status qb200_desc_set_network(qb200_desc* desc, const int32_t* sizes, int3
 
 qb200_status qb200_desc_set_activation(qb200_desc* desc, int32_t activation) {
     if (desc == nullptr) return fail(QB200_INVALID, "set_activation needs a description");
-    if (activation != QB200_ACT_TANH && activation != QB200_ACT_SIN)
-        return fail(QB200_UNSUPPORTED, "activation %d is not supported: tanh (0) or sin (1)", activation);
+    if (activation < QB200_ACT_TANH || activation > QB200_ACT_GELU)
+        return fail(QB200_UNSUPPORTED, "activation %d is not supported: tanh (0), sin (1), sigmoid (2), softplus (3), "
+                                       "silu (4) or gelu (5)", activation);
     desc->activation = activation;
     return QB200_OK;
 }

@@ -58,6 +58,32 @@ __device__ __forceinline__ void qb_sincos(double x, double* s, double* c) { sinc
 // Hidden-layer activations (qb200_activation in the C ABI).
 constexpr int ACT_TANH = 0;
 constexpr int ACT_SIN = 1;
+constexpr int ACT_SIGMOID = 2;
+constexpr int ACT_SOFTPLUS = 3;
+constexpr int ACT_SILU = 4;
+constexpr int ACT_GELU = 5;
+
+__device__ __forceinline__ float qb_exp(float x) { return expf(x); }
+__device__ __forceinline__ double qb_exp(double x) { return exp(x); }
+__device__ __forceinline__ float qb_log1p(float x) { return log1pf(x); }
+__device__ __forceinline__ double qb_log1p(double x) { return log1p(x); }
+
+// The logistic function s(z) and its first five derivatives, ds[k] = k-th derivative at z.  s is evaluated as
+// the reference composes it, where(z > 0, 1 / (1 + e), e / (1 + e)) with e = exp(-|z|), which never overflows
+// (crates/quabla-python/src/composite.rs:178-199); the derivatives are polynomials in s: with p = s (1 - s) and
+// q = 1 - 2 s they are p, p q, p (q^2 - 2 p), p q (q^2 - 8 p), p (q^4 - 22 p q^2 + 16 p^2).
+template <typename T>
+__device__ __forceinline__ void logistic_derivs(T z, T* ds) {
+    const T e = qb_exp(-fabs(z));
+    const T s = z > T(0) ? T(1) / (T(1) + e) : e / (T(1) + e);
+    const T p = s * (T(1) - s), q = T(1) - T(2) * s, q2 = q * q;
+    ds[0] = s;
+    ds[1] = p;
+    ds[2] = p * q;
+    ds[3] = p * (q2 - T(2) * p);
+    ds[4] = p * q * (q2 - T(8) * p);
+    ds[5] = p * (q2 * q2 - T(22) * p * q2 + T(16) * p * p);
+}
 
 // t1..t5 = the first five derivatives of the activation at z.  For tanh they are polynomials in
 // t = tanh(z); for sin they cycle through cos, -sin, -cos, sin, cos.
@@ -67,6 +93,55 @@ struct TanhD {
     __device__ __forceinline__ TanhD() {}
     // Activation `act` at z; *value receives the activation itself.
     __device__ __forceinline__ TanhD(T z, int act, T* value) {
+        if (act >= ACT_SIGMOID) {
+            T ds[6];
+            if (act == ACT_GELU) {
+                // x * s(v(x)), v = c (x + a x^3), c = 2 sqrt(2 / pi) (python/quabla/_ops.py:481-505); beyond
+                // |x| = 40 the reference returns x or -0 with a constant derivative.
+                if (fabs(z) > T(40)) {
+                    *value = z > T(0) ? z : T(-0.0);
+                    t1 = z > T(0) ? T(1) : T(0);
+                    t2 = t3 = t4 = t5 = T(0);
+                    return;
+                }
+                const T c = T(1.5957691216057308), a = T(0.044715);
+                const T v1 = c * (T(1) + T(3) * a * z * z), v2 = T(6) * a * c * z, v3 = T(6) * a * c;
+                logistic_derivs(c * (z + a * z * z * z), ds);
+                // Derivatives of S(x) = s(v(x)) (Faa di Bruno; the fourth derivative of v is zero), then of x S(x).
+                const T S0 = ds[0];
+                const T S1 = ds[1] * v1;
+                const T S2 = ds[2] * v1 * v1 + ds[1] * v2;
+                const T S3 = ds[3] * v1 * v1 * v1 + T(3) * ds[2] * v1 * v2 + ds[1] * v3;
+                const T S4 = ds[4] * v1 * v1 * v1 * v1 + T(6) * ds[3] * v1 * v1 * v2 +
+                             ds[2] * (T(3) * v2 * v2 + T(4) * v1 * v3);
+                const T S5 = ds[5] * v1 * v1 * v1 * v1 * v1 + T(10) * ds[4] * v1 * v1 * v1 * v2 +
+                             ds[3] * (T(15) * v1 * v2 * v2 + T(10) * v1 * v1 * v3) + ds[2] * T(10) * v2 * v3;
+                *value = z * S0;
+                t1 = z * S1 + S0;
+                t2 = z * S2 + T(2) * S1;
+                t3 = z * S3 + T(3) * S2;
+                t4 = z * S4 + T(4) * S3;
+                t5 = z * S5 + T(5) * S4;
+                return;
+            }
+            logistic_derivs(z, ds);
+            if (act == ACT_SIGMOID) {
+                *value = ds[0];
+                t1 = ds[1]; t2 = ds[2]; t3 = ds[3]; t4 = ds[4]; t5 = ds[5];
+            } else if (act == ACT_SOFTPLUS) {
+                // relu(z) + log1p(exp(-|z|)) (composite.rs:201-209); its derivative is the logistic function.
+                *value = fmax(z, T(0)) + qb_log1p(qb_exp(-fabs(z)));
+                t1 = ds[0]; t2 = ds[1]; t3 = ds[2]; t4 = ds[3]; t5 = ds[4];
+            } else {  // ACT_SILU: z * s(z) (python/quabla/_ops.py:475-478)
+                *value = z * ds[0];
+                t1 = z * ds[1] + ds[0];
+                t2 = z * ds[2] + T(2) * ds[1];
+                t3 = z * ds[3] + T(3) * ds[2];
+                t4 = z * ds[4] + T(4) * ds[3];
+                t5 = z * ds[5] + T(5) * ds[4];
+            }
+            return;
+        }
         if (act == ACT_SIN) {
             T sn, cs;
             qb_sincos(z, &sn, &cs);

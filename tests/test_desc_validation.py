@@ -119,9 +119,11 @@ def test_activation_is_checked():
     lib = _lib.load()
     desc = C.c_void_p()
     _lib.check(lib.qb200_desc_create(_lib.F32, C.byref(desc)))
-    assert lib.qb200_desc_set_activation(desc, _lib.ACT_SIN) == 0
-    assert lib.qb200_desc_set_activation(desc, 7) == UNSUPPORTED
-    assert "tanh (0) or sin (1)" in lib.qb200_last_error().decode()
+    for code in _lib.ACTIVATIONS.values():
+        assert lib.qb200_desc_set_activation(desc, code) == 0
+    for code in (-1, 6, 7):
+        assert lib.qb200_desc_set_activation(desc, code) == UNSUPPORTED
+        assert "tanh (0), sin (1), sigmoid (2), softplus (3), silu (4) or gelu (5)" in lib.qb200_last_error().decode()
     lib.qb200_desc_destroy(desc)
 
 

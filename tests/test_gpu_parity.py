@@ -143,10 +143,13 @@ def test_trainer_reduces_the_loss(cuda_device):
     assert trainer._executor.device_buffer_count > 0
 
 
+@pytest.mark.parametrize("activation", ["sin", "sigmoid", "softplus", "silu", "gelu"])
 @pytest.mark.parametrize("name", ["poisson1d", "poisson2d", "burgers", "heat3d", "beam"])
-def test_sin_activation_matches_the_oracle(cuda_device, name):
-    # Networks with a sin activation run on the layer-wise engine, whatever their width.
-    w, compiled, inputs = traced(name, SMALL[name], "sin")
+def test_other_activations_match_the_oracle(cuda_device, name, activation):
+    # Networks with an activation other than tanh run on the layer-wise engine, whatever their width; the jets
+    # of every activation go up to the order the workload needs (four on the beam, plus one in the reverse sweep).
+    w, compiled, inputs = traced(name, SMALL[name], activation)
+    assert compiled.spec.activation == activation
     expected_loss, expected_grads = contracted.value_and_grad(compiled.spec, inputs)
     plan = Plan(compiled.spec, 0)
     for key, value in inputs.items():

@@ -141,7 +141,11 @@ def test_vectorised_random_streams_equal_the_scalar_restatement():
 
 @pytest.mark.parametrize("name,points,activation", [
     ("poisson1d", 16, "tanh"), ("poisson2d", 16, "tanh"), ("burgers", 8, "tanh"), ("heat3d", 4, "tanh"),
-    ("beam", 8, "tanh"), ("poisson1d", 16, "sin"), ("burgers", 8, "sin"), ("beam", 8, "sin")])
+    ("beam", 8, "tanh"), ("poisson1d", 16, "sin"), ("burgers", 8, "sin"), ("beam", 8, "sin"),
+    # The reference's composite activations (where / exp / log1p graphs, composite.rs:160-209, _ops.py:475-505)
+    # against closed-form derivative polynomials, to fourth order on the beam:
+    ("poisson1d", 16, "sigmoid"), ("beam", 6, "sigmoid"), ("burgers", 8, "softplus"), ("beam", 6, "softplus"),
+    ("poisson2d", 8, "silu"), ("beam", 6, "silu"), ("burgers", 8, "gelu"), ("beam", 6, "gelu")])
 def test_contracted_oracle_equals_the_literal_oracle(name, points, activation):
     # Literal: the reference's graph transforms and per-node rounding.  Contracted:
     # jets forward, one reverse sweep, float64.  Equal up to rounding.
