@@ -14,6 +14,7 @@ import numpy as _np
 from . import optim, random  # noqa: F401
 from ._errors import QuablaError, TracerError, UnsupportedOperationError  # noqa: F401
 from ._io import load, save  # noqa: F401
+from ._plantext import plan_spec_from_text  # noqa: F401
 from ._transforms import (cos, erf, erfc, exp, expm1, gelu, grad, hessian, jit, jvp, log, log1p, mean,  # noqa: F401,A004
                           reshape, sigmoid, silu, sin, softplus, sqrt, stack, sum, tan, tanh, trace, value_and_grad, vmap)
 
