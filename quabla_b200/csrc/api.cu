@@ -166,15 +166,15 @@ static qb200_status weight_gradient_typed(const void* acts, const void* cots, in
     const int slices = (int)((rows + qb::WGRAD_ROWS_PER_SLICE - 1) / qb::WGRAD_ROWS_PER_SLICE);
     const size_t count = (size_t)d_in * d_out;
     cudaError_t e;
-    if (std::is_same<T, float>::value && qb::tc_enabled() && qb::tc_wgrad_ok(d_in, d_out)) {
+    if (std::is_same<T, float>::value && qb::tc_available() && qb::tc_wgrad_ok(d_in, d_out)) {
         // Tensor-core contraction (tcgen05, 3xTF32); same slices, same reduction.
         const size_t flag_offset = ((size_t)slices * count * sizeof(T) + 15) / 16 * 16;
         int* flag = reinterpret_cast<int*>(static_cast<char*>(scratch) + flag_offset);
         e = cudaMemsetAsync(flag, 0, sizeof(int), stream);
         if (e == cudaSuccess)
-            e = (qb::tc_generation() == 2 ? qb::tc2_wgrad_launch : qb::tc_wgrad_launch)(
-                static_cast<const float*>(acts), d_in, static_cast<const float*>(cots), d_out,
-                static_cast<float*>(scratch), (int)rows, d_in, d_out, qb::WGRAD_ROWS_PER_SLICE, flag, stream);
+            e = qb::tc2_wgrad_launch(static_cast<const float*>(acts), d_in, static_cast<const float*>(cots), d_out,
+                                     static_cast<float*>(scratch), (int)rows, d_in, d_out, qb::WGRAD_ROWS_PER_SLICE, flag,
+                                     stream);
     } else {
         qb::GemmArgs<T> g;
         g.A = static_cast<const T*>(acts);
@@ -649,6 +649,8 @@ qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d
                                  int32_t N, int32_t K, int64_t bias_rows, void* cuda_stream) {
     if (d_a == nullptr || d_w == nullptr || d_c == nullptr) return fail(QB200_INVALID, "matmul_3xtf32 needs A, W and C");
     if (M < 1 || M > (int64_t)1 << 30) return fail(QB200_INVALID, "matmul_3xtf32: M = %lld out of range", (long long)M);
+    if (!qb::tc_available())
+        return fail(QB200_UNSUPPORTED, "matmul_3xtf32 needs the driver's tensor-map encoder (and QB200_TC not set to 0)");
     if (!qb::tc_rows_ok(N, K))
         return fail(QB200_UNSUPPORTED, "matmul_3xtf32 needs N %% 64 == 0, 64 <= N <= 256 and K %% 32 == 0; got N = %d, K = %d", N, K);
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
@@ -656,21 +658,14 @@ qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d
     QB_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&image), (qb::tc_image_words(K, N) + 4) * sizeof(uint32_t), s));
     int* flag = reinterpret_cast<int*>(image + qb::tc_image_words(K, N));
     QB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), s));
-    cudaError_t e;
-    if (qb::tc_generation() == 2) {
-        // TMA kernel: the K-major operand is W transposed, unsplit.
-        float* wt = reinterpret_cast<float*>(image);
-        e = qb::tc2_prepare_launch(static_cast<const float*>(d_w), K, N, wt, wt + (size_t)K * N, wt + 2 * (size_t)K * N, s);
-        if (e == cudaSuccess)
-            e = qb::tc2_rows_launch(static_cast<const float*>(d_a), K, wt, wt + (size_t)K * N, K, static_cast<float*>(d_c), N,
-                                    static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, N, K,
-                                    flag, s);
-    } else {
-        e = qb::tc_prep_launch(static_cast<const float*>(d_w), K, N, image, s);
-        if (e == cudaSuccess)
-            e = qb::tc_rows_launch(static_cast<const float*>(d_a), K, image, false, K, N, static_cast<float*>(d_c), N,
-                                   static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, flag, s);
-    }
+    // The K-major operand is W transposed, unsplit; its lo plane is written beside it.
+    float* wt = reinterpret_cast<float*>(image);
+    cudaError_t e = qb::tc2_prepare_launch(static_cast<const float*>(d_w), K, N, wt, wt + (size_t)K * N,
+                                           wt + 2 * (size_t)K * N, s);
+    if (e == cudaSuccess)
+        e = qb::tc2_rows_launch(static_cast<const float*>(d_a), K, wt, wt + (size_t)K * N, K, static_cast<float*>(d_c), N,
+                                static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, N, K,
+                                flag, s);
     int host_flag = 0;
     if (e == cudaSuccess) e = cudaMemcpyAsync(&host_flag, flag, sizeof(int), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);

@@ -898,7 +898,7 @@ qb200_status Plan<float>::tc_setup() {
     tc_fwd_.assign(L_, 0);
     tc_bwd_.assign(L_, 0);
     tc_wgrad_.assign(L_, 0);
-    if (!tc_enabled()) return QB200_OK;
+    if (!tc_available()) return QB200_OK;
     for (int l = 0; l < L_; ++l) {
         const int K = desc_.sizes[l], N = desc_.sizes[l + 1];
         tc_fwd_[l] = tc_rows_ok(N, K);
@@ -918,10 +918,8 @@ qb200_status Plan<float>::tc_prepare() {
         // forward product.  Image: [W^T | lo(W^T) | lo(W)], K*N floats each.
         const size_t kn = (size_t)desc_.sizes[l] * desc_.sizes[l + 1];
         float* image = reinterpret_cast<float*>(tc_image_[l]);
-        cudaError_t e = tc_generation() == 2
-                            ? tc2_prepare_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], image, image + kn,
-                                                 image + 2 * kn, stream_)
-                            : tc_prep_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], tc_image_[l], stream_);
+        cudaError_t e = tc2_prepare_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], image, image + kn, image + 2 * kn,
+                                           stream_);
         ++launches_;
         if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of tc_prep_weight_kernel failed: %s", cudaGetErrorString(e));
     }
@@ -932,12 +930,9 @@ template <>
 bool Plan<float>::tc_forward(int layer, const float* A, float* C, long long rows, int bias_rows, qb200_status* st) {
     if (!tc_fwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc_generation() == 2
-                        ? tc2_rows_launch(A, K, reinterpret_cast<const float*>(tc_image_[layer]),
-                                          reinterpret_cast<const float*>(tc_image_[layer]) + (size_t)K * N, K, C, N,
-                                          bias(layer), bias_rows, (int)rows, N, K, d_error_, cs_)
-                        : tc_rows_launch(A, K, tc_image_[layer], false, K, N, C, N, bias(layer), bias_rows, (int)rows,
-                                         d_error_, cs_);
+    cudaError_t e = tc2_rows_launch(A, K, reinterpret_cast<const float*>(tc_image_[layer]),
+                                    reinterpret_cast<const float*>(tc_image_[layer]) + (size_t)K * N, K, C, N, bias(layer),
+                                    bias_rows, (int)rows, N, K, d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(forward) failed: %s", cudaGetErrorString(e));
     return true;
@@ -947,11 +942,8 @@ template <>
 bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long rows, qb200_status* st) {
     if (!tc_bwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc_generation() == 2
-                        ? tc2_rows_launch(G, N, weight(layer), reinterpret_cast<const float*>(tc_image_[layer]) + 2 * (size_t)K * N,
-                                          N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, cs_)
-                        : tc_rows_launch(G, N, tc_image_[layer], true, K, N, Gprev, K, nullptr, 0, (int)rows, d_error_,
-                                         cs_);
+    cudaError_t e = tc2_rows_launch(G, N, weight(layer), reinterpret_cast<const float*>(tc_image_[layer]) + 2 * (size_t)K * N,
+                                    N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(dgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -962,8 +954,7 @@ bool Plan<float>::tc_wgrad(int layer, const float* H, const float* G, long long 
                            qb200_status* st) {
     if (layer < 0 || layer >= L_ || !tc_wgrad_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = (tc_generation() == 2 ? tc2_wgrad_launch : tc_wgrad_launch)(H, K, G, N, wpartial_, (int)rows, K, N,
-                                                                                rows_per_slice, d_error_, cs_);
+    cudaError_t e = tc2_wgrad_launch(H, K, G, N, wpartial_, (int)rows, K, N, rows_per_slice, d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(wgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -1041,8 +1032,8 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     auto wgrad = [&](const T* Hprev, const T* Gz, int d_in, int d_out, int leaf, int layer) -> qb200_status {
         {
             qb200_status tc_status = QB200_OK;
-            // Output tiles of the tensor-core kernel: 128 rows of dW by all (first generation) or 128/64 columns.
-            const int tc_col_tiles = tc_generation() == 2 ? d_out / (d_out % 128 == 0 ? 128 : 64) : 1;
+            // Output tiles of the tensor-core kernel: 128 rows of dW by 128 or 64 columns.
+            const int tc_col_tiles = d_out / (d_out % 128 == 0 ? 128 : 64);
             const int tc_chunk = slice_rows(rows, std::max(1, d_in / 128) * std::max(1, tc_col_tiles), 32);
             const bool tc_takes = layer >= 0 && layer < L_ && tc_wgrad_ok_layer(layer);
             if (tc_takes) timer_begin(2.0 * (double)rows * d_in * d_out);

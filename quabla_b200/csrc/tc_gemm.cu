@@ -4,12 +4,11 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "tc_gemm.cuh"
 #include "tc_tma_gemm.cuh"
 
 namespace qb {
 
-bool tc_enabled() {
+static bool tc_switch_on() {
     const char* env = getenv("QB200_TC");
     return !(env != nullptr && strcmp(env, "0") == 0);
 }
@@ -18,70 +17,7 @@ bool tc_rows_ok(int N, int K) { return N % 64 == 0 && N >= 64 && N <= 256 && K %
 
 bool tc_wgrad_ok(int Mw, int N) { return Mw % TC_BM == 0 && N % 64 == 0 && N >= 64 && N <= 256; }
 
-size_t tc_image_words(int K, int N) { return (size_t)4 * K * N; }
-
-cudaError_t tc_prep_launch(const float* w, int K, int N, uint32_t* image, cudaStream_t stream) {
-    const int blocks = (K * N + 255) / 256;
-    tc_prep_weight_kernel<<<blocks < 296 ? blocks : 296, 256, 0, stream>>>(w, K, N, image);
-    return cudaGetLastError();
-}
-
-static size_t smem_bytes(int N) { return (size_t)2 * (2 * TC_BM * TC_BK * 4 + 2 * N * TC_BK * 4) + 64; }
-
-template <bool WGRAD>
-static cudaError_t configure(int N) {
-    return cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_gemm_kernel<WGRAD>),
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(N));
-}
-
-cudaError_t tc_rows_launch(const float* A, int lda, const uint32_t* image, bool backward, int wK, int wN, float* C,
-                           int ldc, const float* bias, int bias_rows, int M, int* error, cudaStream_t stream) {
-    TcGemmArgs a;
-    memset(&a, 0, sizeof(a));
-    const size_t plane = (size_t)wK * wN;
-    a.A = A;
-    a.Bhi = image + (backward ? 2 : 0) * plane;
-    a.Blo = image + (backward ? 3 : 1) * plane;
-    a.C = C;
-    a.bias = bias;
-    a.M = M;
-    a.N = backward ? wK : wN;   // output width
-    a.K = backward ? wN : wK;   // contraction
-    a.lda = lda;
-    a.ldc = ldc;
-    a.bias_rows = bias_rows;
-    a.error = error;
-    cudaError_t e = configure<false>(a.N);
-    if (e != cudaSuccess) return e;
-    tc_gemm_kernel<false><<<(M + TC_BM - 1) / TC_BM, TC_THREADS, smem_bytes(a.N), stream>>>(a);
-    return cudaGetLastError();
-}
-
-cudaError_t tc_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw,
-                            int N, int rows_per_slice, int* error, cudaStream_t stream) {
-    TcGemmArgs a;
-    memset(&a, 0, sizeof(a));
-    a.A = H;
-    a.B = G;
-    a.C = partials;
-    a.M = Mw;
-    a.N = N;
-    a.K = rows;
-    a.lda = ldh;
-    a.ldb = ldg;
-    a.ldc = N;
-    a.k_slice = rows_per_slice;
-    a.error = error;
-    cudaError_t e = configure<true>(N);
-    if (e != cudaSuccess) return e;
-    const int slices = (rows + rows_per_slice - 1) / rows_per_slice;
-    tc_gemm_kernel<true><<<dim3(slices, Mw / TC_BM), TC_THREADS, smem_bytes(N), stream>>>(a);
-    return cudaGetLastError();
-}
-
-// ---------------------------------------------------------------------------
-// Second generation: tensor-map (TMA) operand loads.
-// ---------------------------------------------------------------------------
+size_t tc_image_words(int K, int N) { return (size_t)3 * K * N; }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -99,14 +35,9 @@ static EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-int tc_generation() {
-    static const int generation = [] {
-        const char* env = getenv("QB200_TC");
-        if (env != nullptr && strcmp(env, "0") == 0) return 0;
-        if (env != nullptr && strcmp(env, "1") == 0) return 1;
-        return encode_tiled() != nullptr ? 2 : 1;
-    }();
-    return generation;
+bool tc_available() {
+    static const bool available = tc_switch_on() && encode_tiled() != nullptr;
+    return available;
 }
 
 // Row-major float32 matrix [rows][cols] with leading dimension ld, boxes of box_cols x box_rows,

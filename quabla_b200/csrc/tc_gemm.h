@@ -1,4 +1,4 @@
-// Launchers of the tcgen05 float32 GEMMs (tc_gemm.cuh).
+// Launchers of the tcgen05 float32 GEMMs (tc_tma_gemm.cuh).
 #pragma once
 #include <cuda_runtime.h>
 
@@ -10,25 +10,13 @@ namespace qb {
 // Shapes the tensor-core kernels accept.
 bool tc_rows_ok(int N, int K);     // C[M][N] = A[M][K] * W: N % 64 == 0, 64 <= N <= 256, K % 32 == 0
 bool tc_wgrad_ok(int Mw, int N);   // P = H^T G with H [rows][Mw], G [rows][N]: Mw % 128 == 0, N as above
-bool tc_enabled();                 // QB200_TC=0 switches the tensor-core GEMMs off
+// Whether the tensor-core GEMMs can run: QB200_TC=0 switches them off, and the driver must provide the
+// tensor-map encoder (operands arrive by TMA tensor maps).
+bool tc_available();
 
-// Words of the four pre-split image planes of a weight [K][N].
+// float32 words of the per-layer weight image [W^T | lo(W^T) | lo(W)] of a weight [K][N] (tc2_prepare_launch).
 size_t tc_image_words(int K, int N);
-cudaError_t tc_prep_launch(const float* w, int K, int N, uint32_t* image, cudaStream_t stream);
 
-// C[M][N] = A[M][K] * B (+ bias on the first bias_rows rows); backward selects the image
-// planes that make B = W^T (then K is W's N and N is W's K).
-cudaError_t tc_rows_launch(const float* A, int lda, const uint32_t* image, bool backward, int wK, int wN, float* C,
-                           int ldc, const float* bias, int bias_rows, int M, int* error, cudaStream_t stream);
-
-// partials[z][m][n] = sum over rows of slice z of H[r][m] * G[r][n]; returns the slice count.
-cudaError_t tc_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw,
-                            int N, int rows_per_slice, int* error, cudaStream_t stream);
-
-// Second generation (tc_tma_gemm.cuh): operands by TMA tensor maps, no pre-split images.
-// 0: tensor-core GEMMs off (QB200_TC=0); 1: first generation (QB200_TC=1, or no driver entry point
-// for tensor maps); 2: TMA kernels.
-int tc_generation();
 // wt[n][k] = w[k][n]: the K-major operand of the forward GEMM.
 cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaStream_t stream);
 // One pass over W [K][N]: wt = W^T [N][K], wt_lo = the lo plane of W^T, w_lo = the lo plane of W (each K*N floats).
