@@ -13,7 +13,8 @@ import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
-LIBRARY = os.path.join(_HERE, "libqb200.so")
+# QB200_LIBRARY points the binding at another build of the same sources (A/B comparisons on one GPU box).
+LIBRARY = os.environ.get("QB200_LIBRARY") or os.path.join(_HERE, "libqb200.so")
 SOURCES = ["api.cu", "plan.cu", "static_scratch.cu", "fused.cu", "tc_gemm.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
