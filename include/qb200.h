@@ -160,7 +160,8 @@ qb200_status qb200_desc_set_network(qb200_desc* desc, const int32_t* sizes, int3
  * softplus (crates/quabla-python/src/composite.rs:178-209), silu = x sigmoid(x) and the tanh-approximated gelu
  * written through sigmoid (python/quabla/_ops.py:475-505); derivative chains of elementwise.rs:400-468.  The jets
  * of every activation are composed to the order the derivative signature needs (up to 4, plus one for the
- * reverse sweep).  Networks with an activation other than tanh run on the layer-wise engine. */
+ * reverse sweep).  tanh and sin networks use every engine; the composite activations run on the layer-wise
+ * engine. */
 typedef enum {
     QB200_ACT_TANH = 0,
     QB200_ACT_SIN = 1,

@@ -783,7 +783,8 @@ template <typename T>
 bool Plan<T>::choose_fused() {
     if (const char* env = getenv("QB200_ENGINE"))
         if (std::string(env) == "layerwise") return false;
-    if (desc_.activation != QB200_ACT_TANH) return false;  // the fused kernels are written for tanh
+    // The fused kernels carry tanh and sin; the composite activations run on the layer-wise engine.
+    if (desc_.activation != QB200_ACT_TANH && desc_.activation != QB200_ACT_SIN) return false;
     const int hidden = L_ - 1;
     if (hidden < 1 || hidden > FUSED_MAX_LAYERS || desc_.sizes[0] > 4) return false;
     const int W = desc_.sizes[1];
@@ -866,6 +867,7 @@ qb200_status Plan<T>::run_fused(int si, bool forward_only) {
     for (int j = 0; j < MAX_DIRS; ++j) a.merge_w[j] = sets_[si].merge_w.w[j];
     for (size_t j = 0; j < s.dirs.size(); ++j)
         for (int k = 0; k < a.d0; ++k) a.dirs[j * a.d0 + k] = (T)s.dirs[j][k];
+    a.act = desc_.activation;
     a.prog = st.prog;
     a.cotangent = d_ct_;
     a.weight = (T)s.weight;
