@@ -12,11 +12,11 @@ namespace qb {
 
 namespace {
 
-template <typename T, int W, int CODE>
+template <typename T, int W, int CODE, int ACT>
 FusedEntry<T> make_entry() {
     typedef FusedGeom<T, W, CODE> G;
     FusedEntry<T> e;
-    e.kernel = fused_step_kernel<T, W, CODE>;
+    e.kernel = fused_step_kernel<T, W, CODE, ACT>;
     e.streams = G::S;
     e.tile_points = G::TP;
     e.smem_bytes = G::SMEM_BASE_BYTES;
@@ -27,11 +27,11 @@ FusedEntry<T> make_entry() {
     return e;
 }
 
-template <int CODE, int PG>
+template <int CODE, int PG, int ACT>
 FusedEntry<float> make_mma_entry() {
     typedef MmaGeom<CODE, PG> G;
     FusedEntry<float> e;
-    e.kernel = fused_mma_kernel<CODE, PG>;
+    e.kernel = fused_mma_kernel<CODE, PG, ACT>;
     e.streams = G::S;
     e.tile_points = G::TP;
     e.smem_bytes = G::SMEM_BASE_BYTES;
@@ -58,23 +58,40 @@ bool want_wide_tile() {
 
 }  // namespace
 
-#define QB_MMA_CASE(CODE)                                                                  \
-    if (width == 64 && code == CODE && !want_simt()) {                                      \
-        *out = want_wide_tile() ? make_mma_entry<CODE, 2>() : make_mma_entry<CODE, 1>();   \
-        return true;                                                                        \
+// tanh networks have every variant; sin networks the default ones (tensor-core kernel with two CTAs per SM at
+// width 64, the FP32/FP64-pipe kernel at widths 16 and 32) and otherwise fall to the layer-wise engine.
+#define QB_MMA_CASE(CODE)                                                                                        \
+    if (width == 64 && code == CODE && !want_simt()) {                                                            \
+        if (act == ACT_TANH) {                                                                                    \
+            *out = want_wide_tile() ? make_mma_entry<CODE, 2, ACT_TANH>() : make_mma_entry<CODE, 1, ACT_TANH>(); \
+            return true;                                                                                          \
+        }                                                                                                         \
+        if (!want_wide_tile()) {                                                                                  \
+            *out = make_mma_entry<CODE, 1, ACT_SIN>();                                                            \
+            return true;                                                                                          \
+        }                                                                                                         \
+        return false;                                                                                             \
     }
 
 // Signature codes: 0 = value only; 1 = {1}; 2 = {2}; 3 = {3}; 4 = {4}; 6 = {1,1};
 // 7 = {2,1}; 11 = {1,2}; 12 = {2,2}; SIG_MERGED + 6 / 31 = {1,1} / {1,1,1} plus the merged
 // second-order stream (2-D / 3-D Laplacian).
-#define QB_CASE(T, W, CODE)                           \
-    if (width == W && code == CODE) {                 \
-        *out = make_entry<T, W, CODE>();              \
-        return true;                                  \
+#define QB_CASE(T, W, CODE)                                     \
+    if (width == W && code == CODE) {                           \
+        if (act == ACT_TANH) {                                  \
+            *out = make_entry<T, W, CODE, ACT_TANH>();          \
+            return true;                                        \
+        }                                                       \
+        if (W < 64) {                                           \
+            *out = make_entry<T, (W < 64 ? W : 16), CODE, ACT_SIN>(); \
+            return true;                                        \
+        }                                                       \
+        return false;                                           \
     }
 
 template <>
-bool fused_lookup<float>(int width, int code, FusedEntry<float>* out) {
+bool fused_lookup<float>(int width, int code, int act, FusedEntry<float>* out) {
+    if (act != ACT_TANH && act != ACT_SIN) return false;
     QB_MMA_CASE(0) QB_MMA_CASE(1) QB_MMA_CASE(2) QB_MMA_CASE(4) QB_MMA_CASE(7) QB_MMA_CASE(12)
     QB_MMA_CASE(SIG_MERGED + 6) QB_MMA_CASE(SIG_MERGED + 31)
     QB_CASE(float, 64, 0) QB_CASE(float, 64, 1) QB_CASE(float, 64, 2) QB_CASE(float, 64, 4)
@@ -87,7 +104,8 @@ bool fused_lookup<float>(int width, int code, FusedEntry<float>* out) {
 }
 
 template <>
-bool fused_lookup<double>(int width, int code, FusedEntry<double>* out) {
+bool fused_lookup<double>(int width, int code, int act, FusedEntry<double>* out) {
+    if (act != ACT_TANH && act != ACT_SIN) return false;
     QB_CASE(double, 16, 0) QB_CASE(double, 16, 1) QB_CASE(double, 16, 2) QB_CASE(double, 16, 7)
     QB_CASE(double, 16, 12) QB_CASE(double, 16, SIG_MERGED + 6)
     QB_CASE(double, 32, 0) QB_CASE(double, 32, 1) QB_CASE(double, 32, 2)

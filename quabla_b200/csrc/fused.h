@@ -28,10 +28,10 @@ inline size_t fused_smem_bytes(const FusedEntry<T>& entry, int n_instr) {
     return entry.smem_bytes + (size_t)n_instr * 16 + 16;
 }
 
-// True when a kernel exists for this dtype, hidden width and derivative
-// signature code (sum over directions j of order_j * 5^j).
+// True when a kernel exists for this dtype, hidden width, derivative signature code (sum over
+// directions j of order_j * 5^j) and activation (ACT_TANH or ACT_SIN).
 template <typename T>
-bool fused_lookup(int width, int code, FusedEntry<T>* out);
+bool fused_lookup(int width, int code, int act, FusedEntry<T>* out);
 
 // Launches entry.kernel; sets the shared-memory attribute on first use.
 template <typename T>

@@ -81,7 +81,6 @@ struct FusedArgs {
     long long n_points;
     T dirs[MAX_DIRS * 4];  // [ndirs][d0]
     T merge_w[MAX_DIRS];   // weights of the merged second-order stream (merged signatures only)
-    int act;               // activation of the hidden layers: ACT_TANH or ACT_SIN
     ProgramRef prog;
     const T* cotangent;
     T weight;
@@ -183,19 +182,20 @@ __device__ __forceinline__ void tile_gemm(const T* __restrict__ A, const T* __re
     }
 }
 
-// Derivatives of the fused engines' activations at z; *value receives the activation itself.
-template <typename T>
-__device__ __forceinline__ TanhD<T> fused_activation(T z, int act, T* value) {
-    if (act == ACT_SIN) return TanhD<T>(z, ACT_SIN, value);
+// Derivatives of the fused engines' activations (ACT_TANH or ACT_SIN, a compile-time choice: a run-time switch
+// cost the tensor-core kernel 8 % on the tanh path) at z; *value receives the activation itself.
+template <typename T, int ACT>
+__device__ __forceinline__ TanhD<T> fused_activation(T z, T* value) {
+    if (ACT == ACT_SIN) return TanhD<T>(z, ACT_SIN, value);
     *value = qb_tanh<T>(z);
     return TanhD<T>(*value);
 }
 
 // Forward jet composition on the S streams of one (point, unit); mw: weights of the merged stream.
-template <typename T, typename SG, typename MW>
-__device__ __forceinline__ void jet_apply(T (&v)[SG::S], const MW& mw, int act) {
+template <typename T, typename SG, int ACT, typename MW>
+__device__ __forceinline__ void jet_apply(T (&v)[SG::S], const MW& mw) {
     T t;
-    const TanhD<T> d = fused_activation<T>(v[0], act, &t);
+    const TanhD<T> d = fused_activation<T, ACT>(v[0], &t);
     T hM = T(0);
     if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG, MW>(v, mw), v[SG::MS]);
     v[0] = t;
@@ -258,14 +258,14 @@ __device__ __forceinline__ void jet_apply_transposed_with(const TanhD<T>& d, con
 }
 
 // The same, rebuilding the activation's derivatives from z_0.
-template <typename T, typename SG, typename MW>
-__device__ __forceinline__ void jet_apply_transposed(const T (&z)[SG::S], T (&g)[SG::S], const MW& mw, int act) {
+template <typename T, typename SG, int ACT, typename MW>
+__device__ __forceinline__ void jet_apply_transposed(const T (&z)[SG::S], T (&g)[SG::S], const MW& mw) {
     T unused;
-    const TanhD<T> d = fused_activation<T>(z[0], act, &unused);
+    const TanhD<T> d = fused_activation<T, ACT>(z[0], &unused);
     jet_apply_transposed_with<T, SG, MW>(d, z, g, mw);
 }
 
-template <typename T, int W, int CODE>
+template <typename T, int W, int CODE, int ACT>
 __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_step_kernel(FusedArgs<T> a) {
     typedef FusedGeom<T, W, CODE> G;
     typedef Sig<CODE> SG;
@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_step_kernel(FusedArgs<
                     T v[S];
 #pragma unroll
                     for (int s = 0; s < S; ++s) v[s] = acc[s][i][j];
-                    jet_apply<T, SG>(v, a.merge_w, a.act);
+                    jet_apply<T, SG, ACT>(v, a.merge_w);
 #pragma unroll
                     for (int s = 0; s < S; ++s) acc[s][i][j] = v[s];
                 }
@@ -473,7 +473,7 @@ __global__ void __launch_bounds__(FUSED_THREADS, 1) fused_step_kernel(FusedArgs<
                         z[s] = zs[s][j];
                         g[s] = acc[s][i][j];
                     }
-                    jet_apply_transposed<T, SG>(z, g, a.merge_w, a.act);
+                    jet_apply_transposed<T, SG, ACT>(z, g, a.merge_w);
 #pragma unroll
                     for (int s = 0; s < S; ++s) acc[s][i][j] = g[s];
                 }

@@ -241,7 +241,7 @@ __device__ __forceinline__ void reduce_units_over_points(float (&v)[4], float* d
 #define QB_PHASE(i)
 #endif
 
-template <int CODE, int PG>
+template <int CODE, int PG, int ACT>
 __global__ void __launch_bounds__(128 * PG, 3 - PG) fused_mma_kernel(FusedArgs<float> a) {
     typedef MmaGeom<CODE, PG> G;
     constexpr int THREADS = G::THREADS, NBUF = G::NBUF;
@@ -396,7 +396,7 @@ __global__ void __launch_bounds__(128 * PG, 3 - PG) fused_mma_kernel(FusedArgs<f
                     float v[S];
 #pragma unroll
                     for (int s = 0; s < S; ++s) v[s] = acc[s][j][c];
-                    jet_apply<float, SG>(v, a.merge_w, a.act);
+                    jet_apply<float, SG, ACT>(v, a.merge_w);
 #pragma unroll
                     for (int s = 0; s < S; ++s) acc[s][j][c] = v[s];
                 }
@@ -515,8 +515,8 @@ __global__ void __launch_bounds__(128 * PG, 3 - PG) fused_mma_kernel(FusedArgs<f
                         g0[s] = acc[s][j][2 * i];
                         g1[s] = acc[s][j][2 * i + 1];
                     }
-                    jet_apply_transposed<float, SG>(z0, g0, a.merge_w, a.act);
-                    jet_apply_transposed<float, SG>(z1, g1, a.merge_w, a.act);
+                    jet_apply_transposed<float, SG, ACT>(z0, g0, a.merge_w);
+                    jet_apply_transposed<float, SG, ACT>(z1, g1, a.merge_w);
 #pragma unroll
                     for (int s = 0; s < S; ++s) {
                         acc[s][j][2 * i] = g0[s];

@@ -802,7 +802,7 @@ bool Plan<T>::choose_fused() {
             scale *= 5;
         }
         if (!s.merge_w.empty()) code += SIG_MERGED;
-        if (!fused_lookup<T>(W, code, &fused_entries_[si])) return false;
+        if (!fused_lookup<T>(W, code, desc_.activation, &fused_entries_[si])) return false;
         if (fused_smem_bytes(fused_entries_[si], (int)s.code.size() / 4) > FUSED_MAX_SMEM) return false;
         const long long tiles = (s.n + fused_entries_[si].tile_points - 1) / fused_entries_[si].tile_points;
         fused_grid_[si] = (int)std::min<long long>(tiles, (long long)sms * fused_entries_[si].ctas_per_sm);
@@ -867,7 +867,6 @@ qb200_status Plan<T>::run_fused(int si, bool forward_only) {
     for (int j = 0; j < MAX_DIRS; ++j) a.merge_w[j] = sets_[si].merge_w.w[j];
     for (size_t j = 0; j < s.dirs.size(); ++j)
         for (int k = 0; k < a.d0; ++k) a.dirs[j * a.d0 + k] = (T)s.dirs[j][k];
-    a.act = desc_.activation;
     a.prog = st.prog;
     a.cotangent = d_ct_;
     a.weight = (T)s.weight;
