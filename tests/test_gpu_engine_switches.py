@@ -55,3 +55,35 @@ def test_fused_engine_variants(cuda_device, name, points, switches):
     result = _run(name, points, **switches)
     assert result["engine"] == (1 if switches.get("QB200_FUSED") == "simt" else 2)
     assert result["max_error"] <= TOLERANCE[np.dtype(np.float32)]
+
+
+def test_two_lanes_are_repeatable_and_agree_with_one_lane(cuda_device, monkeypatch):
+    # float64 plans of the layer-wise engine send consecutive chunks down two streams with their own scratch and
+    # accumulators (added in lane order): the result must not depend on how the lanes overlapped, and must agree
+    # with the single-lane order of additions to rounding.
+    from quabla_b200 import _lib
+    from quabla_b200._plan import Plan
+
+    from _util import relative_error, traced
+
+    w, compiled, inputs = traced("burgers", 20480)
+
+    def run(lanes):
+        monkeypatch.setenv("QB200_LANES", lanes)
+        plan = Plan(compiled.spec, 0)
+        for key, value in inputs.items():
+            plan.bind(key, value)
+        assert plan.query(_lib.Q_LANES) == int(lanes)
+        results = []
+        for _ in range(3):
+            plan.execute()
+            results.append([o.copy() for o in plan.outputs()])
+        plan.close()
+        for later in results[1:]:
+            for a, b in zip(results[0], later):
+                assert a.tobytes() == b.tobytes()
+        return results[0]
+
+    two, one = run("2"), run("1")
+    for a, b in zip(two, one):
+        assert relative_error(a, b) <= 1e-12
