@@ -349,7 +349,7 @@ class Rig:
 
 
 ENGINES = {0: "layer-wise (FP64 tensor-core / SIMT GEMMs)", 1: "fused (FP32/FP64 pipe)",
-           2: "fused (tensor cores, 3xTF32 mma)", 3: "layer-wise (tcgen05 3xTF32 GEMMs)"}
+           2: "fused (tensor cores, 3xTF32 mma)", 3: "layer-wise (tcgen05 split-float32 GEMMs)"}
 
 
 def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: int, peaks: dict, live: dict,
@@ -389,10 +389,14 @@ def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: i
         gemm_ns = plan.query(_lib.Q_GEMM_NANOSECONDS)
         gemm_launches = max(1, plan.query(_lib.Q_GEMM_LAUNCHES))
         gemm_flops = float(plan.query(_lib.Q_GEMM_FLOPS))
-        kernel = {"name": "tc_tma_gemm_kernel (tcgen05, 3xTF32)" if engine == 3 else
+        # Tensor-pipe work of the same launches at the bf16 rate: 6 passes per FLOP for a product made of three
+        # tf32 instructions, 4 where the two correction products are bf16 instructions (0 off the tensor pipe).
+        pipe_flops = float(plan.query(_lib.Q_GEMM_PIPE_FLOPS))
+        kernel = {"name": "tc_tma_gemm_kernel (tcgen05: tf32 product + two correction products)" if engine == 3 else
                   "dmma_gemm_kernel (FP64 MMA) / gemm_kernel" if dtype_name == "f64" else "gemm_kernel",
                   "launches_per_step": int(gemm_launches), "us_per_launch": gemm_ns * 1e-3 / gemm_launches,
-                  "flops_per_launch": gemm_flops / gemm_launches, "us_per_step": gemm_ns * 1e-3}
+                  "flops_per_launch": gemm_flops / gemm_launches, "us_per_step": gemm_ns * 1e-3,
+                  "bf16_rate_passes_per_flop": pipe_flops / gemm_flops if gemm_flops else 0.0}
         achieved = gemm_flops / max(gemm_ns, 1) * 1e-3  # FLOP / ns = GFLOP/s; / 1e3 = TFLOP/s
         if lanes > 1:
             kernel["timed"] = "two extra steps with the chunks serialised on one stream"
@@ -401,7 +405,8 @@ def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: i
         set0_ns = plan.query(_lib.Q_SET0_NANOSECONDS)
         flops = w.flops_per_point(interior.streams) * local_points
         kernel = {"name": "fused_mma_kernel" if engine == 2 else "fused_step_kernel", "launches_per_step": 1,
-                  "us_per_launch": set0_ns * 1e-3, "flops_per_launch": flops, "us_per_step": set0_ns * 1e-3}
+                  "us_per_launch": set0_ns * 1e-3, "flops_per_launch": flops, "us_per_step": set0_ns * 1e-3,
+                  "bf16_rate_passes_per_flop": 6.0 if dtype_name == "f32" else 0.0}
         achieved = flops / max(set0_ns, 1) * 1e-3
     allreduce_us = plan.query(_lib.Q_ALLREDUCE_NANOSECONDS) * 1e-3 if rig.world > 1 else 0.0
 
@@ -443,12 +448,15 @@ def measure(rig: Rig, name: str, total_points: int | None, steps: int, warmup: i
     step_flops = (w.flops_per_point(streams) * w.interior_points
                   + sum(w.flops_per_point(s) * n for n, s in w.extra))
     if dtype_name == "f32":
-        # 3xTF32 on the tensor pipe: TF32 runs at half the bf16 rate, three passes per product.  The burst
-        # figure for kernels timed alone in a short step, the sustained one (seconds-long loop under the
-        # power cap) when the timed kernels keep the GPU busy for tens of milliseconds per step.
+        # Split float32 on the tensor pipe: a tf32 instruction runs at half the bf16 rate, so three tf32 products
+        # cost 6 bf16-rate passes per FLOP and a tf32 product with two bf16 correction products costs 4; the
+        # denominator is the bf16 rate over the passes the timed launches actually execute.  The burst figure
+        # for kernels timed alone in a short step, the sustained one (seconds-long loop under the power cap)
+        # when the timed kernels keep the GPU busy for tens of milliseconds per step.
         sustained = kernel["us_per_step"] > 2e4 and "bf16_tflops_sustained" in peaks
-        peak = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"] / 2.0 / 3.0
-        peak_source = f"bf16 {'sustained' if sustained else 'burst'} / 2 (tf32) / 3 (3xTF32 passes)"
+        passes = kernel["bf16_rate_passes_per_flop"] or 6.0
+        peak = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"] / passes
+        peak_source = f"bf16 {'sustained' if sustained else 'burst'} / {passes:.2f} (tensor-pipe passes per FLOP at the bf16 rate)"
     else:
         peak = live.get("dgemm_tflops")
         peak_source = "torch.matmul float64 4096^3, best of 5, timed at start-up of this run"
@@ -614,8 +622,9 @@ def main() -> None:
                      "kernel_us": kernel["us_per_launch"], "flops_per_launch": kernel["flops_per_launch"],
                      "kernel_us_per_step": kernel["us_per_step"],
                      "peak_source": f"{peak_kind}: {main_result['peak_source']}",
-                     "frac_of_tf32_gemm_over_3": (main_result["kernel_tflops"] / (live["tf32_gemm_tflops"] / 3.0)
-                                                  if main_result["dtype"] == "f32" else None)},
+                     # the same fraction against the library's TF32 GEMM timed in this run (tf32 = 2 bf16-rate passes)
+                     "frac_of_library_tf32_gemm": (main_result["kernel_tflops"] * kernel["bf16_rate_passes_per_flop"] / 2.0
+                                                   / live["tf32_gemm_tflops"] if main_result["dtype"] == "f32" else None)},
     }
     if rig.rank == 0:
         if rig.world == 1 and not args.no_cpu_baseline:

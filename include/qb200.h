@@ -97,7 +97,10 @@ typedef enum qb200_query {
                                         (tcgen05 / FP64-MMA / SIMT products of the layer-wise engine; 0 on the fused engines) */
     QB200_Q_GEMM_LAUNCHES = 13,      /* ... how many launches that sum covers */
     QB200_Q_GEMM_FLOPS = 14,         /* ... and their 2*M*N*K in total */
-    QB200_Q_LANES = 15               /* streams over which the layer-wise engine spreads consecutive chunks (1 or 2) */
+    QB200_Q_LANES = 15,              /* streams over which the layer-wise engine spreads consecutive chunks (1 or 2) */
+    QB200_Q_GEMM_PIPE_FLOPS = 16     /* ... the tensor-pipe work of those launches in FLOPs at the bfloat16 rate: 2*M*N*K times 6 where the
+                                        three products of an element are tf32 instructions (tf32 runs at half the bfloat16 rate), times 4
+                                        where the two correction products are bfloat16 instructions; 0 for float64 and SIMT launches */
 } qb200_query;
 
 /* Keys of qb200_plan_set_option. */
@@ -342,11 +345,16 @@ qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void
                                    int32_t d_in, int32_t d_out, void* d_grad, void* cuda_stream);
 
 /* ------------------------------------------------------------------------
- * Stand-alone float32 matrix product on the tensor cores (tcgen05, 3xTF32 split):
+ * Stand-alone float32 matrix product on the tensor cores (tcgen05, split operands):
  *   C[M][N] = A[M][K] * W[K][N]  (+ bias[N] on the first bias_rows rows),
  * the layer contraction h @ W (+ b) of the hot path (a1/a2: tensor_ir.rs:4968-4972,
  * op/batch.rs:58-79) for all streams at once.  N % 64 == 0, 64 <= N <= 256,
  * K % 32 == 0, all arrays row-major float32 on the device.  Synchronises the stream.
+ * Each element is split as x = hi + lo with hi = x rounded to tf32; hi.hi runs as
+ * tf32 instructions and the two correction products lo.x and x.lo as bfloat16
+ * instructions (QB200_TC_COR=tf32 in the environment: all three as tf32 instructions
+ * on truncated hi parts).  Error against a float64 product, K = 64..256: 7e-7 relative
+ * rms (2e-7 with QB200_TC_COR=tf32; a float32 FMA product: 1.5e-7 to 3e-7).
  * ------------------------------------------------------------------------ */
 qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d_bias, void* d_c, int64_t M,
                                  int32_t N, int32_t K, int64_t bias_rows, void* cuda_stream);

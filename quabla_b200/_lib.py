@@ -22,7 +22,8 @@ SGD, ADAM = 0, 1
 REDUCE_SUM, REDUCE_MEAN = 0, 1
 (Q_DEVICE_BUFFER_COUNT, Q_NONFINITE_CLIP_SEEN, Q_STREAM, Q_PARAMETER_COUNT, Q_OUTPUT_COUNT,
  Q_KERNEL_LAUNCHES, Q_FLAT_DEVICE_PTR, Q_SCRATCH_BYTES, Q_STEP_COUNT, Q_ENGINE, Q_SET0_NANOSECONDS,
- Q_ALLREDUCE_NANOSECONDS, Q_GEMM_NANOSECONDS, Q_GEMM_LAUNCHES, Q_GEMM_FLOPS, Q_LANES) = range(16)
+ Q_ALLREDUCE_NANOSECONDS, Q_GEMM_NANOSECONDS, Q_GEMM_LAUNCHES, Q_GEMM_FLOPS, Q_LANES,
+ Q_GEMM_PIPE_FLOPS) = range(17)
 OPT_KERNEL_TIMERS, OPT_SINGLE_LANE = 0, 1
 
 

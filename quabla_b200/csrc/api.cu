@@ -661,7 +661,7 @@ qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d
     // The K-major operand is W transposed, unsplit; its lo plane is written beside it.
     float* wt = reinterpret_cast<float*>(image);
     cudaError_t e = qb::tc2_prepare_launch(static_cast<const float*>(d_w), K, N, wt, wt + (size_t)K * N,
-                                           wt + 2 * (size_t)K * N, s);
+                                           wt + 2 * (size_t)K * N, wt + 3 * (size_t)K * N, s);
     if (e == cudaSuccess)
         e = qb::tc2_rows_launch(static_cast<const float*>(d_a), K, wt, wt + (size_t)K * N, K, static_cast<float*>(d_c), N,
                                 static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, N, K,

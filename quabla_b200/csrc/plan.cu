@@ -227,6 +227,9 @@ class Plan final : public qb200_plan {
     qb200_status check_device_error();
     bool choose_fused();
     bool tc_fwd_ok(int layer) const { return !tc_fwd_.empty() && tc_fwd_[layer]; }
+    bool tc_bwd_ok(int layer) const { return !tc_bwd_.empty() && tc_bwd_[layer]; }
+    // Tensor-pipe passes of a forward or data-gradient product at the bfloat16 rate (QB200_Q_GEMM_PIPE_FLOPS).
+    static double tc_rows_weight() { return tc_cor16() ? 4.0 : 6.0; }
     bool tc_wgrad_ok_layer(int layer) const { return !tc_wgrad_.empty() && tc_wgrad_[layer]; }
     StepStatus<T> step_status(bool with_flat_flag) const {
         StepStatus<T> s;
@@ -237,7 +240,7 @@ class Plan final : public qb200_plan {
     }
     // Device time of the tensor-core GEMM launches (option QB200_OPT_KERNEL_TIMERS): an event pair
     // around each one, summed by query().
-    void timer_begin(double flops) {
+    void timer_begin(double flops, double pipe_weight = 0.0) {
         if (!timers_) return;
         if (timer_events_.size() < 2 * (timer_used_ + 1)) {
             cudaEvent_t a = nullptr, b = nullptr;
@@ -250,6 +253,7 @@ class Plan final : public qb200_plan {
         }
         cudaEventRecord(timer_events_[2 * timer_used_], cs_);
         timer_flops_ += flops;
+        timer_pipe_flops_ += flops * pipe_weight;
     }
     void timer_end() {
         if (!timers_) return;
@@ -343,7 +347,7 @@ class Plan final : public qb200_plan {
     bool timers_ = false;
     std::vector<cudaEvent_t> timer_events_;
     size_t timer_used_ = 0;
-    double timer_flops_ = 0.0;
+    double timer_flops_ = 0.0, timer_pipe_flops_ = 0.0;
 
     bool fused_tensor_core_ = false;
     // layer-wise engine, float32: tcgen05 GEMMs for the layers whose shapes allow it
@@ -916,11 +920,11 @@ qb200_status Plan<float>::tc_prepare() {
     for (int l = 0; l < L_; ++l) {
         if (tc_image_[l] == nullptr) continue;
         // TMA kernels take the weight unsplit plus its lo plane: W itself for the data gradient, W^T for the
-        // forward product.  Image: [W^T | lo(W^T) | lo(W)], K*N floats each.
+        // forward product.  Image: four parts of K*N words (tc_image_words).
         const size_t kn = (size_t)desc_.sizes[l] * desc_.sizes[l + 1];
         float* image = reinterpret_cast<float*>(tc_image_[l]);
         cudaError_t e = tc2_prepare_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], image, image + kn, image + 2 * kn,
-                                           stream_);
+                                           image + 3 * kn, stream_);
         ++launches_;
         if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of tc_prep_weight_kernel failed: %s", cudaGetErrorString(e));
     }
@@ -943,7 +947,9 @@ template <>
 bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long rows, qb200_status* st) {
     if (!tc_bwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc2_rows_launch(G, N, weight(layer), reinterpret_cast<const float*>(tc_image_[layer]) + 2 * (size_t)K * N,
+    // The weight itself is the K-major operand here (its tf32-rounded copy when the corrections run in bfloat16).
+    const float* image = reinterpret_cast<const float*>(tc_image_[layer]);
+    cudaError_t e = tc2_rows_launch(G, N, tc_cor16() ? image + 3 * (size_t)K * N : weight(layer), image + 2 * (size_t)K * N,
                                     N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(dgrad) failed: %s", cudaGetErrorString(e));
@@ -992,7 +998,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         g.k_chunk = g.K;
         qb200_status tc_status = QB200_OK;
         const bool narrow = g.K <= 4 && g.N % 4 == 0 && g.N >= 32 && 256 % (g.N / 4) == 0;
-        if (tc_fwd_ok(l - 1) || !narrow) timer_begin(2.0 * (double)rows * g.N * g.K);
+        if (tc_fwd_ok(l - 1) || !narrow) timer_begin(2.0 * (double)rows * g.N * g.K, tc_fwd_ok(l - 1) ? tc_rows_weight() : 0.0);
         if (tc_forward(l - 1, H_[l - 1], Z_[l], rows, C, &tc_status)) {
             QB_TRY(tc_status);
             timer_end();
@@ -1037,7 +1043,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             const int tc_col_tiles = d_out / (d_out % 128 == 0 ? 128 : 64);
             const int tc_chunk = slice_rows(rows, std::max(1, d_in / 128) * std::max(1, tc_col_tiles), 32);
             const bool tc_takes = layer >= 0 && layer < L_ && tc_wgrad_ok_layer(layer);
-            if (tc_takes) timer_begin(2.0 * (double)rows * d_in * d_out);
+            if (tc_takes) timer_begin(2.0 * (double)rows * d_in * d_out, 6.0);
             if (tc_wgrad(layer, Hprev, Gz, rows, tc_chunk, &tc_status)) {
                 QB_TRY(tc_status);
                 timer_end();
@@ -1169,7 +1175,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             g.bias_rows = 0;
             g.k_chunk = g.K;
             qb200_status tc_status = QB200_OK;
-            timer_begin(2.0 * (double)rows * g.N * g.K);
+            timer_begin(2.0 * (double)rows * g.N * g.K, tc_bwd_ok(l - 1) ? tc_rows_weight() : 0.0);
             if (tc_dgrad(l - 1, G_[cur], G_[cur ^ 1], rows, &tc_status)) {
                 QB_TRY(tc_status);
             } else {
@@ -1192,6 +1198,7 @@ qb200_status Plan<T>::run(bool forward_only) {
     if (!forward_only) {
         timer_used_ = 0;
         timer_flops_ = 0.0;
+        timer_pipe_flops_ = 0.0;
     }
     if (!forward_only && !fused_)
         for (const Lane& ln : lanes_) QB_CUDA(cudaMemsetAsync(ln.acc, 0, n_params_ * sizeof(double), stream_));
@@ -1487,6 +1494,7 @@ qb200_status Plan<T>::query(int key, int64_t* out) {
         case QB200_Q_GEMM_LAUNCHES: *out = (int64_t)timer_used_; return QB200_OK;
         case QB200_Q_LANES: *out = (int64_t)std::max<size_t>(1, lanes_.size()); return QB200_OK;
         case QB200_Q_GEMM_FLOPS: *out = (int64_t)timer_flops_; return QB200_OK;
+        case QB200_Q_GEMM_PIPE_FLOPS: *out = (int64_t)timer_pipe_flops_; return QB200_OK;
         case QB200_Q_SET0_NANOSECONDS: {
             if (!ev_valid_) return fail(QB200_INVALID, "no execute has run yet");
             QB_TRY(use_device());

@@ -13,11 +13,21 @@ static bool tc_switch_on() {
     return !(env != nullptr && strcmp(env, "0") == 0);
 }
 
+// The two correction products of the forward and data-gradient GEMMs run as bfloat16 instructions;
+// QB200_TC_COR=tf32 runs them as tf32 instructions (the plain 3xTF32 scheme).
+bool tc_cor16() {
+    static const bool on = [] {
+        const char* env = getenv("QB200_TC_COR");
+        return !(env != nullptr && strcmp(env, "tf32") == 0);
+    }();
+    return on;
+}
+
 bool tc_rows_ok(int N, int K) { return N % 64 == 0 && N >= 64 && N <= 256 && K % TC_BK == 0 && K >= TC_BK; }
 
 bool tc_wgrad_ok(int Mw, int N) { return Mw % TC_BM == 0 && N % 64 == 0 && N >= 64 && N <= 256; }
 
-size_t tc_image_words(int K, int N) { return (size_t)3 * K * N; }
+size_t tc_image_words(int K, int N) { return (size_t)4 * K * N; }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -58,20 +68,37 @@ cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaSt
     return cudaGetLastError();
 }
 
-cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, cudaStream_t stream) {
+// bfloat16 matrix [rows][cols], boxes of box_cols x box_rows under the 64-byte swizzle.
+static bool make_map16(CUtensorMap* map, const void* base, long long rows, int cols, int ld, int box_cols, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode_tiled()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, float* w_hi,
+                               cudaStream_t stream) {
+    if (tc_cor16()) {
+        t2_prepare16_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), dim3(32, 8), 0, stream>>>(
+            w, K, N, wt, reinterpret_cast<uint16_t*>(wt_lo), reinterpret_cast<uint16_t*>(w_lo), w_hi);
+        return cudaGetLastError();
+    }
     t2_prepare_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), dim3(32, 8), 0, stream>>>(
         w, K, N, wt, reinterpret_cast<uint32_t*>(wt_lo), reinterpret_cast<uint32_t*>(w_lo));
     return cudaGetLastError();
 }
 
-template <bool WGRAD, int BN, bool PRELO>
+template <bool WGRAD, int BN, bool PRELO, bool C16 = false>
 static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mblo, const CUtensorMap& mc,
                            const TcTmaArgs& a, dim3 grid, cudaStream_t stream) {
-    typedef T2Geom<WGRAD, BN, PRELO> G;
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN, PRELO>),
+    typedef T2Geom<WGRAD, BN, PRELO, C16> G;
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(tc_tma_gemm_kernel<WGRAD, BN, PRELO, C16>),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    tc_tma_gemm_kernel<WGRAD, BN, PRELO><<<grid, T2_THREADS_TOTAL, G::SMEM_BYTES, stream>>>(ma, mb, mblo, mc, a);
+    tc_tma_gemm_kernel<WGRAD, BN, PRELO, C16><<<grid, T2_THREADS_TOTAL, G::SMEM_BYTES, stream>>>(ma, mb, mblo, mc, a);
     return cudaGetLastError();
 }
 
@@ -79,9 +106,11 @@ cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const floa
                             const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream) {
     const int BN = N % 128 == 0 ? 128 : 64;
     CUtensorMap ma, mb, mblo, mc;
+    const bool c16 = Bt_lo != nullptr && tc_cor16();  // Bt_lo is then the pair of bfloat16 planes, 2N rows of K
     if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&mblo, Bt_lo != nullptr ? Bt_lo : Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !(c16 ? make_map16(&mblo, Bt_lo, 2LL * N, K, ldb, T2_BK, BN)
+              : make_map(&mblo, Bt_lo != nullptr ? Bt_lo : Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) ||
         !make_map(&mc, C, M, N, ldc, 32, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     TcTmaArgs a;
@@ -96,6 +125,9 @@ cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const floa
     a.units = ((M + T2_BM - 1) / T2_BM) * (N / BN);
     a.error = error;
     const dim3 grid(a.units < 148 ? a.units : 148);
+    if (c16)
+        return BN == 128 ? launch2<false, 128, true, true>(ma, mb, mblo, mc, a, grid, stream)
+                         : launch2<false, 64, true, true>(ma, mb, mblo, mc, a, grid, stream);
     if (Bt_lo != nullptr)
         return BN == 128 ? launch2<false, 128, true>(ma, mb, mblo, mc, a, grid, stream)
                          : launch2<false, 64, true>(ma, mb, mblo, mc, a, grid, stream);

@@ -52,9 +52,20 @@ struct TcTmaArgs {
 // PRELO (ROWS only): the lo plane of the weight operand is not computed per tile but loaded from a
 // second matrix written once per step (tc2_prepare_launch); a stage then holds A, Bt and Bt_lo, the
 // ring has three stages, and the consumers convert the activation tile only.
-template <bool WGRAD, int BN, bool PRELO = false>
+//
+// C16 (with PRELO): the two correction products run as bfloat16 instructions (kind::f16, k = 16 per
+// instruction, half the tensor-pipe time of two tf32 instructions).  Here hi is x rounded to nearest
+// tf32 (not the truncation the tensor core would apply), so |lo| = |x - hi| <= 2^-12 of x's binade, and a
+// correction product multiplies such a lo by a full-size value: rounding either factor to bfloat16
+// (relative error <= 2^-8) leaves an error of the order of 2^-21 of a term, about the float32 rounding
+// of the term itself (measured: 3e-7 relative rms on a 256-long product, as torch's float32 matmul).
+// The weight operand comes prepared: Bt already rounded to tf32, and a pair of bfloat16 planes
+// [bf16(Bt) | bf16(lo(Bt))], each BN rows of 64 bytes per stage (64-byte swizzle).  The consumers write
+// the activation tile's tf32(x), bf16(x) and bf16(lo(x)) to tensor memory.
+template <bool WGRAD, int BN, bool PRELO = false, bool C16 = false>
 struct T2Geom {
     static_assert(!(WGRAD && PRELO), "the weight gradient has no weight operand");
+    static_assert(PRELO || !C16, "bfloat16 corrections need the prepared weight planes");
     static constexpr int STAGES = PRELO ? 3 : T2_STAGES;
     static constexpr int B_BYTES = BN * T2_BK * 4;
     static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES + (PRELO ? B_BYTES : 0);  // multiple of 1024
@@ -81,6 +92,11 @@ __device__ __forceinline__ uint64_t t2_desc_kmajor(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
+// K-major bfloat16 tile under the 64-byte swizzle (layout type 4): rows of 64 bytes, 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t t2_desc_kmajor64(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)4 << 61);
+}
 __device__ __forceinline__ uint64_t t2_desc_mnmajor(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)(4096 >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)1 << 61);
@@ -92,6 +108,11 @@ __device__ __forceinline__ uint32_t t2_idesc(int N, bool mn_major) {
     uint32_t d = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(T2_BM >> 4) << 24);
     if (mn_major) d |= (1u << 15) | (1u << 16);
     return d;
+}
+
+// The same with bfloat16 operands (kind::f16), K-major.
+__device__ __forceinline__ uint32_t t2_idesc16(int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(T2_BM >> 4) << 24);
 }
 
 // One box of a 2-D tensor map into shared memory; completion is counted in bytes on `bar`.
@@ -110,6 +131,9 @@ __device__ __forceinline__ uint32_t t2_lo_bits(uint32_t x) {
     const float d = __uint_as_float(x) - __uint_as_float(x & 0xffffe000u);
     return __float_as_uint(d) + 0x1000u;
 }
+
+// x rounded to the nearest tf32 (ties away from zero), as float32 bits with the low 13 bits clear.
+__device__ __forceinline__ uint32_t t2_round_tf32(uint32_t x) { return (x + 0x1000u) & 0xffffe000u; }
 
 // 32 lanes x 32 consecutive columns into registers; the caller waits (tcgen05.wait::ld) once for
 // all loads it issued.
@@ -130,6 +154,33 @@ __device__ __forceinline__ void t2_store16(uint32_t taddr, const uint32_t (&r)[1
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
         "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// 32 lanes x 8 consecutive columns from registers into tensor memory.
+__device__ __forceinline__ void t2_store8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+// Two float32 values rounded to bfloat16 and packed, `first` in the low half (the lower k index).
+__device__ __forceinline__ uint32_t t2_pack_bf16(float first, float second) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(second), "f"(first));
+    return d;
+}
+
+// D (+)= A * B with bfloat16 operands: A [128 lanes][8 columns, two k per column] in tensor memory, k = 16.
+__device__ __forceinline__ void t2_mma16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
 
@@ -160,12 +211,12 @@ __device__ __forceinline__ void t2_arrive(uint64_t* bar) {
 //   empty[stage]  the item's MMAs completed        tcgen05.commit  -> producer (stage reusable)
 // A consumer arrives on ready[buf] of item i only after it drained item i-2, so that arrival
 // also tells the issuer that accumulator buffer `buf` is free.
-template <bool WGRAD, int BN, bool PRELO>
+template <bool WGRAD, int BN, bool PRELO, bool C16>
 __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     tc_tma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_blo, const __grid_constant__ CUtensorMap map_c,
                        TcTmaArgs a) {
-    typedef T2Geom<WGRAD, BN, PRELO> G;
+    typedef T2Geom<WGRAD, BN, PRELO, C16> G;
     constexpr int STAGES = G::STAGES;
     extern __shared__ unsigned char t2_smem_raw[];
     // Swizzled tiles need 1024-byte alignment.
@@ -241,7 +292,11 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                 if (!WGRAD) {
                     t2_tma_load(stage, &map_a, k0, m0, full + s);               // box {32 k, 128 rows}
                     t2_tma_load(stage + T2_A_BYTES, &map_b, k0, n0, full + s);  // box {32 k, BN rows}
-                    if (PRELO) t2_tma_load(stage + T2_A_BYTES + G::B_BYTES, &map_blo, k0, n0, full + s);
+                    if (PRELO && !C16) t2_tma_load(stage + T2_A_BYTES + G::B_BYTES, &map_blo, k0, n0, full + s);
+                    if (C16) {  // rows n0.. of the bf16(Bt) plane, then of the bf16(lo(Bt)) plane a.N rows further on
+                        t2_tma_load(stage + T2_A_BYTES + G::B_BYTES, &map_blo, k0, n0, full + s);
+                        t2_tma_load(stage + T2_A_BYTES + G::B_BYTES + G::B_BYTES / 2, &map_blo, k0, a.N + n0, full + s);
+                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < T2_BM / 32; ++j) t2_tma_load(stage + j * 4096, &map_a, m0 + 32 * j, k0, full + s);
@@ -273,8 +328,20 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                 // of an MN-major atom.  The small correction products go first (they add onto a
                 // small accumulator without loss), the full-magnitude products last.
                 constexpr uint32_t STEP = WGRAD ? 1024 : 32;
+                if (C16) {
+                    // Operand buffer b: x in columns 0-31, bf16(x) in 32-47, bf16(lo(x)) in 48-63; sixteen k
+                    // (32 bytes of a weight-plane row) per instruction.
+                    const uint32_t idesc16 = t2_idesc16(BN);
+                    const uint32_t b16h = bh + G::B_BYTES, b16l = b16h + G::B_BYTES / 2;
 #pragma unroll
-                for (int kb = 0; kb < T2_BK / 8; ++kb) {
+                    for (int kc = 0; kc < T2_BK / 16; ++kc) {
+                        const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + b * 64 + 32 + kc * 8);
+                        t2_mma16_tmem_a(dst, ta + 16, t2_desc_kmajor64(b16h + kc * 32), idesc16, kc == 0 ? 0u : 1u);
+                        t2_mma16_tmem_a(dst, ta, t2_desc_kmajor64(b16l + kc * 32), idesc16, 1u);
+                    }
+                }
+#pragma unroll
+                for (int kb = 0; kb < (C16 ? 0 : T2_BK / 8); ++kb) {
                     const uint32_t o = kb * STEP;
                     if (WGRAD) {
                         tc_mma(dst, t2_desc_mnmajor(al + o), t2_desc_mnmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
@@ -378,11 +445,27 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                     const uint4 x = *reinterpret_cast<const uint4*>(hi + trow * 128 + chunk * 16);
                     xh[4 * c + 0] = x.x; xh[4 * c + 1] = x.y; xh[4 * c + 2] = x.z; xh[4 * c + 3] = x.w;
                 }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) xl[i] = t2_lo_bits(xh[i]);
                 const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(A_COL0 + b * 64 + half * 16);
-                t2_store16(ta, xh);
-                t2_store16(ta + 32, xl);
+                if (C16) {
+                    uint32_t h16[8], l16[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float x0 = __uint_as_float(xh[2 * i]), x1 = __uint_as_float(xh[2 * i + 1]);
+                        xh[2 * i] = t2_round_tf32(xh[2 * i]);
+                        xh[2 * i + 1] = t2_round_tf32(xh[2 * i + 1]);
+                        h16[i] = t2_pack_bf16(x0, x1);
+                        l16[i] = t2_pack_bf16(x0 - __uint_as_float(xh[2 * i]), x1 - __uint_as_float(xh[2 * i + 1]));
+                    }
+                    t2_store16(ta, xh);
+                    const uint32_t t16 = ta - (uint32_t)(half * 16) + 32 + (uint32_t)(half * 8);
+                    t2_store8(t16, h16);
+                    t2_store8(t16 + 16, l16);
+                } else {
+                    t2_store16(ta, xh);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) xl[i] = t2_lo_bits(xh[i]);
+                    t2_store16(ta + 32, xl);
+                }
                 // Weight tile: lo plane in shared memory, element by element (unless it was loaded).
 #pragma unroll
                 for (int i = 0; i < (PRELO ? 0 : (G::B_BYTES / 16) / T2_THREADS); ++i) {
@@ -459,6 +542,40 @@ __global__ void t2_prepare_kernel(const float* __restrict__ w, int K, int N, flo
             const float v = tile[threadIdx.x][r];
             wt[(size_t)n * K + k] = v;
             wt_lo[(size_t)n * K + k] = t2_lo_bits(__float_as_uint(v));
+        }
+    }
+}
+
+// The same pass for the C16 kernels, with hi(x) = x rounded to the nearest tf32 and lo(x) = x - hi(x):
+// wt = hi(W^T) and w_hi = hi(W) in float32, then bfloat16 planes [bf16(W^T) | bf16(lo(W^T))] (wt16, 2*K*N
+// halves) and [bf16(W) | bf16(lo(W))] (w16).
+__global__ void t2_prepare16_kernel(const float* __restrict__ w, int K, int N, float* __restrict__ wt,
+                                    uint16_t* __restrict__ wt16, uint16_t* __restrict__ w16, float* __restrict__ w_hi) {
+    __shared__ float tile[32][33];
+    const size_t kn = (size_t)K * N;
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    auto split = [](float v, float* hi32, uint16_t* hi, uint16_t* lo) {
+        const float rounded = __uint_as_float(t2_round_tf32(__float_as_uint(v)));
+        const uint32_t packed = t2_pack_bf16(v, v - rounded);
+        *hi32 = rounded;
+        *hi = (uint16_t)(packed & 0xffffu);
+        *lo = (uint16_t)(packed >> 16);
+    };
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int k = k0 + r, n = n0 + threadIdx.x;
+        const float v = (k < K && n < N) ? w[(size_t)k * N + n] : 0.0f;
+        tile[r][threadIdx.x] = v;
+        if (k < K && n < N) {
+            const size_t at = (size_t)k * N + n;
+            split(v, w_hi + at, w16 + at, w16 + kn + at);
+        }
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int n = n0 + r, k = k0 + threadIdx.x;
+        if (n < N && k < K) {
+            const size_t at = (size_t)n * K + k;
+            split(tile[threadIdx.x][r], wt + at, wt16 + at, wt16 + kn + at);
         }
     }
 }

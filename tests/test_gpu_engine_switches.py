@@ -26,7 +26,8 @@ def _run(name, points, **switches):
     return json.loads(out.stdout.strip().splitlines()[-1])
 
 
-@pytest.mark.parametrize("switches", [{}, {"QB200_TC": "0"}], ids=["tcgen05", "simt"])
+@pytest.mark.parametrize("switches", [{}, {"QB200_TC_COR": "tf32"}, {"QB200_TC": "0"}],
+                         ids=["tcgen05, bf16 corrections", "tcgen05, tf32 corrections", "simt"])
 def test_wide_float32_network_on_every_gemm_variant(cuda_device, switches):
     result = _run("heat3d", 640, **switches)
     assert result["engine"] == (0 if switches.get("QB200_TC") == "0" else 3)
@@ -40,9 +41,10 @@ def test_wide_float64_network_on_every_gemm_variant(cuda_device, switches):
     assert result["max_error"] <= TOLERANCE[np.dtype(np.float64)]
 
 
-def test_narrow_network_forced_onto_the_layerwise_engine(cuda_device):
+@pytest.mark.parametrize("corrections", ["bf16", "tf32"])
+def test_narrow_network_forced_onto_the_layerwise_engine(cuda_device, corrections):
     # Width 64 float32 through the layer-wise kernels: tcgen05 GEMMs with 64-column tiles.
-    result = _run("poisson2d", 3000, QB200_ENGINE="layerwise")
+    result = _run("poisson2d", 3000, QB200_ENGINE="layerwise", QB200_TC_COR=corrections)
     assert result["engine"] == 3
     assert result["max_error"] <= TOLERANCE[np.dtype(np.float32)]
 
