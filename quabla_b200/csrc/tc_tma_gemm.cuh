@@ -31,6 +31,18 @@
 
 namespace qb {
 
+// -DQB_T2_TIMING: consumer thread 0 of CTA 0 sums the cycles it spends in each phase of an item and prints them.
+#ifdef QB_T2_TIMING
+#define QB_T2_PHASE(i)                         \
+    do {                                       \
+        const long long now_ = clock64();      \
+        t2_phase[i] += now_ - t2_last;         \
+        t2_last = now_;                        \
+    } while (0)
+#else
+#define QB_T2_PHASE(i)
+#endif
+
 constexpr int T2_BM = 128;
 constexpr int T2_BK = 32;
 constexpr int T2_THREADS = 256;                    // consumer threads
@@ -373,15 +385,20 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
 #pragma unroll
         for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
 
+#ifdef QB_T2_TIMING
+        long long t2_phase[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}, t2_last = clock64();
+#endif
         // Partial of item q: wait for its instructions, add its buffer into the registers.
         auto drain = [&](int q) {
             mbar_wait(done + (q & 1), (uint32_t)((q >> 1) & 1), a.error);
+            QB_T2_PHASE(4);  // wait for the MMAs
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t src = my_tmem + (uint32_t)((q & 1) * BN);
             uint32_t v[NH];
 #pragma unroll
             for (int c = 0; c < NH / 32; ++c) t2_load32_nowait(src + c * 32, v + c * 32);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            QB_T2_PHASE(5);  // tensor-memory loads
 #pragma unroll
             for (int i = 0; i < NH; ++i) acc[i] += __uint_as_float(v[i]);
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -394,6 +411,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
         auto write_out = [&](int u) {
             if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging is free again
             asm volatile("bar.sync 1, %0;" ::"n"(T2_THREADS) : "memory");
+            QB_T2_PHASE(8);  // staging free, every warp here
             const int m0 = unit_m0(u), n0 = unit_n0(u);
             const bool biased = !WGRAD && a.bias != nullptr && m0 + trow < a.bias_rows;
 #pragma unroll
@@ -415,8 +433,10 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             }
 #pragma unroll
             for (int i = 0; i < NH; ++i) acc[i] = 0.0f;
+            QB_T2_PHASE(9);  // staging written
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("bar.sync 1, %0;" ::"n"(T2_THREADS) : "memory");
+            QB_T2_PHASE(10);  // every warp's part written
             if (tid == 0) {
                 const int y = WGRAD ? (int)blockIdx.z * a.M + m0 : m0;
 #pragma unroll
@@ -433,6 +453,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             const unsigned char* hi = smem + s * G::STAGE_BYTES;
             unsigned char* lo = smem + G::LO_OFFSET + b * G::LO_BYTES;
             mbar_wait(full + s, (uint32_t)((it / STAGES) & 1), a.error);
+            QB_T2_PHASE(0);  // wait for the loads
             // The lo buffer b was last read by item it-2, which this thread has drained.
             if (A_TMEM) {
                 // Activation tile: this thread's row (its accumulator lane), 16 of the 32 k (by column
@@ -474,7 +495,9 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                     *reinterpret_cast<uint4*>(lo + 16 * v) =
                         make_uint4(t2_lo_bits(x.x), t2_lo_bits(x.y), t2_lo_bits(x.z), t2_lo_bits(x.w));
                 }
+                QB_T2_PHASE(1);  // read, convert, issue the tensor-memory stores
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                QB_T2_PHASE(2);  // stores complete
             } else {
 #pragma unroll
                 for (int i = 0; i < G::VECTORS / T2_THREADS; ++i) {
@@ -490,11 +513,21 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             if (!PRELO) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             t2_arrive(ready + b);
+            QB_T2_PHASE(3);  // fences, arrive
             if (it >= 1) {
                 drain(it - 1);
+                QB_T2_PHASE(6);
                 if (it % k_tiles == 0) write_out(it / k_tiles - 1);  // item it-1 closed a unit
+                QB_T2_PHASE(7);
             }
         }
+#ifdef QB_T2_TIMING
+        if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && items > 100)
+            printf("t2 phases WGRAD=%d C16=%d items=%d: full %lld conv %lld wait_st %lld arrive %lld done %lld ld %lld adds %lld out %lld (per unit: sync %lld stage %lld sync %lld)\n",
+                   (int)WGRAD, (int)C16, items, t2_phase[0] / items, t2_phase[1] / items, t2_phase[2] / items, t2_phase[3] / items,
+                   t2_phase[4] / items, t2_phase[5] / items, t2_phase[6] / items, t2_phase[7] / items, t2_phase[8] / units, t2_phase[9] / units,
+                   t2_phase[10] / units);
+#endif
         if (items > 0) {
             drain(items - 1);
             write_out(units - 1);
