@@ -448,6 +448,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             }
         };
 
+        int drained = 0, unit_done = 0;
         for (int it = 0; it < items; ++it) {
             const int s = it % STAGES, b = it & 1;
             const unsigned char* hi = smem + s * G::STAGE_BYTES;
@@ -517,7 +518,10 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             if (it >= 1) {
                 drain(it - 1);
                 QB_T2_PHASE(6);
-                if (it % k_tiles == 0) write_out(it / k_tiles - 1);  // item it-1 closed a unit
+                if (++drained == k_tiles) {  // item it-1 closed a unit (counters: no integer division in this loop)
+                    drained = 0;
+                    write_out(unit_done++);
+                }
                 QB_T2_PHASE(7);
             }
         }
