@@ -82,8 +82,9 @@ struct T2Geom {
     static constexpr int B_BYTES = BN * T2_BK * 4;
     static constexpr int STAGE_BYTES = T2_A_BYTES + B_BYTES + (PRELO ? B_BYTES : 0);  // multiple of 1024
     static constexpr int LO_OFFSET = STAGES * STAGE_BYTES;
-    // ROWS keeps the activation operand in tensor memory, so only the weight tile has a lo plane here.
-    static constexpr int LO_BYTES = PRELO ? 0 : (WGRAD ? STAGE_BYTES : B_BYTES);
+    // The first operand's hi and lo parts live in tensor memory, so only the second operand has a lo plane here
+    // (and in ROWS with PRELO that one is loaded with the stage).
+    static constexpr int LO_BYTES = PRELO ? 0 : B_BYTES;
     // Output staging for the tensor-map store: BN/32 boxes of [128 rows][128 bytes].  WGRAD writes
     // once, after its last MMA, and reuses the stage ring; ROWS overlaps the store with the next tile.
     static constexpr int OUT_BYTES = T2_BM * BN * 4;
@@ -240,11 +241,12 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     uint64_t* const ready = empty + T2_STAGES;                                 // [2]
     uint64_t* const done = ready + 2;                                          // [2]
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
-    // ROWS keeps the activation operand (hi and lo, 32 columns each, two buffers) in tensor memory
-    // behind the two accumulator buffers, so an MMA reads only the weight operand from shared memory.
-    constexpr bool A_TMEM = !WGRAD;
-    constexpr int A_COL0 = 2 * BN;                               // first column of the operand buffers
-    constexpr int TMEM_COLS = A_TMEM ? (BN == 128 ? 512 : 256) : 2 * BN;  // a power of two >= 32
+    // The first operand (hi and lo, 32 columns each, two buffers) sits in tensor memory behind the two accumulator
+    // buffers, written there by the consumer warps, so an MMA reads only the second operand from shared memory:
+    // both kernels are bound by shared-memory bandwidth (loads written, operands read by the MMAs, tiles moved by
+    // the consumers).  ROWS: the activation rows.  WGRAD: H transposed, lane = m, column = row r of the k-tile.
+    constexpr int A_COL0 = 2 * BN;                         // first column of the operand buffers
+    constexpr int TMEM_COLS = BN == 128 ? 512 : 256;       // 2 BN + 128, rounded up to a power of two
     constexpr int NH = BN / 2;         // columns drained by one consumer thread
     constexpr int ISSUE_WARP = T2_THREADS / 32 + 1, LOAD_WARP = T2_THREADS / 32;
 
@@ -327,14 +329,15 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     } else if (warp == ISSUE_WARP) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            const uint32_t idesc = t2_idesc(BN, WGRAD);
+            // The first operand comes from tensor memory (K-major by construction); WGRAD's second is MN-major.
+            const uint32_t idesc = t2_idesc(BN, false) | (WGRAD ? (1u << 16) : 0u);
             for (int it = 0; it < items; ++it) {
                 const int s = it % STAGES, b = it & 1;
                 mbar_wait(ready + b, (uint32_t)((it >> 1) & 1), a.error);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t ah = smem_u32(smem + s * G::STAGE_BYTES);
-                const uint32_t al = smem_u32(smem + G::LO_OFFSET + b * G::LO_BYTES);  // WGRAD only: lo of A, then of B
-                const uint32_t bh = ah + T2_A_BYTES, bl = PRELO ? bh + G::B_BYTES : (WGRAD ? al + T2_A_BYTES : al);
+                const uint32_t al = smem_u32(smem + G::LO_OFFSET + b * G::LO_BYTES);  // without PRELO: lo of the second operand
+                const uint32_t bh = ah + T2_A_BYTES, bl = PRELO ? bh + G::B_BYTES : al;
                 const uint32_t dst = tmem_base + (uint32_t)(b * BN);
                 // k = 8 per instruction: 32 bytes along a K-major row, two 4-row groups (1024 bytes)
                 // of an MN-major atom.  The small correction products go first (they add onto a
@@ -355,11 +358,11 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
 #pragma unroll
                 for (int kb = 0; kb < (C16 ? 0 : T2_BK / 8); ++kb) {
                     const uint32_t o = kb * STEP;
+                    const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + b * 64 + kb * 8);  // hi; lo is 32 columns on
                     if (WGRAD) {
-                        tc_mma(dst, t2_desc_mnmajor(al + o), t2_desc_mnmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
-                        tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bl + o), idesc, 1u);
+                        t2_mma_tmem_a(dst, ta + 32, t2_desc_mnmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
+                        t2_mma_tmem_a(dst, ta, t2_desc_mnmajor(bl + o), idesc, 1u);
                     } else {
-                        const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + b * 64 + kb * 8);  // hi; lo is 32 columns on
                         t2_mma_tmem_a(dst, ta + 32, t2_desc_kmajor(bh + o), idesc, kb == 0 ? 0u : 1u);
                         t2_mma_tmem_a(dst, ta, t2_desc_kmajor(bl + o), idesc, 1u);
                     }
@@ -367,10 +370,8 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
 #pragma unroll
                 for (int kb = 0; kb < T2_BK / 8; ++kb) {
                     const uint32_t o = kb * STEP;
-                    if (WGRAD)
-                        tc_mma(dst, t2_desc_mnmajor(ah + o), t2_desc_mnmajor(bh + o), idesc, 1u);
-                    else
-                        t2_mma_tmem_a(dst, tmem_base + (uint32_t)(A_COL0 + b * 64 + kb * 8), t2_desc_kmajor(bh + o), idesc, 1u);
+                    t2_mma_tmem_a(dst, tmem_base + (uint32_t)(A_COL0 + b * 64 + kb * 8),
+                                  WGRAD ? t2_desc_mnmajor(bh + o) : t2_desc_kmajor(bh + o), idesc, 1u);
                 }
                 tc_commit(done + b);
                 tc_commit(empty + s);
@@ -456,7 +457,7 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
             mbar_wait(full + s, (uint32_t)((it / STAGES) & 1), a.error);
             QB_T2_PHASE(0);  // wait for the loads
             // The lo buffer b was last read by item it-2, which this thread has drained.
-            if (A_TMEM) {
+            if (!WGRAD) {
                 // Activation tile: this thread's row (its accumulator lane), 16 of the 32 k (by column
                 // half), read through the 128-byte swizzle (chunk c of row r sits at c ^ (r & 7)) and
                 // written, hi and lo, to the operand buffer b in tensor memory.
@@ -500,13 +501,29 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 QB_T2_PHASE(2);  // stores complete
             } else {
+                // H tile, transposed into tensor memory: this thread's m (its accumulator lane) and 16 of the 32 rows
+                // (by column half).  The tile is four atoms [32 r][32 m] whose 32-byte unit u of row r sits at
+                // u ^ (r & 3); a warp reads the 128 bytes of one row of its atom per load.
+                uint32_t xh[16], xl[16];
+                const unsigned char* column = hi + (warp & 3) * 4096 + (lane & 7) * 4;
 #pragma unroll
-                for (int i = 0; i < G::VECTORS / T2_THREADS; ++i) {
+                for (int i = 0; i < 16; ++i) {
+                    const int r = half * 16 + i;
+                    xh[i] = *reinterpret_cast<const uint32_t*>(column + r * 128 + (((lane >> 3) ^ (r & 3)) << 5));
+                    xl[i] = t2_lo_bits(xh[i]);
+                }
+                const uint32_t ta = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(A_COL0 + b * 64 + half * 16);
+                t2_store16(ta, xh);
+                t2_store16(ta + 32, xl);
+                // G tile: lo plane in shared memory at the same offsets.
+#pragma unroll
+                for (int i = 0; i < (G::B_BYTES / 16) / T2_THREADS; ++i) {
                     const int v = tid + i * T2_THREADS;
-                    const uint4 x = *reinterpret_cast<const uint4*>(hi + 16 * v);
+                    const uint4 x = *reinterpret_cast<const uint4*>(hi + T2_A_BYTES + 16 * v);
                     *reinterpret_cast<uint4*>(lo + 16 * v) =
                         make_uint4(t2_lo_bits(x.x), t2_lo_bits(x.y), t2_lo_bits(x.z), t2_lo_bits(x.w));
                 }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
             // Generic-proxy writes must be visible to the tensor core (async proxy) before the
             // issuer is told; the tcgen05 fence orders the drain of item it-2 before that too.
