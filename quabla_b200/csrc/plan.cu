@@ -494,7 +494,12 @@ qb200_status Plan<T>::init() {
         wmax = std::max(wmax, (size_t)desc_.sizes[l] * desc_.sizes[l + 1]);
     }
     dmax = std::max(dmax, d0);
-    size_t budget = (size_t)6 << 30;
+    // 16 GB of the 180: the 3-D heat step (1,048,576 points, 86 KB of saved jets per point) then runs in seven
+    // chunks of 150 K points; it measured 115.8 ms with chunks of 65,536 points, 113.5-113.8 with 131,072 and 112.7
+    // with 174,592, and 126.6 / 139.5 / 176.0 with 18,944 / 9,472 / 4,608 (chunks small enough for a layer's planes
+    // to stay in L2 between the kernel that writes them and the one that reads them lose more to the short
+    // launches than they gain).
+    size_t budget = (size_t)16 << 30;
     if (const char* env = getenv("QB200_SCRATCH_BYTES")) {
         const long long v = atoll(env);
         if (v > 0) budget = (size_t)v;
@@ -557,6 +562,9 @@ qb200_status Plan<T>::init() {
             chunk = s.n;
         } else {
             chunk = std::max<long long>(256, chunk / 256 * 256);
+            // Equal chunks instead of full ones and a short tail: the same count, each rounded up to 256 points.
+            const long long count = (s.n + chunk - 1) / chunk;
+            chunk = std::min(chunk, ((s.n + count - 1) / count + 255) / 256 * 256);
         }
         st.chunk = (int)chunk;
         max_chunk = std::max(max_chunk, (size_t)chunk);
