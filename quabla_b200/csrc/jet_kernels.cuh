@@ -68,22 +68,72 @@ __device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act, const MW& 
     if (SG::merged) v[SG::MS] = hM;
 }
 
-// H = tanh-jet(Z), all streams.
-template <typename T, int CODE>
+// The first hidden layer without its pre-activations in memory (KIN = number of network inputs, 1 to 4):
+// z_s[point][unit] = sum_j x_s[point][j] W[j][unit] (+ b[unit] on the primal stream) costs KIN multiply-adds, so the
+// jet kernels form it from the point's S input jets instead of reading an [S][C][d] array that a separate kernel
+// would have written: forward that saves writing and reading Z_1, backward reading it, writing the cotangents
+// of Z_1 and reading them again for the first layer's weight gradient, which the backward kernel accumulates itself
+// (per-thread sums over its points, then one partial [KIN][d] per block, summed later in block order in double).
+// The arithmetic of z is that of skinny_forward_kernel, term by term.
+template <typename T>
+struct FirstLayer {
+    const T* X;     // [S][C][KIN]: input jets of the chunk
+    const T* W;     // [KIN][d]
+    const T* b;     // [d] or null
+    T* wpartial;    // backward: [blocks][KIN][d]
+    long long C;
+    int d;
+};
+
+template <typename T, int S, int V, int KIN>
+__device__ __forceinline__ void first_layer_z(const FirstLayer<T>& f, long long point, const T (&w)[KIN][V], const T (&bv)[V],
+                                              T (&x)[S][KIN], T (&z)[S][V]) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+#pragma unroll
+        for (int j = 0; j < KIN; ++j) x[s][j] = __ldg(f.X + ((long long)s * f.C + point) * KIN + j);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            T sum = T(0);
+#pragma unroll
+            for (int j = 0; j < KIN; ++j) sum += x[s][j] * w[j][i];
+            z[s][i] = s == 0 ? sum + bv[i] : sum;
+        }
+    }
+}
+
+// H = tanh-jet(Z), all streams.  With KIN > 0, Z is the first layer's product formed here (FirstLayer).
+template <typename T, int CODE, int KIN = 0>
 __global__ void __launch_bounds__(JET_BLOCK) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane,
-                                                              int act, MergeW<T> mw) {
+                                                              int act, MergeW<T> mw, FirstLayer<T> first) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
     constexpr int S = SG::S, V = JV::V;
     const long long nvec = plane / V;
+    // The grid stride is a multiple of the layer width, so a thread always owns the same V units.
+    T w[KIN > 0 ? KIN : 1][V], bv[V];
+    if (KIN > 0) {
+        const int unit0 = (int)(((blockIdx.x * (long long)blockDim.x + threadIdx.x) * V) % first.d);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+#pragma unroll
+            for (int j = 0; j < KIN; ++j) w[j][i] = first.W[(long long)j * first.d + unit0 + i];
+            bv[i] = first.b != nullptr ? first.b[unit0 + i] : T(0);
+        }
+    }
     for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < nvec; e += (long long)gridDim.x * blockDim.x) {
-        VT q[S];
-#pragma unroll
-        for (int s = 0; s < S; ++s) q[s] = reinterpret_cast<const VT*>(Z + (long long)s * plane)[e];
         T lanes[S][V];
+        if (KIN > 0) {
+            T x[S][KIN > 0 ? KIN : 1];
+            first_layer_z<T, S, V, (KIN > 0 ? KIN : 1)>(first, (e * V) / first.d, w, bv, x, lanes);
+        } else {
+            VT q[S];
 #pragma unroll
-        for (int s = 0; s < S; ++s) JV::unpack(q[s], lanes[s]);
+            for (int s = 0; s < S; ++s) q[s] = reinterpret_cast<const VT*>(Z + (long long)s * plane)[e];
+#pragma unroll
+            for (int s = 0; s < S; ++s) JV::unpack(q[s], lanes[s]);
+        }
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             T v[S];
@@ -100,35 +150,56 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_forward_sig_kernel(const T* __r
 
 // In place: G (cotangents of H) becomes the cotangents of Z.  With HEAD the incoming cotangents are
 // not read but formed on the fly as Uhat[s][point] * w_head[unit] (the head layer's data gradient),
-// which saves writing and re-reading that [S][C][d] array.
-template <typename T, int CODE, bool HEAD>
+// which saves writing and re-reading that [S][C][d] array.  With KIN > 0 (FirstLayer) Z is formed here, the
+// cotangents of Z are not written, and the first layer's weight gradient leaves as per-block partials.
+template <typename T, int CODE, bool HEAD, int KIN = 0>
 __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
                                                                T* __restrict__ G, long long plane,
                                                                const T* __restrict__ Uhat, const T* __restrict__ w_head,
                                                                int d, long long C, int act, T* __restrict__ bias_partial,
-                                                               MergeW<T> mw) {
+                                                               MergeW<T> mw, FirstLayer<T> first) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
     constexpr int S = SG::S, V = JV::V;
+    constexpr int KW = KIN > 0 ? KIN : 1;
+    static_assert(!(HEAD && KIN > 0), "the first layer is not the last hidden layer here");
     const long long nvec = plane / V;
     // Bias gradient (column sums of the primal pre-activation cotangents), when asked for: the
     // grid stride is a multiple of the layer width, so a thread always owns the same V units.
-    T bsum[V];
+    T bsum[V], w[KW][V], bv[V], wsum[KW][V];
 #pragma unroll
     for (int i = 0; i < V; ++i) bsum[i] = T(0);
+    if (KIN > 0) {
+        const int unit0 = (int)(((blockIdx.x * (long long)blockDim.x + threadIdx.x) * V) % first.d);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+#pragma unroll
+            for (int j = 0; j < KW; ++j) {
+                w[j][i] = first.W[(long long)j * first.d + unit0 + i];
+                wsum[j][i] = T(0);
+            }
+            bv[i] = first.b != nullptr ? first.b[unit0 + i] : T(0);
+        }
+    }
     for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < nvec; e += (long long)gridDim.x * blockDim.x) {
         VT qz[S], qg[S];
+        T t[V], zl[S][V], gl[S][V], x[S][KW];
         // tanh rebuilds its derivatives from the saved activation, other activations from z_0.
-        const VT qt = reinterpret_cast<const VT*>(act == ACT_TANH ? Hprimal : Z)[e];
+        if (KIN == 0 || act == ACT_TANH) JV::unpack(reinterpret_cast<const VT*>(act == ACT_TANH ? Hprimal : Z)[e], t);
 #pragma unroll
         for (int s = 0; s < S; ++s) {
             // The transposed composition never reads z_0 itself (t replaces it).
-            if (s > 0) qz[s] = reinterpret_cast<const VT*>(Z + (long long)s * plane)[e];
+            if (KIN == 0 && s > 0) qz[s] = reinterpret_cast<const VT*>(Z + (long long)s * plane)[e];
             if (!HEAD) qg[s] = reinterpret_cast<const VT*>(G + (long long)s * plane)[e];
         }
-        T t[V], zl[S][V], gl[S][V];
-        JV::unpack(qt, t);
+        if (KIN > 0) {
+            first_layer_z<T, S, V, KW>(first, (e * V) / first.d, w, bv, x, zl);
+            if (act != ACT_TANH) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) t[i] = zl[0][i];
+            }
+        }
         if (HEAD) {
             const long long elem = e * V, point = elem / d;
             T wv[V];
@@ -142,7 +213,7 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __
         }
 #pragma unroll
         for (int s = 0; s < S; ++s) {
-            if (s > 0) JV::unpack(qz[s], zl[s]);
+            if (KIN == 0 && s > 0) JV::unpack(qz[s], zl[s]);
             if (!HEAD) JV::unpack(qg[s], gl[s]);
         }
 #pragma unroll
@@ -160,24 +231,44 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __
 #pragma unroll
             for (int s = 0; s < S; ++s) gl[s][i] = g[s];
         }
+        if (KIN == 0) {
 #pragma unroll
-        for (int s = 0; s < S; ++s) reinterpret_cast<VT*>(G + (long long)s * plane)[e] = JV::pack(gl[s]);
+            for (int s = 0; s < S; ++s) reinterpret_cast<VT*>(G + (long long)s * plane)[e] = JV::pack(gl[s]);
+        } else {
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+#pragma unroll
+                for (int j = 0; j < KW; ++j)
+#pragma unroll
+                    for (int i = 0; i < V; ++i) wsum[j][i] += x[s][j] * gl[s][i];
+        }
 #pragma unroll
         for (int i = 0; i < V; ++i) bsum[i] += gl[0][i];
     }
-    if (bias_partial != nullptr) {
+    if (bias_partial != nullptr || KIN > 0) {
         // The block covers JET_BLOCK V / d rows of the plane: add them in row order, one partial per block.
         __shared__ T red[JET_BLOCK][V];
-#pragma unroll
-        for (int i = 0; i < V; ++i) red[threadIdx.x][i] = bsum[i];
-        __syncthreads();
         const int groups = d / V;  // threads per row
-        if ((int)threadIdx.x < groups) {
+        for (int pass = bias_partial != nullptr ? 0 : 1; pass <= KIN; ++pass) {
+            __syncthreads();
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                T total = red[threadIdx.x][i];
-                for (int r = groups; r < JET_BLOCK; r += groups) total += red[threadIdx.x + r][i];
-                bias_partial[(long long)blockIdx.x * d + threadIdx.x * V + i] = total;
+                T value = bsum[i];
+#pragma unroll
+                for (int j = 0; j < KW; ++j)
+                    if (KIN > 0 && pass == j + 1) value = wsum[j][i];
+                red[threadIdx.x][i] = value;
+            }
+            __syncthreads();
+            if ((int)threadIdx.x < groups) {
+                T* out = pass == 0 ? bias_partial + (long long)blockIdx.x * d
+                                   : first.wpartial + ((long long)blockIdx.x * KW + (pass - 1)) * d;
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    T total = red[threadIdx.x][i];
+                    for (int r = groups; r < JET_BLOCK; r += groups) total += red[threadIdx.x + r][i];
+                    out[threadIdx.x * V + i] = total;
+                }
             }
         }
     }
@@ -207,11 +298,11 @@ inline int jet_sig_grid(long long vectors) {
 
 // Merged codes: SIG_MERGED + 6 / 31 / 156 = two / three / four first-order directions plus the merged
 // second-order stream (Laplacians in 2 and 3 dimensions; 3-D heat equation with its time direction).
-template <typename T>
-inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, int act, const MergeW<T>& mw,
-                                   cudaStream_t stream) {
+template <typename T, int KIN>
+inline void jet_forward_sig_launch_k(int code, const T* Z, T* H, long long plane, int act, const MergeW<T>& mw,
+                                     const FirstLayer<T>& first, cudaStream_t stream) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
-#define QB_JET_FWD(CODE) jet_forward_sig_kernel<T, CODE><<<grid, JET_BLOCK, 0, stream>>>(Z, H, plane, act, mw)
+#define QB_JET_FWD(CODE) jet_forward_sig_kernel<T, CODE, KIN><<<grid, JET_BLOCK, 0, stream>>>(Z, H, plane, act, mw, first)
     switch (code) {
         case 0: QB_JET_FWD(0); break;
         case 1: QB_JET_FWD(1); break;
@@ -227,14 +318,36 @@ inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, 
 #undef QB_JET_FWD
 }
 
-template <typename T, bool HEAD>
+template <typename T>
+inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, int act, const MergeW<T>& mw,
+                                   cudaStream_t stream) {
+    jet_forward_sig_launch_k<T, 0>(code, Z, H, plane, act, mw, FirstLayer<T>(), stream);
+}
+
+// Inputs of the network (1 to 4) for which the first-layer variants exist.
+inline bool jet_first_inputs_ok(int kin) { return kin >= 1 && kin <= 4; }
+
+// H_1 straight from the input jets (FirstLayer); the caller checked jet_first_inputs_ok and jet_bias_fusable.
+template <typename T>
+inline void jet_forward_first_launch(int code, T* H, long long plane, int act, const MergeW<T>& mw, int kin,
+                                     const FirstLayer<T>& first, cudaStream_t stream) {
+    switch (kin) {
+        case 1: jet_forward_sig_launch_k<T, 1>(code, nullptr, H, plane, act, mw, first, stream); break;
+        case 2: jet_forward_sig_launch_k<T, 2>(code, nullptr, H, plane, act, mw, first, stream); break;
+        case 3: jet_forward_sig_launch_k<T, 3>(code, nullptr, H, plane, act, mw, first, stream); break;
+        default: jet_forward_sig_launch_k<T, 4>(code, nullptr, H, plane, act, mw, first, stream); break;
+    }
+}
+
+template <typename T, bool HEAD, int KIN = 0>
 inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
                                          const T* w_head, int d, long long C, int act, T* bias_partial,
-                                         const MergeW<T>& mw, cudaStream_t stream) {
+                                         const MergeW<T>& mw, cudaStream_t stream,
+                                         const FirstLayer<T>& first = FirstLayer<T>()) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
-#define QB_JET_BWD(CODE)                                                                                             \
-    jet_backward_sig_kernel<T, CODE, HEAD><<<grid, JET_BLOCK, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, \
-                                                                     bias_partial, mw)
+#define QB_JET_BWD(CODE)                                                                                                   \
+    jet_backward_sig_kernel<T, CODE, HEAD, KIN><<<grid, JET_BLOCK, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, \
+                                                                          bias_partial, mw, first)
     switch (code) {
         case 0: QB_JET_BWD(0); break;
         case 1: QB_JET_BWD(1); break;
@@ -255,6 +368,19 @@ inline void jet_backward_sig_launch(int code, const T* Z, const T* Hprimal, T* G
                                     T* bias_partial, const MergeW<T>& mw, cudaStream_t stream) {
     jet_backward_sig_launch_impl<T, false>(code, Z, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, mw,
                                            stream);
+}
+
+// First hidden layer (FirstLayer): G holds the cotangents of H_1 and is only read; the weight-gradient partials go to
+// first.wpartial, one [kin][d] block per CTA of jet_sig_grid(plane / V).
+template <typename T>
+inline void jet_backward_first_launch(int code, const T* Hprimal, T* G, long long plane, int d, int act, T* bias_partial,
+                                      const MergeW<T>& mw, int kin, const FirstLayer<T>& first, cudaStream_t stream) {
+    switch (kin) {
+        case 1: jet_backward_sig_launch_impl<T, false, 1>(code, nullptr, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, mw, stream, first); break;
+        case 2: jet_backward_sig_launch_impl<T, false, 2>(code, nullptr, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, mw, stream, first); break;
+        case 3: jet_backward_sig_launch_impl<T, false, 3>(code, nullptr, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, mw, stream, first); break;
+        default: jet_backward_sig_launch_impl<T, false, 4>(code, nullptr, Hprimal, G, plane, nullptr, nullptr, d, 1, act, bias_partial, mw, stream, first); break;
+    }
 }
 
 // Last hidden layer: the cotangents of H are Uhat (x) w_head, formed inside the kernel; d % V == 0

@@ -987,7 +987,29 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     seed_input_kernel<T><<<grid_for(rows * sz[0], 256), 256, 0, cs_>>>(st.table, st.ncols, point0, C, sz[0], spec,
                                                                            st.dirs, H_[0]);
     QB_TRY(launched("seed_input_kernel"));
+    // The first hidden layer's product is formed inside the jet kernels (FirstLayer in jet_kernels.cuh) when the
+    // network has few inputs and layer 1 is not also the last hidden layer; QB200_FIRST_FUSED=0 keeps it apart.
+    const int first_grid = jet_sig_grid((long long)C * sz[1] / JetVec<T>::V);
+    static const bool first_switch = [] {
+        const char* env = getenv("QB200_FIRST_FUSED");
+        return !(env != nullptr && strcmp(env, "0") == 0);
+    }();
+    const bool first_fused = first_switch && head >= 2 && jet_first_inputs_ok(sz[0]) && jet_bias_fusable<T>(sz[1]) &&
+                             jet_sig_eligible<T>(st.sig_code, (long long)C * sz[1], H_[1], G_[0], G_[1]) &&
+                             (size_t)first_grid * (sz[0] + 1) * sz[1] <= wpartial_elems_;
+    FirstLayer<T> first;
+    first.X = H_[0];
+    first.W = weight(0);
+    first.b = bias(0);
+    first.wpartial = wpartial_ + (size_t)first_grid * sz[1];
+    first.C = C;
+    first.d = sz[1];
     for (int l = 1; l <= head; ++l) {
+        if (l == 1 && first_fused) {
+            jet_forward_first_launch<T>(st.sig_code, H_[1], (long long)C * sz[1], desc_.activation, st.merge_w, sz[0], first, cs_);
+            QB_TRY(launched("jet_forward_kernel(first layer)"));
+            continue;
+        }
         // Z_l = H_{l-1} W_{l-1} (+ bias on the primal rows), H_l = tanh-jet(Z_l).
         GemmArgs<T> g;
         g.A = H_[l - 1];
@@ -1146,6 +1168,20 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     for (int l = head; l >= 1; --l) {
         const long long plane = (long long)C * sz[l];
         // The vectorised kernel can form the bias-gradient partials (one row of sz[l] per block) on its way.
+        if (l == 1 && first_fused) {
+            // Cotangents of H_1 in, bias- and weight-gradient partials out; nothing of layer 1 is written back.
+            T* bias_partial = b_leaf_[0] >= 0 ? wpartial_ : nullptr;
+            jet_backward_first_launch<T>(st.sig_code, H_[1], G_[cur], plane, sz[1], desc_.activation, bias_partial, st.merge_w,
+                                         sz[0], first, cs_);
+            QB_TRY(launched("jet_backward_kernel(first layer)"));
+            if (bias_partial != nullptr) {
+                accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[b_leaf_[0]].offset, sz[1], first_grid, cs_);
+                QB_TRY(launched("accumulate_partials_kernel"));
+            }
+            accumulate_partials_launch<T>(first.wpartial, d_acc_ + leaves_[w_leaf_[0]].offset, sz[0] * sz[1], first_grid, cs_);
+            QB_TRY(launched("accumulate_partials_kernel"));
+            break;
+        }
         const bool sig = (l == head && head_fused) || jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], G_[cur]);
         const int jet_grid = jet_sig_grid(plane / JetVec<T>::V);
         const bool bias_fused = sig && b_leaf_[l - 1] >= 0 && jet_bias_fusable<T>(sz[l]) &&

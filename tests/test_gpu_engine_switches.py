@@ -41,6 +41,14 @@ def test_wide_float64_network_on_every_gemm_variant(cuda_device, switches):
     assert result["max_error"] <= TOLERANCE[np.dtype(np.float64)]
 
 
+@pytest.mark.parametrize("name,points,chunk,engine", [("heat3d", 1800, "512", 3), ("burgers", 1500, "256", 0)])
+def test_point_sets_cut_into_chunks(cuda_device, name, points, chunk, engine):
+    # Several chunks per point set, the last one ragged (its rows are not a multiple of the GEMM tile).
+    result = _run(name, points, QB200_CHUNK_POINTS=chunk)
+    assert result["engine"] == engine
+    assert result["max_error"] <= TOLERANCE[np.dtype(np.float32 if name == "heat3d" else np.float64)]
+
+
 @pytest.mark.parametrize("corrections", ["bf16", "tf32"])
 def test_narrow_network_forced_onto_the_layerwise_engine(cuda_device, corrections):
     # Width 64 float32 through the layer-wise kernels: tcgen05 GEMMs with 64-column tiles.
