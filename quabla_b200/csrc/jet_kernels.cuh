@@ -85,6 +85,33 @@ struct FirstLayer {
     int d;
 };
 
+// The linear output layer on the way out of the last hidden layer's forward kernel: every warp adds its 32 V units
+// of u_s[point] = sum_unit h_s[point][unit] w[unit] (a fixed shuffle tree) and writes one partial per stream, so the
+// [S][C][d] activations are not read again for it; head_combine_kernel adds the d / (32 V) partials of a row in
+// order, plus the bias on the primal rows.  Needs whole warps per point: d % (32 V) == 0.
+template <typename T>
+struct HeadDot {
+    const T* w;   // [d] weights of the output layer, or null: no head product here
+    T* partial;   // [S][C][d / (32 V)]
+    long long C;
+    int d;
+};
+
+template <typename T>
+inline bool head_dot_fusable(int d) {
+    return d % (32 * JetVec<T>::V) == 0;
+}
+
+template <typename T>
+__global__ void head_combine_kernel(const T* __restrict__ partial, const T* __restrict__ b, T* __restrict__ U, long long rows,
+                                    int per_row, long long primal_rows) {
+    for (long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x; r < rows; r += (long long)gridDim.x * blockDim.x) {
+        T s = partial[r * per_row];
+        for (int k = 1; k < per_row; ++k) s += partial[r * per_row + k];
+        U[r] = s + ((b != nullptr && r < primal_rows) ? b[0] : T(0));
+    }
+}
+
 template <typename T, int S, int V, int KIN>
 __device__ __forceinline__ void first_layer_z(const FirstLayer<T>& f, long long point, const T (&w)[KIN][V], const T (&bv)[V],
                                               T (&x)[S][KIN], T (&z)[S][V]) {
@@ -105,14 +132,19 @@ __device__ __forceinline__ void first_layer_z(const FirstLayer<T>& f, long long 
 // H = tanh-jet(Z), all streams.  With KIN > 0, Z is the first layer's product formed here (FirstLayer).
 template <typename T, int CODE, int KIN = 0>
 __global__ void __launch_bounds__(JET_BLOCK) jet_forward_sig_kernel(const T* __restrict__ Z, T* __restrict__ H, long long plane,
-                                                              int act, MergeW<T> mw, FirstLayer<T> first) {
+                                                              int act, MergeW<T> mw, FirstLayer<T> first, HeadDot<T> head) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
     constexpr int S = SG::S, V = JV::V;
     const long long nvec = plane / V;
     // The grid stride is a multiple of the layer width, so a thread always owns the same V units.
-    T w[KIN > 0 ? KIN : 1][V], bv[V];
+    T w[KIN > 0 ? KIN : 1][V], bv[V], wh[V];
+    if (head.w != nullptr) {
+        const int unit0 = (int)(((blockIdx.x * (long long)blockDim.x + threadIdx.x) * V) % head.d);
+#pragma unroll
+        for (int i = 0; i < V; ++i) wh[i] = head.w[unit0 + i];
+    }
     if (KIN > 0) {
         const int unit0 = (int)(((blockIdx.x * (long long)blockDim.x + threadIdx.x) * V) % first.d);
 #pragma unroll
@@ -145,6 +177,21 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_forward_sig_kernel(const T* __r
         }
 #pragma unroll
         for (int s = 0; s < S; ++s) reinterpret_cast<VT*>(H + (long long)s * plane)[e] = JV::pack(lanes[s]);
+        if (head.w != nullptr) {
+            // A warp's 32 V elements lie in one row (d % (32 V) == 0, and the plane is whole rows, so the warp is
+            // either all inside the loop or all outside).
+            const long long elem = e * V, point = elem / head.d;
+            const int per_row = head.d / (32 * V), slot = (int)(elem - point * head.d) / (32 * V);
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                T dot = T(0);
+#pragma unroll
+                for (int i = 0; i < V; ++i) dot += lanes[s][i] * wh[i];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if ((threadIdx.x & 31) == 0) head.partial[((long long)s * head.C + point) * per_row + slot] = dot;
+            }
+        }
     }
 }
 
@@ -300,9 +347,9 @@ inline int jet_sig_grid(long long vectors) {
 // second-order stream (Laplacians in 2 and 3 dimensions; 3-D heat equation with its time direction).
 template <typename T, int KIN>
 inline void jet_forward_sig_launch_k(int code, const T* Z, T* H, long long plane, int act, const MergeW<T>& mw,
-                                     const FirstLayer<T>& first, cudaStream_t stream) {
+                                     const FirstLayer<T>& first, cudaStream_t stream, const HeadDot<T>& head = HeadDot<T>()) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
-#define QB_JET_FWD(CODE) jet_forward_sig_kernel<T, CODE, KIN><<<grid, JET_BLOCK, 0, stream>>>(Z, H, plane, act, mw, first)
+#define QB_JET_FWD(CODE) jet_forward_sig_kernel<T, CODE, KIN><<<grid, JET_BLOCK, 0, stream>>>(Z, H, plane, act, mw, first, head)
     switch (code) {
         case 0: QB_JET_FWD(0); break;
         case 1: QB_JET_FWD(1); break;
@@ -318,10 +365,12 @@ inline void jet_forward_sig_launch_k(int code, const T* Z, T* H, long long plane
 #undef QB_JET_FWD
 }
 
+// `head` (optional): the output layer's product leaves as per-warp partials (HeadDot); the caller checked
+// head_dot_fusable and jet_bias_fusable for this width.
 template <typename T>
 inline void jet_forward_sig_launch(int code, const T* Z, T* H, long long plane, int act, const MergeW<T>& mw,
-                                   cudaStream_t stream) {
-    jet_forward_sig_launch_k<T, 0>(code, Z, H, plane, act, mw, FirstLayer<T>(), stream);
+                                   cudaStream_t stream, const HeadDot<T>& head = HeadDot<T>()) {
+    jet_forward_sig_launch_k<T, 0>(code, Z, H, plane, act, mw, FirstLayer<T>(), stream, head);
 }
 
 // Inputs of the network (1 to 4) for which the first-layer variants exist.

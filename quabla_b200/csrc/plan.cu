@@ -1004,6 +1004,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     first.wpartial = wpartial_ + (size_t)first_grid * sz[1];
     first.C = C;
     first.d = sz[1];
+    static const bool head_switch = [] {
+        const char* env = getenv("QB200_HEAD_FUSED");
+        return !(env != nullptr && strcmp(env, "0") == 0);
+    }();
+    bool head_dotted = false;
     for (int l = 1; l <= head; ++l) {
         if (l == 1 && first_fused) {
             jet_forward_first_launch<T>(st.sig_code, H_[1], (long long)C * sz[1], desc_.activation, st.merge_w, sz[0], first, cs_);
@@ -1050,15 +1055,32 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             timer_end();
         }
         const long long plane = (long long)C * sz[l];
-        if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], nullptr))
-            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, desc_.activation, st.merge_w, cs_);
+        if (jet_sig_eligible<T>(st.sig_code, plane, Z_[l], H_[l], nullptr)) {
+            // The last hidden layer's kernel also leaves the output layer's product as per-warp partials.
+            HeadDot<T> dot = HeadDot<T>();
+            if (l == head && head_switch && head_dot_fusable<T>(sz[l]) && jet_bias_fusable<T>(sz[l]) &&
+                (size_t)rows * (sz[l] / (32 * JetVec<T>::V)) <= wpartial_elems_) {
+                dot.w = weight(head);
+                dot.partial = wpartial_;
+                dot.C = C;
+                dot.d = sz[l];
+                head_dotted = true;
+            }
+            jet_forward_sig_launch<T>(st.sig_code, Z_[l], H_[l], plane, desc_.activation, st.merge_w, cs_, dot);
+        }
         else
             jet_forward_kernel<T><<<grid_for(plane, 256), 256, 0, cs_>>>(Z_[l], H_[l], plane, spec, desc_.activation);
         QB_TRY(launched("jet_forward_kernel"));
     }
-    head_forward_kernel<T><<<grid_for(rows * 32, 256), 256, 0, cs_>>>(H_[head], weight(head), bias(head), U_, rows,
-                                                                          sz[head], C);
-    QB_TRY(launched("head_forward_kernel"));
+    if (head_dotted) {
+        head_combine_kernel<T><<<grid_for(rows, 256), 256, 0, cs_>>>(wpartial_, bias(head), U_, rows,
+                                                                       sz[head] / (32 * JetVec<T>::V), C);
+        QB_TRY(launched("head_combine_kernel"));
+    } else {
+        head_forward_kernel<T><<<grid_for(rows * 32, 256), 256, 0, cs_>>>(H_[head], weight(head), bias(head), U_, rows,
+                                                                              sz[head], C);
+        QB_TRY(launched("head_forward_kernel"));
+    }
     const T w = (T)desc_.sets[si].weight;
     residual_kernel<T><<<(C + 255) / 256, 256, 0, cs_>>>(st.table, st.ncols, point0, C, S, U_,
                                                              forward_only ? nullptr : Uhat_, st.prog, d_ct_, w,
