@@ -68,6 +68,33 @@ __device__ __forceinline__ void jet_apply_act(T (&v)[SG::S], int act, const MW& 
     if (SG::merged) v[SG::MS] = hM;
 }
 
+// The forward composition again, from the activation's derivatives d and value at z_0 and the input jets
+// v[1..] (v[0] is not read): v becomes the output jets.  Same steps as jet_apply_act.
+template <typename T, typename SG, typename MW>
+__device__ __forceinline__ void jet_values_with(const TanhD<T>& d, T value, T (&v)[SG::S], const MW& mw) {
+    T hM = T(0);
+    if (SG::merged) hM = merged_compose(d, merged_square_sum<T, SG, MW>(v, mw), v[SG::MS]);
+    v[0] = value;
+#pragma unroll
+    for (int j = 0; j < SG::ndirs; ++j) {
+        T z[MAX_ORDER], h[MAX_ORDER];
+        const int K = SG::order(j);
+        const int b = SG::base(j);
+#pragma unroll
+        for (int m = 0; m < MAX_ORDER; ++m) z[m] = m < K ? v[b + m] : T(0);
+        switch (K) {
+            case 1: jet_compose<T, 1>(d, z, h); break;
+            case 2: jet_compose<T, 2>(d, z, h); break;
+            case 3: jet_compose<T, 3>(d, z, h); break;
+            default: jet_compose<T, 4>(d, z, h); break;
+        }
+#pragma unroll
+        for (int m = 0; m < MAX_ORDER; ++m)
+            if (m < K) v[b + m] = h[m];
+    }
+    if (SG::merged) v[SG::MS] = hM;
+}
+
 // The first hidden layer without its pre-activations in memory (KIN = number of network inputs, 1 to 4):
 // z_s[point][unit] = sum_j x_s[point][j] W[j][unit] (+ b[unit] on the primal stream) costs KIN multiply-adds, so the
 // jet kernels form it from the point's S input jets instead of reading an [S][C][d] array that a separate kernel
@@ -199,17 +226,25 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_forward_sig_kernel(const T* __r
 // not read but formed on the fly as Uhat[s][point] * w_head[unit] (the head layer's data gradient),
 // which saves writing and re-reading that [S][C][d] array.  With KIN > 0 (FirstLayer) Z is formed here, the
 // cotangents of Z are not written, and the first layer's weight gradient leaves as per-block partials.
+// With HEAD and head_wpartial the kernel also rebuilds the layer's output jets from what it has loaded (the
+// forward composition is a few dozen flops next to 12 planes of traffic) and accumulates the output layer's weight
+// gradient sum_{s, point} h_s[point][unit] Uhat_s[point], one partial [d] per block, so that those activations are
+// not read from memory a third time.
 template <typename T, int CODE, bool HEAD, int KIN = 0>
 __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __restrict__ Z, const T* __restrict__ Hprimal,
                                                                T* __restrict__ G, long long plane,
                                                                const T* __restrict__ Uhat, const T* __restrict__ w_head,
                                                                int d, long long C, int act, T* __restrict__ bias_partial,
-                                                               MergeW<T> mw, FirstLayer<T> first) {
+                                                               MergeW<T> mw, FirstLayer<T> first,
+                                                               T* __restrict__ head_wpartial) {
     typedef Sig<CODE> SG;
     typedef JetVec<T> JV;
     typedef typename JV::type VT;
     constexpr int S = SG::S, V = JV::V;
     constexpr int KW = KIN > 0 ? KIN : 1;
+    T hsum[V], us[S];
+#pragma unroll
+    for (int i = 0; i < V; ++i) hsum[i] = T(0);
     static_assert(!(HEAD && KIN > 0), "the first layer is not the last hidden layer here");
     const long long nvec = plane / V;
     // Bias gradient (column sums of the primal pre-activation cotangents), when asked for: the
@@ -254,6 +289,7 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __
 #pragma unroll
             for (int s = 0; s < S; ++s) {
                 const T u = Uhat[(long long)s * C + point];
+                us[s] = u;
 #pragma unroll
                 for (int i = 0; i < V; ++i) gl[s][i] = u * wv[i];
             }
@@ -272,8 +308,16 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __
                 if (s > 0) z[s] = zl[s][i];
                 g[s] = gl[s][i];
             }
-            T unused;
-            const TanhD<T> dv = act == ACT_TANH ? TanhD<T>(t[i]) : TanhD<T>(t[i], act, &unused);
+            T value = t[i];
+            const TanhD<T> dv = act == ACT_TANH ? TanhD<T>(t[i]) : TanhD<T>(t[i], act, &value);
+            if (HEAD && head_wpartial != nullptr) {
+                T h[S];
+#pragma unroll
+                for (int s = 0; s < S; ++s) h[s] = z[s];
+                jet_values_with<T, SG>(dv, value, h, mw.w);
+#pragma unroll
+                for (int s = 0; s < S; ++s) hsum[i] += h[s] * us[s];
+            }
             jet_apply_transposed_with<T, SG>(dv, z, g, mw.w);
 #pragma unroll
             for (int s = 0; s < S; ++s) gl[s][i] = g[s];
@@ -292,15 +336,18 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __
 #pragma unroll
         for (int i = 0; i < V; ++i) bsum[i] += gl[0][i];
     }
-    if (bias_partial != nullptr || KIN > 0) {
+    const bool head_w = HEAD && head_wpartial != nullptr;
+    if (bias_partial != nullptr || KIN > 0 || head_w) {
         // The block covers JET_BLOCK V / d rows of the plane: add them in row order, one partial per block.
+        // Passes: 0 the bias gradient, 1..KIN the first layer's weight gradient, KIN + 1 the output layer's.
         __shared__ T red[JET_BLOCK][V];
         const int groups = d / V;  // threads per row
-        for (int pass = bias_partial != nullptr ? 0 : 1; pass <= KIN; ++pass) {
+        for (int pass = 0; pass <= KIN + 1; ++pass) {
+            if ((pass == 0 && bias_partial == nullptr) || (pass == KIN + 1 && !head_w)) continue;
             __syncthreads();
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                T value = bsum[i];
+                T value = pass == 0 ? bsum[i] : hsum[i];
 #pragma unroll
                 for (int j = 0; j < KW; ++j)
                     if (KIN > 0 && pass == j + 1) value = wsum[j][i];
@@ -309,7 +356,8 @@ __global__ void __launch_bounds__(JET_BLOCK) jet_backward_sig_kernel(const T* __
             __syncthreads();
             if ((int)threadIdx.x < groups) {
                 T* out = pass == 0 ? bias_partial + (long long)blockIdx.x * d
-                                   : first.wpartial + ((long long)blockIdx.x * KW + (pass - 1)) * d;
+                         : pass == KIN + 1 ? head_wpartial + (long long)blockIdx.x * d
+                                           : first.wpartial + ((long long)blockIdx.x * KW + (pass - 1)) * d;
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
                     T total = red[threadIdx.x][i];
@@ -392,11 +440,11 @@ template <typename T, bool HEAD, int KIN = 0>
 inline void jet_backward_sig_launch_impl(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
                                          const T* w_head, int d, long long C, int act, T* bias_partial,
                                          const MergeW<T>& mw, cudaStream_t stream,
-                                         const FirstLayer<T>& first = FirstLayer<T>()) {
+                                         const FirstLayer<T>& first = FirstLayer<T>(), T* head_wpartial = nullptr) {
     const int grid = jet_sig_grid(plane / JetVec<T>::V);
 #define QB_JET_BWD(CODE)                                                                                                   \
     jet_backward_sig_kernel<T, CODE, HEAD, KIN><<<grid, JET_BLOCK, 0, stream>>>(Z, Hprimal, G, plane, Uhat, w_head, d, C, act, \
-                                                                          bias_partial, mw, first)
+                                                                          bias_partial, mw, first, head_wpartial)
     switch (code) {
         case 0: QB_JET_BWD(0); break;
         case 1: QB_JET_BWD(1); break;
@@ -437,8 +485,9 @@ inline void jet_backward_first_launch(int code, const T* Hprimal, T* G, long lon
 template <typename T>
 inline void jet_backward_head_launch(int code, const T* Z, const T* Hprimal, T* G, long long plane, const T* Uhat,
                                      const T* w_head, int d, long long C, int act, T* bias_partial,
-                                     const MergeW<T>& mw, cudaStream_t stream) {
-    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, act, bias_partial, mw, stream);
+                                     const MergeW<T>& mw, cudaStream_t stream, T* head_wpartial = nullptr) {
+    jet_backward_sig_launch_impl<T, true>(code, Z, Hprimal, G, plane, Uhat, w_head, d, C, act, bias_partial, mw, stream,
+                                          FirstLayer<T>(), head_wpartial);
 }
 
 }  // namespace qb

@@ -1174,14 +1174,18 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     };
 
     // Head: dW = H^T Uhat, db = sum of the primal cotangents, G = Uhat (x) w.
-    QB_TRY(wgrad(H_[head], Uhat_, sz[head], 1, w_leaf_[head], head));
-    QB_TRY(bgrad(Uhat_, 1, b_leaf_[head]));
     int cur = 0;
     // The head's data gradient G = Uhat (x) w is formed inside the last hidden layer's jet kernel when
     // that kernel has a compile-time signature; otherwise it is materialised here.
     const bool head_fused = head >= 1 && sz[head] % JetVec<T>::V == 0 &&
                             jet_sig_eligible<T>(st.sig_code, (long long)C * sz[head], Z_[head], H_[head], G_[cur]) &&
                             (reinterpret_cast<uintptr_t>(weight(head)) & 15) == 0;
+    // ... and dW of the head in the same kernel (jet_kernels.cuh), when its per-block partials fit beside the bias partials.
+    const int head_grid = head >= 1 ? jet_sig_grid((long long)C * sz[head] / JetVec<T>::V) : 0;
+    const bool head_w_fused = head_fused && head_switch && jet_bias_fusable<T>(sz[head]) &&
+                              2 * (size_t)head_grid * sz[head] <= wpartial_elems_;
+    if (!head_w_fused) QB_TRY(wgrad(H_[head], Uhat_, sz[head], 1, w_leaf_[head], head));
+    QB_TRY(bgrad(Uhat_, 1, b_leaf_[head]));
     if (!head_fused) {
         head_backward_kernel<T><<<grid_for(rows * sz[head], 256), 256, 0, cs_>>>(Uhat_, weight(head), G_[cur], rows,
                                                                                      sz[head]);
@@ -1211,7 +1215,8 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         T* bias_partial = bias_fused ? wpartial_ : nullptr;
         if (l == head && head_fused)
             jet_backward_head_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, Uhat_, weight(head), sz[head], C,
-                                        desc_.activation, bias_partial, st.merge_w, cs_);
+                                        desc_.activation, bias_partial, st.merge_w, cs_,
+                                        head_w_fused ? wpartial_ + (size_t)head_grid * sz[head] : nullptr);
         else if (sig)
             jet_backward_sig_launch<T>(st.sig_code, Z_[l], H_[l], G_[cur], plane, sz[l], desc_.activation, bias_partial,
                                        st.merge_w, cs_);
@@ -1220,6 +1225,11 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         QB_TRY(launched("jet_backward_kernel"));
         if (bias_fused) {
             accumulate_partials_launch<T>(wpartial_, d_acc_ + leaves_[b_leaf_[l - 1]].offset, sz[l], jet_grid, cs_);
+            QB_TRY(launched("accumulate_partials_kernel"));
+        }
+        if (l == head && head_w_fused) {
+            accumulate_partials_launch<T>(wpartial_ + (size_t)head_grid * sz[head], d_acc_ + leaves_[w_leaf_[head]].offset,
+                                          sz[head], head_grid, cs_);
             QB_TRY(launched("accumulate_partials_kernel"));
         }
         QB_TRY(wgrad(H_[l - 1], G_[cur], sz[l - 1], sz[l], w_leaf_[l - 1], l - 1));
