@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ G, T*
 // bit-reproducible (the reference sums long axes in double as well, cuda.rs:8202-8247).  A block
 // owns EX consecutive elements; thread (x, y) sums the slices z = y, y + G, ... of element x
 // (G = 256 / EX groups, coalesced along x), then the G partial sums are added in y order.
-// EX = 32 suits many elements and few slices, EX = 8 few elements and thousands of slices.
+// EX = 32 suits many elements and few slices, EX = 8 or 2 few elements and hundreds or thousands of slices.
 template <typename T, int EX>
 __global__ void __launch_bounds__(256) accumulate_partials_kernel(const T* __restrict__ partial, double* __restrict__ acc,
                                                                   int count, int slices) {
@@ -240,7 +240,9 @@ __global__ void __launch_bounds__(256) accumulate_partials_kernel(const T* __res
 
 template <typename T>
 inline void accumulate_partials_launch(const T* partial, double* acc, int count, int slices, cudaStream_t stream) {
-    if (slices > 256 && count <= 4096)
+    if (slices > 1024 && count <= 4096)  // per-block partials of the jet kernels: thousands of slices of a few hundred elements
+        accumulate_partials_kernel<T, 2><<<(count + 1) / 2, 256, 0, stream>>>(partial, acc, count, slices);
+    else if (slices > 256 && count <= 4096)
         accumulate_partials_kernel<T, 8><<<(count + 7) / 8, 256, 0, stream>>>(partial, acc, count, slices);
     else
         accumulate_partials_kernel<T, 32><<<(count + 31) / 32, 256, 0, stream>>>(partial, acc, count, slices);
