@@ -41,6 +41,17 @@ def test_wide_float64_network_on_every_gemm_variant(cuda_device, switches):
     assert result["max_error"] <= TOLERANCE[np.dtype(np.float64)]
 
 
+@pytest.mark.parametrize("name,points", [("heat3d", 900), ("burgers", 1100)])
+@pytest.mark.parametrize("switches", [{"QB200_FIRST_FUSED": "0"}, {"QB200_HEAD_FUSED": "0"},
+                                      {"QB200_FIRST_FUSED": "0", "QB200_HEAD_FUSED": "0"}],
+                         ids=["first layer apart", "output layer apart", "both apart"])
+def test_narrow_layers_in_kernels_of_their_own(cuda_device, name, points, switches):
+    # By default the jet kernels form the first layer's product and weight gradient and the output layer's; the
+    # separate kernels remain for shapes those cannot take and must give the same answer.
+    result = _run(name, points, **switches)
+    assert result["max_error"] <= TOLERANCE[np.dtype(np.float32 if name == "heat3d" else np.float64)]
+
+
 @pytest.mark.parametrize("name,points,chunk,engine", [("heat3d", 1800, "512", 3), ("burgers", 1500, "256", 0)])
 def test_point_sets_cut_into_chunks(cuda_device, name, points, chunk, engine):
     # Several chunks per point set, the last one ragged (its rows are not a multiple of the GEMM tile).
