@@ -63,11 +63,6 @@ static bool make_map(CUtensorMap* map, const float* base, long long rows, int co
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaStream_t stream) {
-    t2_transpose_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), dim3(32, 8), 0, stream>>>(w, K, N, wt);
-    return cudaGetLastError();
-}
-
 // bfloat16 matrix [rows][cols], boxes of box_cols x box_rows under the 64-byte swizzle.
 static bool make_map16(CUtensorMap* map, const void* base, long long rows, int cols, int ld, int box_cols, int box_rows) {
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -106,11 +101,12 @@ cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const floa
                             const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream) {
     const int BN = N % 128 == 0 ? 128 : 64;
     CUtensorMap ma, mb, mblo, mc;
-    const bool c16 = Bt_lo != nullptr && tc_cor16();  // Bt_lo is then the pair of bfloat16 planes, 2N rows of K
+    if (Bt_lo == nullptr) return cudaErrorInvalidValue;
+    const bool c16 = tc_cor16();  // Bt_lo is then the pair of bfloat16 planes, 2N rows of K
     if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !(c16 ? make_map16(&mblo, Bt_lo, 2LL * N, K, ldb, T2_BK, BN)
-              : make_map(&mblo, Bt_lo != nullptr ? Bt_lo : Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) ||
+              : make_map(&mblo, Bt_lo, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) ||
         !make_map(&mc, C, M, N, ldc, 32, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
     TcTmaArgs a;
@@ -128,11 +124,8 @@ cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const floa
     if (c16)
         return BN == 128 ? launch2<false, 128, true, true>(ma, mb, mblo, mc, a, grid, stream)
                          : launch2<false, 64, true, true>(ma, mb, mblo, mc, a, grid, stream);
-    if (Bt_lo != nullptr)
-        return BN == 128 ? launch2<false, 128, true>(ma, mb, mblo, mc, a, grid, stream)
-                         : launch2<false, 64, true>(ma, mb, mblo, mc, a, grid, stream);
-    return BN == 128 ? launch2<false, 128, false>(ma, mb, mblo, mc, a, grid, stream)
-                     : launch2<false, 64, false>(ma, mb, mblo, mc, a, grid, stream);
+    return BN == 128 ? launch2<false, 128, true>(ma, mb, mblo, mc, a, grid, stream)
+                     : launch2<false, 64, true>(ma, mb, mblo, mc, a, grid, stream);
 }
 
 cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,

@@ -1,6 +1,5 @@
-// tcgen05 primitives shared by the float32 GEMMs of the layer-wise engine (tc_tma_gemm.cuh): the MMA
-// instruction with both operands described in shared memory, the commit that arrives on an mbarrier when
-// the issued MMAs have completed, and a tensor-memory load of 32 columns.
+// tcgen05 primitives shared by the float32 GEMMs of the layer-wise engine (tc_tma_gemm.cuh): tile constants and
+// the commit that arrives on an mbarrier when the issued MMAs have completed.
 //
 // These kernels take over the wide-network contractions that the reference issues as cuBLAS strided-batched
 // calls with batch = B, M = 1 (crates/quabla-core/src/tensor_ir/cuda.rs:4936-5035) and as a materialised
@@ -15,38 +14,9 @@ namespace qb {
 constexpr int TC_BM = 128;  // rows of an output tile (tensor-memory lanes)
 constexpr int TC_BK = 32;   // contraction elements per k-tile (one 128-byte swizzle span of float32)
 
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
-        "}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-
 // Arrives on `bar` once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-
-// 32 lanes x 32 consecutive columns: thread i of the warp receives row (lane base + i).
-__device__ __forceinline__ void tc_load32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Byte offset of element (row, k) inside an operand tile of the layout above.
 
 }  // namespace qb

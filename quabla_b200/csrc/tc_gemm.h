@@ -22,15 +22,13 @@ bool tc_cor16();
 // [tf32(W^T) | bf16(W^T), bf16(lo(W^T)) | bf16(W), bf16(lo(W)) | tf32(W)].
 size_t tc_image_words(int K, int N);
 
-// wt[n][k] = w[k][n]: the K-major operand of the forward GEMM.
-cudaError_t tc2_transpose_launch(const float* w, int K, int N, float* wt, cudaStream_t stream);
 // One pass over W [K][N]: wt = W^T [N][K], wt_lo = the lo plane of W^T, w_lo = the lo plane of W (each K*N floats;
 // w_hi is not written).  With bfloat16 corrections: wt = W^T rounded to tf32, w_hi = W rounded to tf32, and wt_lo
 // and w_lo each receive a pair of bfloat16 planes (the value, then its lo part x - tf32(x)).
 cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, float* w_hi,
                                cudaStream_t stream);
-// C[M][N] = A[M][K] * Bt^T (+ bias on the first bias_rows rows), Bt row-major [N][K].  Bt_lo, when
-// given, is what tc2_prepare_launch wrote for Bt (its lo plane; or its pair of bfloat16 planes, and Bt is then
+// C[M][N] = A[M][K] * Bt^T (+ bias on the first bias_rows rows), Bt row-major [N][K].  Bt_lo (required)
+// is what tc2_prepare_launch wrote for Bt (its lo plane; or its pair of bfloat16 planes, and Bt is then
 // the tf32-rounded matrix written with them): the kernel loads it instead of computing a lo plane per tile.
 cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,
                             const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream);

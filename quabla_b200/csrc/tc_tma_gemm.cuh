@@ -1,33 +1,37 @@
-// float32 GEMMs of the layer-wise engine, second generation: operands arrive by TMA tensor-map
-// loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) into a ring of shared-memory
-// stages, the products run on tcgen05.mma (kind::tf32) with accumulators in tensor memory, and
-// completion is tracked by mbarriers with bounded waits.
+// float32 GEMMs of the layer-wise engine: operands arrive by TMA tensor-map loads (cp.async.bulk.tensor,
+// swizzled, no multicast) into a ring of shared-memory stages, the products run on tcgen05.mma with
+// accumulators in tensor memory, and completion is tracked by mbarriers with bounded waits.
 //
-// 3xTF32 without pre-split operands.  The tensor core reads the upper 19 bits of a float32
-// operand, so the tile as loaded IS the hi operand (hi = x & 0xffffe000).  The CTA's threads
-// compute lo = tf32(x - hi) element by element from shared memory into a second buffer at the
-// same offsets (any swizzle carries over), and a product is A_lo.B_hi + A_hi.B_lo + A_hi.B_hi.
+// Split float32.  x = hi + lo and a product is lo_a.hi_b + hi_a.lo_b + hi_a.hi_b.  The tensor core reads the
+// upper 19 bits of a float32 operand, so a tile as loaded IS a hi operand (hi = x & 0xffffe000) and lo =
+// tf32(x - hi) is computed element by element (the weight gradient); the forward and data-gradient products
+// round hi to the nearest tf32 instead and run the two correction products as bfloat16 instructions (C16, below).
+//
+// The first operand of every product lives in TENSOR MEMORY, hi and lo, written there by the consumer warps, so the
+// MMAs read one operand from shared memory: these kernels are bound by the bytes that cross shared memory per
+// k-tile (loads written, MMA operands read, tiles moved by the consumers), not by the tensor pipe.
 //
 // Accuracy.  The tensor core adds into its accumulator with truncation, so a k-tile of 32
 // accumulates from zero into one of two tensor-memory buffers and the threads add that partial to
 // float32 registers with round-to-nearest adds while the next k-tile's instructions run.
 //
-// Work of one CTA (eight consumer warps, a loading warp and an issuing warp): 128 x BN output tiles, k-tiles of 32 floats (one 128-byte
-// swizzle span).
+// Work of one CTA (eight consumer warps, a loading warp and an issuing warp): 128 x BN output tiles, k-tiles of
+// 32 floats (one 128-byte swizzle span).
 //   ROWS   C[m][n] = sum_k A[m][k] * Bt[n][k] (+ bias[n] on rows < bias_rows).  Both operands are
-//          K-major: a stage holds A [128 rows][128 B] and Bt [BN rows][128 B].  The CTA is
-//          persistent over output tiles (tile = blockIdx.x + i * gridDim.x, n-tile fastest), and
-//          the stage ring runs ahead across tile boundaries.
-//   WGRAD  P[z][m][n] = sum over the rows r of slice z of H[r][m] * G[r][n].  Both operands are
-//          MN-major: a stage holds 4 atoms [32 r][32 m] of H and BN/32 atoms [32 r][32 n] of G,
-//          each 4 KB, exactly as a tensor-map box of the row-major matrices lands them.
+//          K-major: a stage holds A [128 rows][128 B], Bt [BN rows][128 B] and Bt's prepared second matrix.  The
+//          consumers copy their row of A into tensor memory.  The CTA is persistent over output tiles (tile =
+//          blockIdx.x + i * gridDim.x, n-tile fastest), and the stage ring runs ahead across tile boundaries.
+//   WGRAD  P[z][m][n] = sum over the rows r of slice z of H[r][m] * G[r][n].  Both operands are loaded
+//          MN-major: a stage holds 4 atoms [32 r][32 m] of H and BN/32 atoms [32 r][32 n] of G, each 4 KB,
+//          exactly as a tensor-map box of the row-major matrices lands them.  The consumers transpose H into
+//          tensor memory (lane = m, column = r) and write G's lo plane beside the stage ring.
 #pragma once
 #include <cuda.h>
 
 #include <cstdint>
 
 #include "fused_mma_kernel.cuh"  // split_tf32, mbarrier helpers
-#include "tc_gemm.cuh"           // tc_mma, tc_commit, tc_load32
+#include "tc_gemm.cuh"           // tc_commit, tile constants
 
 namespace qb {
 
@@ -61,7 +65,7 @@ struct TcTmaArgs {
     int* error;
 };
 
-// PRELO (ROWS only): the lo plane of the weight operand is not computed per tile but loaded from a
+// PRELO (ROWS, always): the lo plane of the weight operand is not computed per tile but loaded from a
 // second matrix written once per step (tc2_prepare_launch); a stage then holds A, Bt and Bt_lo, the
 // ring has three stages, and the consumers convert the activation tile only.
 //
@@ -69,14 +73,14 @@ struct TcTmaArgs {
 // instruction, half the tensor-pipe time of two tf32 instructions).  Here hi is x rounded to nearest
 // tf32 (not the truncation the tensor core would apply), so |lo| = |x - hi| <= 2^-12 of x's binade, and a
 // correction product multiplies such a lo by a full-size value: rounding either factor to bfloat16
-// (relative error <= 2^-8) leaves an error of the order of 2^-21 of a term, about the float32 rounding
-// of the term itself (measured: 3e-7 relative rms on a 256-long product, as torch's float32 matmul).
+// (relative error <= 2^-8) leaves an error of the order of 2^-20 of a term (measured: 6.7e-7 relative rms on a
+// 64- to 256-long product; three tf32 products on truncated hi parts: 2.2e-7; torch's float32 matmul: 1.5-2.9e-7).
 // The weight operand comes prepared: Bt already rounded to tf32, and a pair of bfloat16 planes
 // [bf16(Bt) | bf16(lo(Bt))], each BN rows of 64 bytes per stage (64-byte swizzle).  The consumers write
 // the activation tile's tf32(x), bf16(x) and bf16(lo(x)) to tensor memory.
 template <bool WGRAD, int BN, bool PRELO = false, bool C16 = false>
 struct T2Geom {
-    static_assert(!(WGRAD && PRELO), "the weight gradient has no weight operand");
+    static_assert(WGRAD != PRELO, "ROWS loads the prepared weight planes; the weight gradient has no weight operand");
     static_assert(PRELO || !C16, "bfloat16 corrections need the prepared weight planes");
     static constexpr int STAGES = PRELO ? 3 : T2_STAGES;
     static constexpr int B_BYTES = BN * T2_BK * 4;
@@ -489,14 +493,6 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                     for (int i = 0; i < 16; ++i) xl[i] = t2_lo_bits(xh[i]);
                     t2_store16(ta + 32, xl);
                 }
-                // Weight tile: lo plane in shared memory, element by element (unless it was loaded).
-#pragma unroll
-                for (int i = 0; i < (PRELO ? 0 : (G::B_BYTES / 16) / T2_THREADS); ++i) {
-                    const int v = tid + i * T2_THREADS;
-                    const uint4 x = *reinterpret_cast<const uint4*>(hi + T2_A_BYTES + 16 * v);
-                    *reinterpret_cast<uint4*>(lo + 16 * v) =
-                        make_uint4(t2_lo_bits(x.x), t2_lo_bits(x.y), t2_lo_bits(x.z), t2_lo_bits(x.w));
-                }
                 QB_T2_PHASE(1);  // read, convert, issue the tensor-memory stores
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 QB_T2_PHASE(2);  // stores complete
@@ -559,21 +555,6 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
     __syncthreads();
     if (warp == ISSUE_WARP) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
-    }
-}
-
-// Bt[n][k] = W[k][n]: the K-major forward operand of a weight stored [K][N] row-major.
-__global__ void t2_transpose_kernel(const float* __restrict__ w, int K, int N, float* __restrict__ wt) {
-    __shared__ float tile[32][33];
-    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int k = k0 + r, n = n0 + threadIdx.x;
-        tile[r][threadIdx.x] = (k < K && n < N) ? w[(size_t)k * N + n] : 0.0f;
-    }
-    __syncthreads();
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int n = n0 + r, k = k0 + threadIdx.x;
-        if (n < N && k < K) wt[(size_t)n * K + k] = tile[threadIdx.x][r];
     }
 }
 
