@@ -144,8 +144,20 @@ __device__ __forceinline__ void first_layer_z(const FirstLayer<T>& f, long long 
                                               T (&x)[S][KIN], T (&z)[S][V]) {
 #pragma unroll
     for (int s = 0; s < S; ++s) {
+        const T* row = f.X + ((long long)s * f.C + point) * KIN;
+        if constexpr (KIN * sizeof(T) == 16) {
+            // One 16-byte load per stream (four float or two double inputs); the row is 16-byte aligned.
+            union {
+                uint4 q;
+                T v[KIN];
+            } u;
+            u.q = __ldg(reinterpret_cast<const uint4*>(row));
 #pragma unroll
-        for (int j = 0; j < KIN; ++j) x[s][j] = __ldg(f.X + ((long long)s * f.C + point) * KIN + j);
+            for (int j = 0; j < KIN; ++j) x[s][j] = u.v[j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < KIN; ++j) x[s][j] = __ldg(row + j);
+        }
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             T sum = T(0);

@@ -996,6 +996,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
     }();
     const bool first_fused = first_switch && head >= 2 && jet_first_inputs_ok(sz[0]) && jet_bias_fusable<T>(sz[1]) &&
                              jet_sig_eligible<T>(st.sig_code, (long long)C * sz[1], H_[1], G_[0], G_[1]) &&
+                             (reinterpret_cast<uintptr_t>(H_[0]) & 15) == 0 &&
                              (size_t)first_grid * (sz[0] + 1) * sz[1] <= wpartial_elems_;
     FirstLayer<T> first;
     first.X = H_[0];
