@@ -63,14 +63,15 @@ static bool make_map(CUtensorMap* map, const float* base, long long rows, int co
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// bfloat16 matrix [rows][cols], boxes of box_cols x box_rows under the 64-byte swizzle.
-static bool make_map16(CUtensorMap* map, const void* base, long long rows, int cols, int ld, int box_cols, int box_rows) {
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+// bfloat16 pair matrix of tc2_prepare_launch: [rows][2 * inner] halves, boxes of 64 halves (128 bytes) x box_rows under
+// the 128-byte swizzle.
+static bool make_map16(CUtensorMap* map, const void* base, long long rows, int inner, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)(2 * inner), (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)(2 * inner) * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return encode_tiled()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -102,10 +103,10 @@ cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const floa
     const int BN = N % 128 == 0 ? 128 : 64;
     CUtensorMap ma, mb, mblo, mc;
     if (Bt_lo == nullptr) return cudaErrorInvalidValue;
-    const bool c16 = tc_cor16();  // Bt_lo is then the pair of bfloat16 planes, 2N rows of K
+    const bool c16 = tc_cor16();  // Bt_lo is then the bfloat16 pair matrix, N rows of 2 K halves (dense: ldb == K)
     if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !(c16 ? make_map16(&mblo, Bt_lo, 2LL * N, K, ldb, T2_BK, BN)
+        !(c16 ? make_map16(&mblo, Bt_lo, N, K, BN)
               : make_map(&mblo, Bt_lo, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B)) ||
         !make_map(&mc, C, M, N, ldc, 32, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;

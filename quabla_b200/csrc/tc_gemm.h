@@ -19,17 +19,18 @@ bool tc_cor16();
 
 // float32 words of the per-layer weight image of a weight [K][N] (tc2_prepare_launch), four parts of K*N words:
 // [W^T | lo(W^T) | lo(W) | unused], or with bfloat16 corrections
-// [tf32(W^T) | bf16(W^T), bf16(lo(W^T)) | bf16(W), bf16(lo(W)) | tf32(W)].
+// [tf32(W^T) | pair matrix of W^T | pair matrix of W | tf32(W)]; a pair matrix holds per row and per 32 contraction
+// elements 32 x bf16(v) then 32 x bf16(v - tf32(v)), i.e. 128-byte rows that one tensor-map box brings per k-tile.
 size_t tc_image_words(int K, int N);
 
 // One pass over W [K][N]: wt = W^T [N][K], wt_lo = the lo plane of W^T, w_lo = the lo plane of W (each K*N floats;
 // w_hi is not written).  With bfloat16 corrections: wt = W^T rounded to tf32, w_hi = W rounded to tf32, and wt_lo
-// and w_lo each receive a pair of bfloat16 planes (the value, then its lo part x - tf32(x)).
+// and w_lo each receive the bfloat16 pair matrix described above.
 cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, float* w_hi,
                                cudaStream_t stream);
 // C[M][N] = A[M][K] * Bt^T (+ bias on the first bias_rows rows), Bt row-major [N][K].  Bt_lo (required)
-// is what tc2_prepare_launch wrote for Bt (its lo plane; or its pair of bfloat16 planes, and Bt is then
-// the tf32-rounded matrix written with them): the kernel loads it instead of computing a lo plane per tile.
+// is what tc2_prepare_launch wrote for Bt (its lo plane; or its bfloat16 pair matrix, and Bt is then
+// the tf32-rounded matrix written with it; ldb must equal K): the kernel loads it instead of computing a lo plane per tile.
 cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,
                             const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream);
 cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,

@@ -75,8 +75,8 @@ struct TcTmaArgs {
 // correction product multiplies such a lo by a full-size value: rounding either factor to bfloat16
 // (relative error <= 2^-8) leaves an error of the order of 2^-20 of a term (measured: 6.7e-7 relative rms on a
 // 64- to 256-long product; three tf32 products on truncated hi parts: 2.2e-7; torch's float32 matmul: 1.5-2.9e-7).
-// The weight operand comes prepared: Bt already rounded to tf32, and a pair of bfloat16 planes
-// [bf16(Bt) | bf16(lo(Bt))], each BN rows of 64 bytes per stage (64-byte swizzle).  The consumers write
+// The weight operand comes prepared: Bt already rounded to tf32, and a bfloat16 pair matrix whose 128-byte rows
+// hold [bf16(Bt) | bf16(lo(Bt))] of one k-tile (BN rows per stage, 128-byte swizzle).  The consumers write
 // the activation tile's tf32(x), bf16(x) and bf16(lo(x)) to tensor memory.
 template <bool WGRAD, int BN, bool PRELO = false, bool C16 = false>
 struct T2Geom {
@@ -108,11 +108,6 @@ struct T2Geom {
 __device__ __forceinline__ uint64_t t2_desc_kmajor(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-// K-major bfloat16 tile under the 64-byte swizzle (layout type 4): rows of 64 bytes, 8-row groups 512 bytes apart.
-__device__ __forceinline__ uint64_t t2_desc_kmajor64(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)4 << 61);
 }
 __device__ __forceinline__ uint64_t t2_desc_mnmajor(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)(4096 >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) |
@@ -311,10 +306,8 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                     t2_tma_load(stage, &map_a, k0, m0, full + s);               // box {32 k, 128 rows}
                     t2_tma_load(stage + T2_A_BYTES, &map_b, k0, n0, full + s);  // box {32 k, BN rows}
                     if (PRELO && !C16) t2_tma_load(stage + T2_A_BYTES + G::B_BYTES, &map_blo, k0, n0, full + s);
-                    if (C16) {  // rows n0.. of the bf16(Bt) plane, then of the bf16(lo(Bt)) plane a.N rows further on
-                        t2_tma_load(stage + T2_A_BYTES + G::B_BYTES, &map_blo, k0, n0, full + s);
-                        t2_tma_load(stage + T2_A_BYTES + G::B_BYTES + G::B_BYTES / 2, &map_blo, k0, a.N + n0, full + s);
-                    }
+                    // C16: 64 halves per row of the pair matrix, [bf16(Bt) | bf16(lo(Bt))] of this k-tile
+                    if (C16) t2_tma_load(stage + T2_A_BYTES + G::B_BYTES, &map_blo, 2 * k0, n0, full + s);
                 } else {
 #pragma unroll
                     for (int j = 0; j < T2_BM / 32; ++j) t2_tma_load(stage + j * 4096, &map_a, m0 + 32 * j, k0, full + s);
@@ -351,12 +344,13 @@ __global__ void __launch_bounds__(T2_THREADS_TOTAL, 1)
                     // Operand buffer b: x in columns 0-31, bf16(x) in 32-47, bf16(lo(x)) in 48-63; sixteen k
                     // (32 bytes of a weight-plane row) per instruction.
                     const uint32_t idesc16 = t2_idesc16(BN);
-                    const uint32_t b16h = bh + G::B_BYTES, b16l = b16h + G::B_BYTES / 2;
+                    // Rows of 128 bytes under the 128-byte swizzle: bf16(Bt) in bytes 0-63, bf16(lo(Bt)) in 64-127.
+                    const uint32_t b16h = bh + G::B_BYTES, b16l = b16h + 64;
 #pragma unroll
                     for (int kc = 0; kc < T2_BK / 16; ++kc) {
                         const uint32_t ta = tmem_base + (uint32_t)(A_COL0 + b * 64 + 32 + kc * 8);
-                        t2_mma16_tmem_a(dst, ta + 16, t2_desc_kmajor64(b16h + kc * 32), idesc16, kc == 0 ? 0u : 1u);
-                        t2_mma16_tmem_a(dst, ta, t2_desc_kmajor64(b16l + kc * 32), idesc16, 1u);
+                        t2_mma16_tmem_a(dst, ta + 16, t2_desc_kmajor(b16h + kc * 32), idesc16, kc == 0 ? 0u : 1u);
+                        t2_mma16_tmem_a(dst, ta, t2_desc_kmajor(b16l + kc * 32), idesc16, 1u);
                     }
                 }
 #pragma unroll
@@ -582,36 +576,32 @@ __global__ void t2_prepare_kernel(const float* __restrict__ w, int K, int N, flo
 }
 
 // The same pass for the C16 kernels, with hi(x) = x rounded to the nearest tf32 and lo(x) = x - hi(x):
-// wt = hi(W^T) and w_hi = hi(W) in float32, then bfloat16 planes [bf16(W^T) | bf16(lo(W^T))] (wt16, 2*K*N
-// halves) and [bf16(W) | bf16(lo(W))] (w16).
+// wt = hi(W^T) and w_hi = hi(W) in float32, then the bfloat16 pair matrices wt16 (of W^T) and w16 (of W), 2*K*N
+// halves each: a row holds, per 32 contraction elements, 32 x bf16(v) followed by 32 x bf16(lo(v)), so that one
+// tensor-map box of 128-byte rows brings both planes of a k-tile.
 __global__ void t2_prepare16_kernel(const float* __restrict__ w, int K, int N, float* __restrict__ wt,
                                     uint16_t* __restrict__ wt16, uint16_t* __restrict__ w16, float* __restrict__ w_hi) {
     __shared__ float tile[32][33];
-    const size_t kn = (size_t)K * N;
     const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
-    auto split = [](float v, float* hi32, uint16_t* hi, uint16_t* lo) {
+    // Row r of a pair matrix with `inner` contraction elements: per 32 of them, 64 halves [32 x bf16(v) | 32 x bf16(lo(v))].
+    auto split = [](float v, float* hi32, uint16_t* pair, size_t row, int inner, int c) {
         const float rounded = __uint_as_float(t2_round_tf32(__float_as_uint(v)));
         const uint32_t packed = t2_pack_bf16(v, v - rounded);
         *hi32 = rounded;
-        *hi = (uint16_t)(packed & 0xffffu);
-        *lo = (uint16_t)(packed >> 16);
+        uint16_t* at = pair + row * (2 * (size_t)inner) + (size_t)(c >> 5) * 64 + (c & 31);
+        at[0] = (uint16_t)(packed & 0xffffu);
+        at[32] = (uint16_t)(packed >> 16);
     };
     for (int r = threadIdx.y; r < 32; r += blockDim.y) {
         const int k = k0 + r, n = n0 + threadIdx.x;
         const float v = (k < K && n < N) ? w[(size_t)k * N + n] : 0.0f;
         tile[r][threadIdx.x] = v;
-        if (k < K && n < N) {
-            const size_t at = (size_t)k * N + n;
-            split(v, w_hi + at, w16 + at, w16 + kn + at);
-        }
+        if (k < K && n < N) split(v, w_hi + (size_t)k * N + n, w16, (size_t)k, N, n);
     }
     __syncthreads();
     for (int r = threadIdx.y; r < 32; r += blockDim.y) {
         const int n = n0 + r, k = k0 + threadIdx.x;
-        if (n < N && k < K) {
-            const size_t at = (size_t)n * K + k;
-            split(tile[threadIdx.x][r], wt + at, wt16 + at, wt16 + kn + at);
-        }
+        if (n < N && k < K) split(tile[threadIdx.x][r], wt + (size_t)n * K + k, wt16, (size_t)n, K, k);
     }
 }
 
