@@ -494,8 +494,8 @@ qb200_status Plan<T>::init() {
         wmax = std::max(wmax, (size_t)desc_.sizes[l] * desc_.sizes[l + 1]);
     }
     dmax = std::max(dmax, d0);
-    // 16 GB of the 180: the 3-D heat step (1,048,576 points, 86 KB of saved jets per point) then runs in seven
-    // chunks of 150 K points; it measured 115.8 ms with chunks of 65,536 points, 113.5-113.8 with 131,072 and 112.7
+    // 16 GB of the 180: the 3-D heat step (1,048,576 points, 86 KB of saved jets per point) then runs in six
+    // chunks of 175 K points; it measured 115.8 ms with chunks of 65,536 points, 113.5-113.8 with 131,072 and 112.7
     // with 174,592, and 126.6 / 139.5 / 176.0 with 18,944 / 9,472 / 4,608 (chunks small enough for a layer's planes
     // to stay in L2 between the kernel that writes them and the one that reads them lose more to the short
     // launches than they gain).
@@ -554,8 +554,8 @@ qb200_status Plan<T>::init() {
         const size_t S = st.spec.S;
         const size_t per_point = S * (sum_h + sum_z + 2 * (size_t)dmax + 2) * sizeof(T);
         long long chunk = (long long)std::min<size_t>(budget / per_point, (size_t)chunk_cap);
-        // Bound the split-K slices of a weight gradient.
-        chunk = std::min<long long>(chunk, (long long)K_CHUNK_ROWS * 256 / (long long)S);
+        // Bound the split-K slices of a weight gradient (512: the 3-D heat step then runs in six chunks).
+        chunk = std::min<long long>(chunk, (long long)K_CHUNK_ROWS * 512 / (long long)S);
         // With two lanes a set is cut into at least two chunks.
         if (n_lanes > 1 && s.n >= 16384) chunk = std::min<long long>(chunk, ((s.n + 1) / 2 + 255) / 256 * 256);
         if (chunk >= s.n) {
