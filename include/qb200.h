@@ -350,11 +350,12 @@ qb200_status qb200_weight_gradient(int32_t dtype, const void* d_acts, const void
  * the layer contraction h @ W (+ b) of the hot path (a1/a2: tensor_ir.rs:4968-4972,
  * op/batch.rs:58-79) for all streams at once.  N % 64 == 0, 64 <= N <= 256,
  * K % 32 == 0, all arrays row-major float32 on the device.  Synchronises the stream.
- * Each element is split as x = hi + lo with hi = x rounded to tf32; hi.hi runs as
- * tf32 instructions and the two correction products lo.x and x.lo as bfloat16
- * instructions (QB200_TC_COR=tf32 in the environment: all three as tf32 instructions
- * on truncated hi parts).  Error against a float64 product, K = 64..256: 7e-7 relative
- * rms (2e-7 with QB200_TC_COR=tf32; a float32 FMA product: 1.5e-7 to 3e-7).
+ * Each element is split as x = hi + lo.  M >= 65536: hi = x rounded to tf32, hi.hi runs
+ * as tf32 instructions and the two correction products lo.x and x.lo as bfloat16
+ * instructions; error against a float64 product, K = 64..256: 7e-7 relative rms, random.
+ * M < 65536: hi = x truncated to tf32 and all three products as tf32 instructions: 2e-7,
+ * most of it a common scale factor (a float32 FMA product: 1.5e-7 to 3e-7).
+ * QB200_TC_COR=tf32 or =bf16 in the environment forces one scheme for every M.
  * ------------------------------------------------------------------------ */
 qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d_bias, void* d_c, int64_t M,
                                  int32_t N, int32_t K, int64_t bias_rows, void* cuda_stream);

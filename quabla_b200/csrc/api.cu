@@ -660,12 +660,13 @@ qb200_status qb200_matmul_3xtf32(const void* d_a, const void* d_w, const void* d
     QB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int), s));
     // The K-major operand is W transposed, unsplit; its lo plane is written beside it.
     float* wt = reinterpret_cast<float*>(image);
+    const bool cor16 = qb::tc_cor16_for(M);
     cudaError_t e = qb::tc2_prepare_launch(static_cast<const float*>(d_w), K, N, wt, wt + (size_t)K * N,
-                                           wt + 2 * (size_t)K * N, wt + 3 * (size_t)K * N, s);
+                                           wt + 2 * (size_t)K * N, wt + 3 * (size_t)K * N, cor16, s);
     if (e == cudaSuccess)
         e = qb::tc2_rows_launch(static_cast<const float*>(d_a), K, wt, wt + (size_t)K * N, K, static_cast<float*>(d_c), N,
                                 static_cast<const float*>(d_bias), (int)std::min<int64_t>(bias_rows, M), (int)M, N, K,
-                                flag, s);
+                                cor16, flag, s);
     int host_flag = 0;
     if (e == cudaSuccess) e = cudaMemcpyAsync(&host_flag, flag, sizeof(int), cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);

@@ -229,7 +229,7 @@ class Plan final : public qb200_plan {
     bool tc_fwd_ok(int layer) const { return !tc_fwd_.empty() && tc_fwd_[layer]; }
     bool tc_bwd_ok(int layer) const { return !tc_bwd_.empty() && tc_bwd_[layer]; }
     // Tensor-pipe passes of a forward or data-gradient product at the bfloat16 rate (QB200_Q_GEMM_PIPE_FLOPS).
-    static double tc_rows_weight() { return tc_cor16() ? 4.0 : 6.0; }
+    static double tc_rows_weight(long long rows) { return tc_cor16_for(rows) ? 4.0 : 6.0; }
     bool tc_wgrad_ok_layer(int layer) const { return !tc_wgrad_.empty() && tc_wgrad_[layer]; }
     StepStatus<T> step_status(bool with_flat_flag) const {
         StepStatus<T> s;
@@ -917,7 +917,7 @@ qb200_status Plan<float>::tc_setup() {
         tc_fwd_[l] = tc_rows_ok(N, K);
         tc_bwd_[l] = l > 0 && tc_rows_ok(K, N);
         tc_wgrad_[l] = tc_wgrad_ok(K, N);
-        if (tc_fwd_[l] || tc_bwd_[l]) QB_TRY(dev_alloc(&tc_image_[l], tc_image_words(K, N)));
+        if (tc_fwd_[l] || tc_bwd_[l]) QB_TRY(dev_alloc(&tc_image_[l], 2 * tc_image_words(K, N)));  // one image per scheme
         tc_any_ = tc_any_ || tc_fwd_[l] || tc_bwd_[l] || tc_wgrad_[l];
     }
     return QB200_OK;
@@ -929,12 +929,20 @@ qb200_status Plan<float>::tc_prepare() {
         if (tc_image_[l] == nullptr) continue;
         // TMA kernels take the weight unsplit plus its lo plane: W itself for the data gradient, W^T for the
         // forward product.  Image: four parts of K*N words (tc_image_words).
+        // The first image serves launches with bfloat16 corrections, the second those with tf32 corrections; which
+        // of the two a launch takes depends on its rows (tc_cor16_for), so both are written unless one is forced.
         const size_t kn = (size_t)desc_.sizes[l] * desc_.sizes[l + 1];
-        float* image = reinterpret_cast<float*>(tc_image_[l]);
-        cudaError_t e = tc2_prepare_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], image, image + kn, image + 2 * kn,
-                                           image + 3 * kn, stream_);
-        ++launches_;
-        if (e != cudaSuccess) return fail(QB200_CUDA_ERROR, "launch of tc_prep_weight_kernel failed: %s", cudaGetErrorString(e));
+        const int mode = tc_cor_mode();
+        for (int scheme = 0; scheme < 2; ++scheme) {
+            const bool cor16 = scheme == 0;
+            if ((mode == 0 && cor16) || (mode == 1 && !cor16)) continue;
+            float* image = reinterpret_cast<float*>(tc_image_[l]) + (cor16 ? 0 : 4 * kn);
+            cudaError_t e = tc2_prepare_launch(weight(l), desc_.sizes[l], desc_.sizes[l + 1], image, image + kn, image + 2 * kn,
+                                               image + 3 * kn, cor16, stream_);
+            ++launches_;
+            if (e != cudaSuccess)
+                return fail(QB200_CUDA_ERROR, "launch of tc_prep_weight_kernel failed: %s", cudaGetErrorString(e));
+        }
     }
     return QB200_OK;
 }
@@ -943,9 +951,10 @@ template <>
 bool Plan<float>::tc_forward(int layer, const float* A, float* C, long long rows, int bias_rows, qb200_status* st) {
     if (!tc_fwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
-    cudaError_t e = tc2_rows_launch(A, K, reinterpret_cast<const float*>(tc_image_[layer]),
-                                    reinterpret_cast<const float*>(tc_image_[layer]) + (size_t)K * N, K, C, N, bias(layer),
-                                    bias_rows, (int)rows, N, K, d_error_, cs_);
+    const bool cor16 = tc_cor16_for(rows);
+    const float* image = reinterpret_cast<const float*>(tc_image_[layer]) + (cor16 ? 0 : 4 * (size_t)K * N);
+    cudaError_t e = tc2_rows_launch(A, K, image, image + (size_t)K * N, K, C, N, bias(layer), bias_rows, (int)rows, N, K, cor16,
+                                    d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(forward) failed: %s", cudaGetErrorString(e));
     return true;
@@ -956,9 +965,10 @@ bool Plan<float>::tc_dgrad(int layer, const float* G, float* Gprev, long long ro
     if (!tc_bwd_[layer]) return false;
     const int K = desc_.sizes[layer], N = desc_.sizes[layer + 1];
     // The weight itself is the K-major operand here (its tf32-rounded copy when the corrections run in bfloat16).
-    const float* image = reinterpret_cast<const float*>(tc_image_[layer]);
-    cudaError_t e = tc2_rows_launch(G, N, tc_cor16() ? image + 3 * (size_t)K * N : weight(layer), image + 2 * (size_t)K * N,
-                                    N, Gprev, K, nullptr, 0, (int)rows, K, N, d_error_, cs_);
+    const bool cor16 = tc_cor16_for(rows);
+    const float* image = reinterpret_cast<const float*>(tc_image_[layer]) + (cor16 ? 0 : 4 * (size_t)K * N);
+    cudaError_t e = tc2_rows_launch(G, N, cor16 ? image + 3 * (size_t)K * N : weight(layer), image + 2 * (size_t)K * N, N, Gprev,
+                                    K, nullptr, 0, (int)rows, K, N, cor16, d_error_, cs_);
     ++launches_;
     *st = e == cudaSuccess ? QB200_OK : fail(QB200_CUDA_ERROR, "launch of tc_gemm_kernel(dgrad) failed: %s", cudaGetErrorString(e));
     return true;
@@ -1034,7 +1044,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
         g.k_chunk = g.K;
         qb200_status tc_status = QB200_OK;
         const bool narrow = g.K <= 4 && g.N % 4 == 0 && g.N >= 32 && 256 % (g.N / 4) == 0;
-        if (tc_fwd_ok(l - 1) || !narrow) timer_begin(2.0 * (double)rows * g.N * g.K, tc_fwd_ok(l - 1) ? tc_rows_weight() : 0.0);
+        if (tc_fwd_ok(l - 1) || !narrow) timer_begin(2.0 * (double)rows * g.N * g.K, tc_fwd_ok(l - 1) ? tc_rows_weight(rows) : 0.0);
         if (tc_forward(l - 1, H_[l - 1], Z_[l], rows, C, &tc_status)) {
             QB_TRY(tc_status);
             timer_end();
@@ -1252,7 +1262,7 @@ qb200_status Plan<T>::run_chunk(int si, long long point0, int C, int partial_slo
             g.bias_rows = 0;
             g.k_chunk = g.K;
             qb200_status tc_status = QB200_OK;
-            timer_begin(2.0 * (double)rows * g.N * g.K, tc_bwd_ok(l - 1) ? tc_rows_weight() : 0.0);
+            timer_begin(2.0 * (double)rows * g.N * g.K, tc_bwd_ok(l - 1) ? tc_rows_weight(rows) : 0.0);
             if (tc_dgrad(l - 1, G_[cur], G_[cur ^ 1], rows, &tc_status)) {
                 QB_TRY(tc_status);
             } else {

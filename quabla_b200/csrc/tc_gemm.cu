@@ -13,21 +13,31 @@ static bool tc_switch_on() {
     return !(env != nullptr && strcmp(env, "0") == 0);
 }
 
-// The two correction products of the forward and data-gradient GEMMs run as bfloat16 instructions;
-// QB200_TC_COR=tf32 runs them as tf32 instructions (the plain 3xTF32 scheme).
-bool tc_cor16() {
-    static const bool on = [] {
-        const char* env = getenv("QB200_TC_COR");
-        return !(env != nullptr && strcmp(env, "tf32") == 0);
-    }();
-    return on;
+// Correction products of the forward and data-gradient GEMMs: bfloat16 instructions on tf32-rounded hi parts, or
+// tf32 instructions on truncated hi parts (the plain 3xTF32 scheme).  The bfloat16 scheme is about 9 % faster per
+// GEMM and leaves a random error of 6.7e-7 per output against ~1e-7 (its systematic part is smaller); in sums over
+// the rows of a launch (bias gradients above all) random errors shrink with the square root of the row count, so
+// it is used for launches of at least TC_COR16_MIN_ROWS rows, where it stays below what a plain float32 FMA product
+// leaves on a few hundred rows.  QB200_TC_COR=tf32 or =bf16 (read at every call) forces one scheme.
+constexpr long long TC_COR16_MIN_ROWS = 65536;
+
+int tc_cor_mode() {
+    const char* env = getenv("QB200_TC_COR");
+    if (env != nullptr && strcmp(env, "tf32") == 0) return 0;
+    if (env != nullptr && strcmp(env, "bf16") == 0) return 1;
+    return 2;
+}
+
+bool tc_cor16_for(long long rows) {
+    const int mode = tc_cor_mode();
+    return mode == 1 || (mode == 2 && rows >= TC_COR16_MIN_ROWS);
 }
 
 bool tc_rows_ok(int N, int K) { return N % 64 == 0 && N >= 64 && N <= 256 && K % TC_BK == 0 && K >= TC_BK; }
 
 bool tc_wgrad_ok(int Mw, int N) { return Mw % TC_BM == 0 && N % 64 == 0 && N >= 64 && N <= 256; }
 
-size_t tc_image_words(int K, int N) { return (size_t)4 * K * N; }
+size_t tc_image_words(int K, int N) { return (size_t)4 * K * N; }  // one image; a plan keeps one per scheme
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -76,8 +86,8 @@ static bool make_map16(CUtensorMap* map, const void* base, long long rows, int i
 }
 
 cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, float* w_hi,
-                               cudaStream_t stream) {
-    if (tc_cor16()) {
+                               bool cor16, cudaStream_t stream) {
+    if (cor16) {
         t2_prepare16_kernel<<<dim3((N + 31) / 32, (K + 31) / 32), dim3(32, 8), 0, stream>>>(
             w, K, N, wt, reinterpret_cast<uint16_t*>(wt_lo), reinterpret_cast<uint16_t*>(w_lo), w_hi);
         return cudaGetLastError();
@@ -99,11 +109,12 @@ static cudaError_t launch2(const CUtensorMap& ma, const CUtensorMap& mb, const C
 }
 
 cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,
-                            const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream) {
+                            const float* bias, int bias_rows, int M, int N, int K, bool cor16, int* error,
+                            cudaStream_t stream) {
     const int BN = N % 128 == 0 ? 128 : 64;
     CUtensorMap ma, mb, mblo, mc;
     if (Bt_lo == nullptr) return cudaErrorInvalidValue;
-    const bool c16 = tc_cor16();  // Bt_lo is then the bfloat16 pair matrix, N rows of 2 K halves (dense: ldb == K)
+    const bool c16 = cor16;  // Bt_lo is then the bfloat16 pair matrix, N rows of 2 K halves (dense: ldb == K)
     if (!make_map(&ma, A, M, K, lda, T2_BK, T2_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map(&mb, Bt, N, K, ldb, T2_BK, BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !(c16 ? make_map16(&mblo, Bt_lo, N, K, BN)

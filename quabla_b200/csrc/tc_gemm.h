@@ -13,9 +13,11 @@ bool tc_wgrad_ok(int Mw, int N);   // P = H^T G with H [rows][Mw], G [rows][N]: 
 // Whether the tensor-core GEMMs can run: QB200_TC=0 switches them off, and the driver must provide the
 // tensor-map encoder (operands arrive by TMA tensor maps).
 bool tc_available();
-// Whether the correction products of the forward and data-gradient GEMMs run as bfloat16 instructions
-// (the default) or as tf32 instructions (QB200_TC_COR=tf32).
-bool tc_cor16();
+// Scheme of the forward and data-gradient GEMMs for a launch of `rows` rows: true = hi parts rounded to tf32 and
+// the correction products as bfloat16 instructions (launches of 65,536 rows and more), false = three tf32 products
+// on truncated hi parts.  QB200_TC_COR=tf32|bf16 forces one; tc_cor_mode() is 0 / 1 for those and 2 otherwise.
+bool tc_cor16_for(long long rows);
+int tc_cor_mode();
 
 // float32 words of the per-layer weight image of a weight [K][N] (tc2_prepare_launch), four parts of K*N words:
 // [W^T | lo(W^T) | lo(W) | unused], or with bfloat16 corrections
@@ -27,12 +29,13 @@ size_t tc_image_words(int K, int N);
 // w_hi is not written).  With bfloat16 corrections: wt = W^T rounded to tf32, w_hi = W rounded to tf32, and wt_lo
 // and w_lo each receive the bfloat16 pair matrix described above.
 cudaError_t tc2_prepare_launch(const float* w, int K, int N, float* wt, float* wt_lo, float* w_lo, float* w_hi,
-                               cudaStream_t stream);
+                               bool cor16, cudaStream_t stream);
 // C[M][N] = A[M][K] * Bt^T (+ bias on the first bias_rows rows), Bt row-major [N][K].  Bt_lo (required)
 // is what tc2_prepare_launch wrote for Bt (its lo plane; or its bfloat16 pair matrix, and Bt is then
 // the tf32-rounded matrix written with it; ldb must equal K): the kernel loads it instead of computing a lo plane per tile.
 cudaError_t tc2_rows_launch(const float* A, int lda, const float* Bt, const float* Bt_lo, int ldb, float* C, int ldc,
-                            const float* bias, int bias_rows, int M, int N, int K, int* error, cudaStream_t stream);
+                            const float* bias, int bias_rows, int M, int N, int K, bool cor16, int* error,
+                            cudaStream_t stream);
 cudaError_t tc2_wgrad_launch(const float* H, int ldh, const float* G, int ldg, float* partials, int rows, int Mw, int N,
                              int rows_per_slice, int* error, cudaStream_t stream);
 

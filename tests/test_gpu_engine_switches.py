@@ -26,8 +26,8 @@ def _run(name, points, **switches):
     return json.loads(out.stdout.strip().splitlines()[-1])
 
 
-@pytest.mark.parametrize("switches", [{}, {"QB200_TC_COR": "tf32"}, {"QB200_TC": "0"}],
-                         ids=["tcgen05, bf16 corrections", "tcgen05, tf32 corrections", "simt"])
+@pytest.mark.parametrize("switches", [{}, {"QB200_TC_COR": "bf16"}, {"QB200_TC_COR": "tf32"}, {"QB200_TC": "0"}],
+                         ids=["tcgen05, scheme by size", "tcgen05, bf16 corrections", "tcgen05, tf32 corrections", "simt"])
 def test_wide_float32_network_on_every_gemm_variant(cuda_device, switches):
     result = _run("heat3d", 640, **switches)
     assert result["engine"] == (0 if switches.get("QB200_TC") == "0" else 3)
