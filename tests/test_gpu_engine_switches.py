@@ -108,3 +108,35 @@ def test_two_lanes_are_repeatable_and_agree_with_one_lane(cuda_device, monkeypat
     two, one = run("2"), run("1")
     for a, b in zip(two, one):
         assert relative_error(a, b) <= 1e-12
+
+
+@pytest.mark.parametrize("scheme,passes", [("tf32", 6.0), ("bf16", 14.0 / 3.0)])
+def test_gemm_timers_report_flops_and_tensor_pipe_passes(cuda_device, monkeypatch, scheme, passes):
+    # With QB200_OPT_KERNEL_TIMERS the plan reports, for the layer GEMMs of the last execute, launches, device time,
+    # 2MNK and the tensor-pipe passes behind them at the bfloat16 rate: 6 per FLOP for three tf32 products, 4 where
+    # the two correction products are bfloat16 instructions (forward and data gradient; the weight gradient keeps 6).
+    from quabla_b200 import _lib
+    from quabla_b200._plan import Plan
+
+    from _util import traced
+
+    monkeypatch.setenv("QB200_TC_COR", scheme)
+    w, compiled, inputs = traced("heat3d", 1024)
+    plan = Plan(compiled.spec, 0)
+    for key, value in inputs.items():
+        plan.bind(key, value)
+    plan.set_option(_lib.OPT_KERNEL_TIMERS, 1)
+    plan.execute()
+    plan.synchronize()
+    launches = plan.query(_lib.Q_GEMM_LAUNCHES)
+    flops = plan.query(_lib.Q_GEMM_FLOPS)
+    pipe = plan.query(_lib.Q_GEMM_PIPE_FLOPS)
+    nanoseconds = plan.query(_lib.Q_GEMM_NANOSECONDS)
+    plan.close()
+    # Five 256 x 256 layers: forward, data gradient (not for the first of them... the first hidden layer has no GEMM
+    # at all) and weight gradient each.
+    assert launches == 15
+    rows = 1024 * compiled.spec.sets[0].streams
+    assert flops == 15 * 2 * rows * 256 * 256
+    assert nanoseconds > 0
+    assert abs(pipe / flops - passes) < 1e-9
