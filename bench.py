@@ -631,6 +631,9 @@ def main() -> None:
                      "kernel_us": kernel["us_per_launch"], "flops_per_launch": kernel["flops_per_launch"],
                      "kernel_us_per_step": kernel["us_per_step"],
                      "peak_source": f"{peak_kind}: {main_result['peak_source']}",
+                     # the fraction against the plain 3xTF32 denominator (6 passes per FLOP), comparable across schemes
+                     "frac_at_six_passes": (main_result["kernel_tflops"] * 6.0 / (main_result["peak_tflops"] * kernel["bf16_rate_passes_per_flop"])
+                                            if main_result["dtype"] == "f32" and kernel["bf16_rate_passes_per_flop"] else None),
                      # the same fraction against the library's TF32 GEMM timed in this run (tf32 = 2 bf16-rate passes)
                      "frac_of_library_tf32_gemm": (main_result["kernel_tflops"] * kernel["bf16_rate_passes_per_flop"] / 2.0
                                                    / live["tf32_gemm_tflops"] if main_result["dtype"] == "f32" else None)},
